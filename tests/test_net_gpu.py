@@ -1,0 +1,186 @@
+"""GPU parity of the device-resident Network (forward, trainStep, train, the pipelined
+step) against the oracle's restatement of Network.trainStep, on the benchmark
+configurations' shapes at sizes the single-threaded oracle finishes in seconds."""
+import numpy as np
+import pytest
+
+import zigneuron_b200 as zn
+from oracle import zn_oracle as zo
+from util import assert_close, iris_style, reference_init, rel_l2
+
+pytestmark = pytest.mark.gpu
+P = zn.Precision
+OACT = {"relu": zo.RELU, "linear": zo.LINEAR, "sigmoid": zo.SIGMOID, "tanh": zo.TANH}
+OLOSS = {zn.Loss.mse: zo.MSE, zn.Loss.cross_entropy_logits: zo.CE_LOGITS}
+
+
+@pytest.fixture(scope="module")
+def be():
+    b = zn.Backend(0)
+    yield b
+    b.deinit()
+
+
+def build_pair(be, prec, dims, acts, seed, adam=False, bias_scale=0.0):
+    """The same seeded weights in a GPU network and an oracle network."""
+    rng = np.random.default_rng(seed)
+    gnet, onet = zn.Network(be, prec), zo.Net()
+    for i, ((a, b), act) in enumerate(zip(dims, acts)):
+        gnet.addDense(a, b, act)
+        onet.add_dense(a, b, OACT[act])
+        W = reference_init(rng, a, b, act)
+        bias = (rng.uniform(-1, 1, b) * bias_scale).astype(np.float32)
+        gnet.setWeights(i, W, bias)
+        onet.set_params(i, W, bias)
+        if adam:
+            onet.set_adam(i)
+    if adam:
+        gnet.setOptimizer(zn.Adam())
+    return gnet, onet
+
+
+def compare_params(gnet, onet, tol, what):
+    for i in range(len(gnet.shapes)):
+        W, b = gnet.getWeights(i)
+        oW, ob = onet.get_params(i)
+        assert_close(W, oW, tol, f"{what} W{i}")
+        assert_close(b, ob, tol, f"{what} b{i}") if np.abs(ob).max() > 0 else None
+
+
+IRIS_DIMS, IRIS_ACTS = [(4, 20), (20, 10), (10, 3)], ["relu", "relu", "linear"]
+
+
+@pytest.mark.parametrize("prec,tol", [(P.FP32_EXACT, 2e-6), (P.FP32_SIMT, 1e-5), (P.TF32_TC, 2e-2), (P.BF16_TC, 2e-2)])
+def test_iris_style_full_batch(be, prec, tol):
+    """Config 1: 4-20-10-3, cross-entropy with logits, SGD lr 0.005, full batch of 150."""
+    x, t = iris_style(0)
+    gnet, onet = build_pair(be, prec, IRIS_DIMS, IRIS_ACTS, seed=0)
+    out = gnet.forward(x)
+    assert_close(out, onet.forward(x, 150), tol, "forward")
+    for step in range(40):
+        lg = gnet.trainStep(x, t, 0.005, zn.Loss.cross_entropy_logits)
+        lo = onet.train_step(x, t, 150, 0.005, zo.CE_LOGITS)
+        assert abs(lg - lo) <= tol * max(1.0, abs(lo)), (step, lg, lo)
+        gn, gf = gnet.lastClip()
+        on, of = onet.last_clip()
+        assert abs(gn - on) <= tol * on and abs(gf - of) <= tol * of
+    for i in range(3):
+        gW, gb = gnet.getGrads(i)
+        oW, ob = onet.get_grads(i)
+        assert_close(gW, oW, tol * 5, f"gW{i}")
+        assert_close(gb, ob, tol * 5, f"gb{i}")
+    compare_params(gnet, onet, tol, prec.name)
+
+
+@pytest.mark.parametrize("prec,tol", [(P.FP32_EXACT, 1e-5), (P.FP32_SIMT, 1e-5)])
+def test_per_sample_train_matches_reference_loop(be, prec, tol):
+    """Network.train: one step per sample, epoch loss = mean of sample losses (src/network.zig:596-616)."""
+    x, t = iris_style(0)
+    x, t = x[::5], t[::5]          # 30 samples
+    gnet, onet = build_pair(be, prec, IRIS_DIMS, IRIS_ACTS, seed=0)
+    got = gnet.train(x, t, 4, 0.005, zn.Loss.cross_entropy_logits)
+    want = onet.train(x, t, 4, 0.005, zo.CE_LOGITS)
+    assert np.allclose(got, want, rtol=tol, atol=1e-6), (got, want)
+    compare_params(gnet, onet, tol, "train")
+
+
+@pytest.mark.parametrize("prec,tol", [(P.FP32_EXACT, 1e-5), (P.FP32_SIMT, 1e-5), (P.TF32_TC, 2e-2), (P.BF16_TC, 2e-2)])
+def test_mlp_784_adam(be, prec, tol):
+    """Config 2 shapes (784-512-256-10, Adam, CE) at batch 256, 6 steps."""
+    rng = np.random.default_rng(1)
+    B = 256
+    x = rng.uniform(0, 1, (B, 784)).astype(np.float32)
+    t = np.eye(10, dtype=np.float32)[rng.integers(0, 10, B)]
+    gnet, onet = build_pair(be, prec, [(784, 512), (512, 256), (256, 10)], ["relu", "relu", "linear"], seed=1, adam=True)
+    for step in range(6):
+        lg = gnet.trainStep(x, t, 1e-3, zn.Loss.cross_entropy_logits)
+        lo = onet.train_step(x, t, B, 1e-3, zo.CE_LOGITS)
+        assert abs(lg - lo) <= tol * max(1.0, abs(lo)), (step, lg, lo)
+    compare_params(gnet, onet, tol, prec.name)
+
+
+@pytest.mark.parametrize("prec,tol", [(P.FP32_SIMT, 1e-5), (P.TF32_TC, 2e-2), (P.BF16_TC, 2e-2)])
+def test_wide_mlp_mse_gradients(be, prec, tol):
+    """Config 3's structure (relu x3, linear, MSE, SGD) at 1/16 width: gradients of one step."""
+    rng = np.random.default_rng(2)
+    B, dims = 512, [(256, 512), (512, 512), (512, 512), (512, 256)]
+    acts = ["relu", "relu", "relu", "linear"]
+    x = rng.standard_normal((B, 256)).astype(np.float32)
+    t = rng.standard_normal((B, 256)).astype(np.float32)
+    gnet, onet = build_pair(be, prec, dims, acts, seed=2, bias_scale=0.1)
+    lg = gnet.trainStep(x, t, 1e-3, zn.Loss.mse)
+    lo = onet.train_step(x, t, B, 1e-3, zo.MSE)
+    assert abs(lg - lo) <= tol * abs(lo)
+    for i in range(4):
+        gW, gb = gnet.getGrads(i)
+        oW, ob = onet.get_grads(i)
+        assert_close(gW, oW, tol, f"gW{i}")
+        assert_close(gb, ob, tol, f"gb{i}")
+    compare_params(gnet, onet, tol, prec.name)
+    # gradient with respect to the input: the reference computes it for layer 0 too
+    gx = gnet.getInputGrad(B)
+    assert gx.shape == (B, 256) and np.isfinite(gx).all() and np.abs(gx).max() > 0
+
+
+def test_activations_beyond_relu(be):
+    rng = np.random.default_rng(3)
+    B = 64
+    x = rng.standard_normal((B, 24)).astype(np.float32)
+    t = rng.standard_normal((B, 8)).astype(np.float32)
+    for prec, tol in [(P.FP32_SIMT, 1e-5), (P.BF16_TC, 2e-2)]:
+        gnet, onet = build_pair(be, prec, [(24, 40), (40, 16), (16, 8)], ["tanh", "sigmoid", "relu"], seed=3, bias_scale=0.1)
+        for _ in range(3):
+            lg = gnet.trainStep(x, t, 0.01, zn.Loss.mse)
+            lo = onet.train_step(x, t, B, 0.01, zo.MSE)
+            assert abs(lg - lo) <= tol * abs(lo)
+        compare_params(gnet, onet, tol, prec.name)
+
+
+def test_pipelined_step_equals_blocking_step(be):
+    rng = np.random.default_rng(4)
+    B, dims, acts = 128, [(32, 64), (64, 16)], ["relu", "linear"]
+    xs = [rng.standard_normal((B, 32)).astype(np.float32) for _ in range(5)]
+    ts = [rng.standard_normal((B, 16)).astype(np.float32) for _ in range(5)]
+    a, _ = build_pair(be, P.FP32_SIMT, dims, acts, seed=4)
+    b, _ = build_pair(be, P.FP32_SIMT, dims, acts, seed=4)
+    want = [a.trainStep(x, t, 0.01, zn.Loss.mse) for x, t in zip(xs, ts)]
+    got = []
+    b.submitStep(xs[0], ts[0], B, 0.01, zn.Loss.mse)
+    for i in range(1, 5):
+        b.submitStep(xs[i], ts[i], B, 0.01, zn.Loss.mse)
+        got.append(b.waitStep())
+    got.append(b.waitStep())
+    assert got == want
+    for i in range(2):
+        assert np.array_equal(a.getWeights(i)[0], b.getWeights(i)[0])
+    with pytest.raises(zn.ZnError):
+        b.waitStep()
+
+
+def test_batch_size_may_shrink_and_grow(be):
+    """The reference infers the batch from cache capacity and breaks when it shrinks
+    (src/network.zig:468-471 with :325-332); here the row count is explicit."""
+    rng = np.random.default_rng(5)
+    gnet, onet = build_pair(be, P.FP32_SIMT, [(8, 12), (12, 4)], ["relu", "linear"], seed=5)
+    for B in (64, 7, 130, 1):
+        x = rng.standard_normal((B, 8)).astype(np.float32)
+        t = rng.standard_normal((B, 4)).astype(np.float32)
+        lg = gnet.trainStep(x, t, 0.01, zn.Loss.mse)
+        lo = onet.train_step(x, t, B, 0.01, zo.MSE)
+        assert abs(lg - lo) <= 1e-5 * abs(lo)
+    compare_params(gnet, onet, 1e-5, "resize")
+
+
+def test_shape_errors(be):
+    net = zn.Network(be, P.FP32_SIMT)
+    with pytest.raises(zn.ZnError) as ei:
+        net.addDense(0, 4, "relu")           # error.InvalidInputSize, src/layer.zig:307
+    assert ei.value.status == 7
+    net.addDense(4, 8, "relu")
+    with pytest.raises(zn.ZnError):
+        net.addDense(5, 2, "linear")         # does not chain
+    with pytest.raises(zn.ZnError):
+        net.addDense(8, 2, "gelu")
+    net.addDense(8, 2, "linear")
+    with pytest.raises(zn.ZnError):
+        net.trainStep(np.zeros((2, 4), np.float32), np.zeros((2, 2), np.float32), 0.1, zn.Loss.kl_divergence)

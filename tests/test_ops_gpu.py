@@ -1,0 +1,293 @@
+"""GPU parity of every Backend op on the Dense path against the CPU oracle, through
+the C ABI.  Tolerances: bit-exact for FP32_EXACT GEMMs and element-wise ops; 1e-5
+relative (L2 and max norm) for the fp32 FMA path; 2e-2 for TF32/BF16 tensor-core
+GEMMs on raw inputs, and 1e-5 again when the inputs are pre-rounded to the operand
+type (which isolates the kernel from the input rounding)."""
+import numpy as np
+import pytest
+
+import zigneuron_b200 as zn
+from oracle import zn_oracle as zo
+from util import assert_close, rel_l2, round_bf16, trunc_tf32
+
+pytestmark = pytest.mark.gpu
+
+P = zn.Precision
+
+
+@pytest.fixture(scope="module")
+def be():
+    b = zn.Backend(0)
+    yield b
+    b.deinit()
+
+
+def _operands(rng, orient, m, n, k):
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    return a, b
+
+
+def _store(orient, a, b):
+    """Memory layout each entry point expects."""
+    if orient == "NN":
+        return np.ascontiguousarray(a), np.ascontiguousarray(b)
+    if orient == "TN":
+        return np.ascontiguousarray(a.T), np.ascontiguousarray(b)      # A stored [k][m]
+    return np.ascontiguousarray(a), np.ascontiguousarray(b.T)          # B stored [n][k]
+
+
+def _oracle(orient, sa, sb, m, n, k, c=None, acc=False):
+    f = {"NN": zo.matmul, "TN": zo.matmul_transpose_a, "NT": zo.matmul_transpose_b}[orient]
+    return f(sa, sb, m, n, k, c=c, accumulate=acc)
+
+
+def _gpu(be, orient, sa, sb, m, n, k, c=None, acc=False):
+    out = np.zeros((m, n), np.float32) if c is None else c.copy()
+    f = {"NN": be.matMul, "TN": be.matMulTransposeA, "NT": be.matMulTransposeB}[orient]
+    f(sa, sb, out, m, n, k, acc)
+    return out
+
+
+SHAPES = [(2, 2, 3), (64, 64, 64), (150, 20, 4), (1, 10, 256), (129, 257, 65), (1024, 512, 784), (300, 130, 1000)]
+
+
+@pytest.mark.parametrize("orient", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_fp32(be, orient, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(4)
+    sa, sb = _store(orient, *_operands(rng, orient, m, n, k))
+    want = _oracle(orient, sa, sb, m, n, k)
+    be.set_precision(P.FP32_EXACT)
+    got = _gpu(be, orient, sa, sb, m, n, k)
+    assert np.array_equal(got, want), f"exact path differs: {rel_l2(got, want):.3e}"
+    be.set_precision(P.FP32_SIMT)
+    assert_close(_gpu(be, orient, sa, sb, m, n, k), want, 1e-5, f"simt {orient} {shape}")
+
+
+def test_gemm_golden_vectors(be):
+    """The reference's own known answers (src/test/unit/backend.zig:196-250)."""
+    be.set_precision(P.FP32_SIMT)
+    a = np.array([1, 2, 3, 4, 5, 6], np.float32)
+    b = np.array([7, 8, 9, 10, 11, 12], np.float32)
+    c = np.zeros(4, np.float32)
+    be.matMul(a, b, c, 2, 2, 3)
+    assert np.allclose(c, [58, 64, 139, 154], atol=1e-4)
+    ones = np.ones(64 * 64, np.float32)
+    c = np.zeros(64 * 64, np.float32)
+    for prec in (P.FP32_SIMT, P.TF32_TC, P.BF16_TC):
+        be.set_precision(prec)
+        be.matMul(ones, ones, c, 64, 64, 64)
+        assert np.allclose(c, 64.0, atol=1e-4), prec
+
+
+@pytest.mark.parametrize("orient", ["NN", "NT", "TN"])
+def test_gemm_accumulate(be, orient):
+    m, n, k = 70, 40, 33
+    rng = np.random.default_rng(5)
+    sa, sb = _store(orient, *_operands(rng, orient, m, n, k))
+    c0 = rng.standard_normal((m, n)).astype(np.float32)
+    want = _oracle(orient, sa, sb, m, n, k, c=c0, acc=True)
+    be.set_precision(P.FP32_EXACT)
+    assert np.array_equal(_gpu(be, orient, sa, sb, m, n, k, c=c0, acc=True), want)
+    be.set_precision(P.BF16_TC)
+    assert_close(_gpu(be, orient, sa, sb, m, n, k, c=c0, acc=True), want, 2e-2)
+
+
+TC_SHAPES = [(128, 256, 64), (256, 512, 256), (300, 200, 100), (130, 10, 256), (1024, 512, 784), (64, 2048, 1500),
+             (2048, 1024, 512)]
+
+
+@pytest.mark.parametrize("prec", [P.BF16_TC, P.TF32_TC])
+@pytest.mark.parametrize("orient", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_gemm_tensor_core(be, prec, orient, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(4)
+    a, b = _operands(rng, orient, m, n, k)
+    be.set_precision(prec)
+    # (1) raw fp32 inputs: the bar for the tensor-core path is 2e-2
+    sa, sb = _store(orient, a, b)
+    want = _oracle(orient, sa, sb, m, n, k)
+    assert_close(_gpu(be, orient, sa, sb, m, n, k), want, 2e-2, f"{prec.name} {orient} {shape}")
+    # (2) inputs already representable in the operand type: only accumulation order differs
+    rnd = round_bf16 if prec == P.BF16_TC else trunc_tf32
+    sa, sb = _store(orient, rnd(a), rnd(b))
+    want = _oracle(orient, sa, sb, m, n, k)
+    assert_close(_gpu(be, orient, sa, sb, m, n, k), want, 1e-5, f"{prec.name} {orient} {shape} pre-rounded")
+
+
+@pytest.mark.parametrize("prec", [P.FP32_EXACT, P.FP32_SIMT, P.TF32_TC, P.BF16_TC])
+@pytest.mark.parametrize("act", ["linear", "relu", "sigmoid", "tanh"])
+def test_matmul_bias_act(be, prec, act):
+    batch, n, k = 200, 96, 72
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((batch, k)).astype(np.float32)
+    w = rng.standard_normal((k, n)).astype(np.float32)
+    bias = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+    want = zo.activation_forward(getattr(zo, act.upper()), zo.add_bias(zo.matmul(a, w, batch, n, k), bias))
+    be.set_precision(prec)
+    got = np.zeros((batch, n), np.float32)
+    be._mm_bias(a, w, bias, got, batch, n, k, zn.Activation[act])
+    if prec == P.FP32_EXACT and act in ("linear", "relu"):
+        assert np.array_equal(got, want)
+    else:
+        assert_close(got, want, 1e-5 if prec in (P.FP32_EXACT, P.FP32_SIMT) else 2e-2, f"{prec.name} {act}")
+
+
+def test_bias_ops(be):
+    rng = np.random.default_rng(6)
+    for rows, cols in [(1, 1), (150, 3), (1024, 10), (4097, 513), (64, 8192)]:
+        out = rng.standard_normal((rows, cols)).astype(np.float32)
+        bias = rng.standard_normal(cols).astype(np.float32)
+        want = zo.add_bias(out, bias)
+        got = out.copy()
+        be.addBias(got, bias)
+        assert np.array_equal(got, want)
+        gb0 = rng.standard_normal(cols).astype(np.float32)
+        want = zo.accumulate_bias(gb0, out)
+        be.set_precision(P.FP32_EXACT)
+        got = gb0.copy()
+        be.accumulateBias(got, out)
+        assert np.array_equal(got, want), (rows, cols)
+        be.set_precision(P.FP32_SIMT)
+        got = gb0.copy()
+        be.accumulateBias(got, out)
+        # a blocked sum of `rows` terms: bound the error against the size of the terms
+        assert np.max(np.abs(got - want)) <= 1e-5 * max(1.0, np.sqrt(rows)) * np.max(np.abs(out)), (rows, cols)
+
+
+def test_activations(be):
+    # reference vectors: src/test/cuda/operations.zig:201-258
+    x = np.array([-1.0, -0.5, 0.0, 0.5, 1.0, 2.0], np.float32)
+    y = np.empty_like(x)
+    be.activationForward(zn.Activation.relu, x, y)
+    assert np.array_equal(y, [0, 0, 0, 0.5, 1, 2])
+    gi = np.empty_like(x)
+    be.activationBackward(zn.Activation.relu, y, np.ones(6, np.float32), gi)
+    assert np.array_equal(gi, [0, 0, 0, 1, 1, 1])
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal(10007).astype(np.float32) * 3
+    g = rng.standard_normal(10007).astype(np.float32)
+    for name in ("relu", "linear", "sigmoid", "tanh"):
+        act, oact = zn.Activation[name], getattr(zo, name.upper())
+        y = np.empty_like(x)
+        be.activationForward(act, x, y)
+        want = zo.activation_forward(oact, x)
+        if name in ("relu", "linear"):
+            assert np.array_equal(y, want)
+        else:
+            assert_close(y, want, 1e-6, name)
+        gi = np.empty_like(x)
+        be.activationBackward(act, want, g, gi)
+        assert np.array_equal(gi, zo.activation_backward(oact, want, g)), name
+    x2 = x.copy()
+    be.activationForward(zn.Activation.relu, x2, x2)      # in place, as Dense.forward does
+    assert np.array_equal(x2, np.maximum(x, 0))
+    with pytest.raises(zn.ZnError):
+        be.activationForward(zn.Activation.gelu, x, y)
+
+
+def test_losses(be):
+    # golden: src/test/unit/loss.zig:14-42, :75-87
+    assert abs(be.lossForward(zn.Loss.mse, np.array([1, 2, 3], np.float32), np.array([0, 1, 2], np.float32)) - 1.0) < 1e-6
+    g = np.empty(2, np.float32)
+    be.lossBackward(zn.Loss.mse, np.array([1, 2], np.float32), np.array([0, 1], np.float32), g)
+    assert np.allclose(g, [1, 1], atol=1e-6)
+    be.lossBackward(zn.Loss.cross_entropy_logits, np.zeros(2, np.float32), np.array([1, 0], np.float32), g)
+    assert np.allclose(g, [-0.5, 0.5], atol=1e-6)
+    rng = np.random.default_rng(8)
+    for rows, cols in [(1, 3), (150, 3), (1024, 10), (33, 1000), (513, 4096)]:
+        o = rng.standard_normal((rows, cols)).astype(np.float32) * 2
+        t = np.eye(cols, dtype=np.float32)[rng.integers(0, cols, rows)]
+        tm = rng.standard_normal((rows, cols)).astype(np.float32)
+        g = np.empty((rows, cols), np.float32)
+        be.lossBackward(zn.Loss.mse, o, tm, g, rows)
+        assert np.array_equal(g, zo.loss_backward(zo.MSE, o, tm, rows, cols))
+        got = be.lossForward(zn.Loss.mse, o, tm, rows)
+        exact = float(np.mean((o.astype(np.float64) - tm) ** 2))
+        assert abs(got - exact) <= 1e-6 * exact
+        # the oracle's single running f32 sum loses digits on long inputs; allow for ITS error there
+        assert abs(got - zo.loss_forward(zo.MSE, o, tm, rows, cols)) <= (1e-5 if rows * cols <= 200000 else 5e-4) * exact
+        be.lossBackward(zn.Loss.cross_entropy_logits, o, t, g, rows)
+        assert_close(g, zo.loss_backward(zo.CE_LOGITS, o, t, rows, cols), 1e-5, f"ce grad {rows}x{cols}")
+        got = be.lossForward(zn.Loss.cross_entropy_logits, o, t, rows)
+        want = zo.loss_forward(zo.CE_LOGITS, o, t, rows, cols)
+        assert abs(got - want) <= 1e-5 * max(1.0, abs(want)), (rows, cols)
+    with pytest.raises(zn.ZnError):
+        be.lossForward(zn.Loss.binary_cross_entropy, o, t, rows)
+
+
+def test_optimizers(be):
+    rng = np.random.default_rng(9)
+    n = 100003
+    w = rng.standard_normal(n).astype(np.float32) * 40
+    g = rng.standard_normal(n).astype(np.float32) * 4
+    g[::97] = np.nan
+    g[5::101] = 77.0
+    for lr, wd in [(0.01, 0.0), (0.5, 0.01)]:
+        got = w.copy()
+        be.sgdUpdate(got, g, lr, wd)
+        assert np.array_equal(got, zo.sgd_update(w, g, lr, wd))
+    got = w.copy()
+    be.sgdUpdateBias(got, g, 2.0)
+    assert np.array_equal(got, zo.sgd_update_bias(w, g, 2.0))
+    m = rng.standard_normal(n).astype(np.float32) * 0.1
+    v = np.abs(rng.standard_normal(n)).astype(np.float32) * 0.01
+    for t in (1, 2, 100):
+        bc1, bc2 = zo.adam_bias_corrections(0.9, 0.999, t)
+        ww, mm, vv = zo.adam_update(w, g, m, v, 1e-3, 0.9, 0.999, 1e-8, bc1, bc2)
+        gw, gm, gv = w.copy(), m.copy(), v.copy()
+        be.adamUpdate(gw, g, gm, gv, 1e-3, 0.9, 0.999, 1e-8, bc1, bc2)
+        assert np.array_equal(gm, mm) and np.array_equal(gv, vv)
+        assert np.array_equal(gw, ww)
+    # golden: w 0.5, g 0.1, lr 1e-3, t = 1 -> 0.499 (src/test/unit/optimizer.zig:66-88, src/backend.zig:2760-2772)
+    w1, m1, v1 = np.array([0.5], np.float32), np.zeros(1, np.float32), np.zeros(1, np.float32)
+    bc1, bc2 = zo.adam_bias_corrections(0.9, 0.999, 1)
+    be.adamUpdate(w1, np.array([0.1], np.float32), m1, v1, 1e-3, 0.9, 0.999, 1e-8, bc1, bc2)
+    assert abs(w1[0] - 0.499) < 1e-6
+
+
+def test_clip_grad_norm(be):
+    rng = np.random.default_rng(10)
+    grads = [rng.standard_normal(s).astype(np.float32) for s in (20 * 4, 20, 200 * 100 + 3, 1)]
+    want = [g.copy() for g in grads]
+    wn, wf = zo.clip_grad_norm(want)
+    norm, fac = be.clipGradNorm(grads)
+    assert abs(norm - wn) <= 1e-5 * wn and abs(fac - wf) <= 1e-5 * wf
+    for a, b in zip(grads, want):
+        assert_close(a, b, 1e-5)
+    small = [np.full(4, 0.1, np.float32)]
+    norm, fac = be.clipGradNorm(small)
+    assert fac == 1.0 and np.array_equal(small[0], np.full(4, 0.1, np.float32))
+
+
+def test_device_resident_operands(be):
+    """Device handles in place of host slices: nothing is copied per op."""
+    be.set_precision(P.FP32_EXACT)
+    rng = np.random.default_rng(12)
+    m, n, k = 96, 48, 40
+    a, b = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    da, db, dbias, dc = be.tensor(a), be.tensor(b), be.tensor(bias), be.tensor(m * n)
+    be.beginCommandBatch()
+    be.matMul(da, db, dc, m, n, k)
+    be.addBias(dc, dbias)
+    be.activationForward(zn.Activation.relu, dc, dc)
+    be.endCommandBatch()
+    want = zo.activation_forward(zo.RELU, zo.add_bias(zo.matmul(a, b, m, n, k), bias))
+    assert np.array_equal(dc.numpy((m, n)), want)
+    for t in (da, db, dbias, dc):
+        t.free()
+
+
+def test_argument_errors(be):
+    a = np.zeros(4, np.float32)
+    with pytest.raises(zn.ZnError) as ei:
+        be.matMul(a, a, a, 0, 2, 2)
+    assert ei.value.status == 7          # ZN_ERR_SHAPE
+    with pytest.raises(zn.ZnError):
+        be.addBias(np.zeros(5, np.float32), np.zeros(2, np.float32))
+    with pytest.raises(zn.ZnError):
+        be.matMul(None, a, a, 2, 2, 1)

@@ -1,0 +1,116 @@
+// Data-parallel plumbing: one rank per GPU, gradients summed with NCCL.
+//
+// The reference's multi-GPU layer (src/cuda_multi_gpu.zig) plans a contiguous
+// batch split and nothing else; there is no collective anywhere in it.  Here the
+// split keeps its semantics (zn_distribute_workload) and the missing exchange is
+// one ncclAllReduce(sum, fp32) per layer on the context's communication stream.
+//
+// NCCL is bound at run time with dlopen, the way the reference binds libcuda
+// (src/cuda_driver.zig:786-816), so the library loads on machines without it and
+// shares the copy of NCCL a host process may already have loaded.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+#include "zn_internal.h"
+
+namespace {
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+
+NcclApi &api() {
+    static NcclApi a;
+    static bool tried = false;
+    if (tried) return a;
+    tried = true;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *nm : names) {
+        a.handle = dlopen(nm, RTLD_NOW | RTLD_GLOBAL);
+        if (a.handle) break;
+    }
+    if (!a.handle) return a;
+#define ZN_SYM(field, name) *(void **)(&a.field) = dlsym(a.handle, name)
+    ZN_SYM(GetUniqueId, "ncclGetUniqueId");
+    ZN_SYM(CommInitRank, "ncclCommInitRank");
+    ZN_SYM(CommDestroy, "ncclCommDestroy");
+    ZN_SYM(CommAbort, "ncclCommAbort");
+    ZN_SYM(AllReduce, "ncclAllReduce");
+    ZN_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+    ZN_SYM(GetErrorString, "ncclGetErrorString");
+#undef ZN_SYM
+    a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.GetErrorString;
+    return a;
+}
+
+}   // namespace
+
+struct zn_dp_state {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+bool zn_dp_active(const zn_ctx *ctx) { return ctx && ctx->dp && ctx->dp->world > 1; }
+
+zn_status zn_dp_allreduce(zn_ctx *ctx, float *buf, size_t count, cudaStream_t stream) {
+    if (!zn_dp_active(ctx)) return ZN_OK;
+    ncclResult_t r = api().AllReduce(buf, buf, count, ncclFloat32, ncclSum, ctx->dp->comm, stream);
+    if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllReduce: %s", api().GetErrorString(r));
+    return ZN_OK;
+}
+
+static_assert(sizeof(ncclUniqueId) == 128, "the C ABI carries the NCCL id as 128 bytes");
+
+extern "C" zn_status zn_dp_unique_id(uint8_t id_out[128]) {
+    if (!id_out) return ZN_ERR_INVALID_VALUE;
+    if (!api().ok) return ZN_ERR_NCCL;
+    ncclUniqueId id;
+    if (api().GetUniqueId(&id) != ncclSuccess) return ZN_ERR_NCCL;
+    memcpy(id_out, &id, 128);
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_dp_init(zn_ctx *ctx, int32_t rank, int32_t world, const uint8_t id_bytes[128]) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (world < 1 || rank < 0 || rank >= world) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "dp_init: rank %d of %d", rank, world);
+    if (ctx->dp) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "dp_init: already initialised");
+    zn_dp_state *st = new zn_dp_state();
+    st->rank = rank;
+    st->world = world;
+    if (world > 1) {
+        if (!id_bytes) { delete st; return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "dp_init: null id"); }
+        if (!api().ok) { delete st; return zn_fail(ctx, ZN_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
+        cudaSetDevice(ctx->device);
+        ncclUniqueId id;
+        memcpy(&id, id_bytes, 128);
+        ncclResult_t r = api().CommInitRank(&st->comm, world, id, rank);
+        if (r != ncclSuccess) {
+            delete st;
+            return zn_fail(ctx, ZN_ERR_NCCL, "ncclCommInitRank: %s", api().GetErrorString(r));
+        }
+    }
+    ctx->dp = st;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_dp_destroy(zn_ctx *ctx) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!ctx->dp) return ZN_OK;
+    if (ctx->dp->comm) {
+        cudaStreamSynchronize(ctx->comm_stream);
+        api().CommDestroy(ctx->dp->comm);
+    }
+    delete ctx->dp;
+    ctx->dp = nullptr;
+    return ZN_OK;
+}

@@ -1,0 +1,541 @@
+// tcgen05 / TMEM GEMM for the three Dense products on sm_100a.
+//
+// One persistent CTA per SM walks 128 x 256 output tiles.  Warp 0 feeds a
+// 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
+// no multicast); one thread of warp 1 issues tcgen05.mma (cta_group::1, M=128,
+// N=256) into one of two 256-column fp32 accumulators in tensor memory; warps
+// 2..5 drain the other accumulator with tcgen05.ld and apply the fused epilogue
+// (bias, activation, activation-derivative mask, accumulate, down-convert), so
+// the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// The three orientations of the reference (Backend.matMul, matMulTransposeB,
+// matMulTransposeA; src/backend.zig:169-195, :298-325) differ only in which
+// operand is K-major and which is MN-major; that is a bit in the instruction
+// descriptor plus a different shared-memory tile shape, never a transpose pass:
+//   NN  C = A[m][k] . B[k][n]      A K-major,  B N-major
+//   NT  C = A[m][k] . B[n][k]^T    A K-major,  B K-major
+//   TN  C = A[k][m]^T . B[k][n]    A M-major,  B N-major
+//
+// Every wait on an mbarrier is bounded: after about a second without progress
+// the waiting thread raises a CTA-wide abort flag, records a code in the
+// context's status word, and all roles fall through to the common exit, where
+// tensor memory is released.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "zn_internal.h"
+
+namespace {
+
+constexpr int BM = 128, BN = 256;
+constexpr int STAGES = 4;
+constexpr int ROW_BYTES = 128;                    // one swizzle row
+constexpr int A_STAGE = BM * ROW_BYTES;           // 16 KiB
+constexpr int B_STAGE = BN * ROW_BYTES;           // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+
+struct TcParams {
+    int M, N, K;
+    int num_m_tiles, num_n_tiles, num_k_blocks;
+    int a_mn, b_mn;           // operand majorness
+    uint32_t idesc;
+    uint32_t mn_lbo, mn_sbo;  // byte strides of an MN-major operand tile (see the MMA warp)
+    // epilogue
+    const float *bias;
+    int act;
+    const void *mask;
+    long long ld_mask;
+    float *out_f32;
+    long long ld_out_f32;
+    void *out_t;
+    long long ld_out_t;
+    int accumulate;
+    int *status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA has been aborted or the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                          int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                __threadfence_system();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <bool TF32>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    if (TF32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    }
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// lbo / sbo in bytes.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float act_apply(int act, float v) {
+    switch (act) {
+    case ZN_ACT_RELU: return v > 0.f ? v : 0.f;
+    case ZN_ACT_SIGMOID:
+        if (v >= 0.f) return 1.f / (1.f + __expf(-v));
+        else { const float e = __expf(v); return e / (1.f + e); }
+    case ZN_ACT_TANH: return tanhf(v);
+    default: return v;
+    }
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int &tm, int &tn) {
+    constexpr int G = 16;   // m-tiles per band: keeps a wave's A and B strips resident in L2
+    const int per_band = G * num_n;
+    const int band = t / per_band, first_m = band * G;
+    const int rows = min(num_m - first_m, G);
+    const int r = t - band * per_band;
+    tm = first_m + r % rows;
+    tn = r / rows;
+}
+
+// ET: operand element type (__nv_bfloat16 or float-as-tf32).
+template <typename ET>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+    constexpr bool TF32 = sizeof(ET) == 4;
+    constexpr int ES = sizeof(ET);
+    constexpr int BK = ROW_BYTES / ES;            // k elements per stage: 64 bf16 / 32 tf32
+    constexpr int CH = ROW_BYTES / ES;            // MN elements per 128-byte chunk of an MN-major tile
+    constexpr int UMMA_K_BYTES = 32;              // 16 bf16 / 8 tf32 per instruction
+    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;   // 4 instructions per stage
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - raw);
+    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2]; then tmem ptr, abort flag
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+    auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int nkb = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d(sa, &tmA, k0, m0, full_bar(s));                       // box {BK, 128}
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / CH; ++c)                                   // box {CH, BK} each
+                            tma_load_2d(sa + c * (BK * ROW_BYTES), &tmA, m0 + c * CH, k0, full_bar(s));
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(sb, &tmB, k0, n0, full_bar(s));                       // box {BK, 256}
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / CH; ++c)
+                            tma_load_2d(sb + c * (BK * ROW_BYTES), &tmB, n0 + c * CH, k0, full_bar(s));
+                    }
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            // Byte strides of the canonical 128B-swizzle layouts:
+            //   K-major : 8-row groups 1024 B apart (SBO); LBO unused.  k advances 32 B inside the row.
+            //   MN-major: 8-row (k) groups 1024 B apart (SBO); 128-byte MN chunks BK*128 B apart (LBO).
+            //             k advances by whole rows: UMMA_K rows * 128 B.
+            const uint32_t a_lbo = p.a_mn ? p.mn_lbo : 16, b_lbo = p.b_mn ? p.mn_lbo : 16;
+            const uint32_t a_sbo = p.a_mn ? p.mn_sbo : 1024, b_sbo = p.b_mn ? p.mn_sbo : 1024;
+            const uint32_t a_kstep = p.a_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
+            const uint32_t b_kstep = p.b_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
+            int it = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ++ks) {
+                        const uint64_t ad = make_desc(sa + ks * a_kstep, a_lbo, a_sbo);
+                        const uint64_t bd = make_desc(sb + ks * b_kstep, b_lbo, b_sbo);
+                        tc_mma<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));          // frees the stage when these MMAs have read it
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(tfull_bar(buf));    // accumulator complete
+            }
+        }
+    } else {
+        // ================= epilogue: warps 2..5, TMEM lanes 32*(warp%4).. =================
+        const int q = warp & 3;
+        const bool t_bf16 = !TF32;
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            int tm, tn;
+            tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+            const int buf = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            tc_fence_after();
+            const long long row = (long long)tm * BM + q * 32 + lane;
+            const int n0 = tn * BN;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
+            for (int c = 0; c < nchunks; ++c) {
+                uint32_t r[32];
+                tc_ld32(taddr + (uint32_t)(c * 32), r);
+                tc_wait_ld();
+                if (c == nchunks - 1) {
+                    // all reads of this accumulator are done: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+                if (row >= p.M) continue;
+                const int col0 = n0 + c * 32;
+                const int valid = min(32, p.N - col0);
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < valid) v[j] += __ldg(p.bias + col0 + j);
+                }
+                if (p.act != ZN_ACT_LINEAR) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = act_apply(p.act, v[j]);
+                }
+                if (p.mask) {
+                    if (t_bf16) {
+                        const __nv_bfloat16 *mrow = static_cast<const __nv_bfloat16 *>(p.mask) + row * p.ld_mask + col0;
+                        if (valid == 32 && ((reinterpret_cast<uintptr_t>(mrow) & 15) == 0)) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                const uint4 u = *reinterpret_cast<const uint4 *>(mrow + g * 8);
+                                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                                for (int h = 0; h < 4; ++h) {
+                                    // bf16 > 0  <=>  sign bit clear and magnitude bits non-zero
+                                    const uint32_t lo = w[h] & 0xFFFFu, hi = w[h] >> 16;
+                                    if (!(lo != 0u && lo < 0x8000u)) v[g * 8 + h * 2] = 0.f;
+                                    if (!(hi != 0u && hi < 0x8000u)) v[g * 8 + h * 2 + 1] = 0.f;
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < valid && !(__bfloat162float(mrow[j]) > 0.f)) v[j] = 0.f;
+                        }
+                    } else {
+                        const float *mrow = static_cast<const float *>(p.mask) + row * p.ld_mask + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid && !(mrow[j] > 0.f)) v[j] = 0.f;
+                    }
+                }
+                if (p.out_f32) {
+                    float *orow = p.out_f32 + row * p.ld_out_f32 + col0;
+                    const bool vec = valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) v[j] += orow[j];
+                    }
+                    if (vec) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            *reinterpret_cast<float4 *>(orow + g * 4) =
+                                make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) orow[j] = v[j];
+                    }
+                }
+                if (p.out_t) {
+                    if (t_bf16) {
+                        __nv_bfloat16 *orow = static_cast<__nv_bfloat16 *>(p.out_t) + row * p.ld_out_t + col0;
+                        if (valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0)) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int h = 0; h < 4; ++h) {
+                                    const __nv_bfloat162 b2 =
+                                        __floats2bfloat162_rn(v[g * 8 + h * 2], v[g * 8 + h * 2 + 1]);
+                                    w[h] = *reinterpret_cast<const uint32_t *>(&b2);
+                                }
+                                *reinterpret_cast<uint4 *>(orow + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < valid) orow[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    } else {
+                        float *orow = static_cast<float *>(p.out_t) + row * p.ld_out_t + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) orow[j] = v[j];
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- common exit
+    if (*abort_flag) {
+        // Something gave up: let copies and MMAs already in flight land before the CTA's memory goes away.
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// 2-D row-major tensor [outer][inner], row pitch ld elements; box {box_inner, box_outer}; 128B swizzle;
+// out-of-bounds elements read as zero.
+zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int64_t inner, int64_t outer, int64_t ld,
+                    int box_inner, int box_outer) {
+    char key[160];
+    snprintf(key, sizeof key, "%p|%d|%lld|%lld|%lld|%d|%d", ptr, es, (long long)inner, (long long)outer,
+             (long long)ld, box_inner, box_outer);
+    auto it = ctx->tmap_cache.find(key);
+    if (it != ctx->tmap_cache.end()) {
+        memcpy(out, it->second.data(), sizeof(CUtensorMap));
+        return ZN_OK;
+    }
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return zn_fail(ctx, ZN_ERR_NOT_INITIALIZED, "cuTensorMapEncodeTiled is not available from the driver");
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * es) % 16 != 0)
+        return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "tensor-core GEMM operand needs a 16-byte aligned base and row pitch");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)(ld * es)};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    CUresult r = enc(out, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return zn_fail(ctx, ZN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    if (ctx->tmap_cache.size() > 4096) ctx->tmap_cache.clear();
+    std::vector<uint8_t> bytes(sizeof(CUtensorMap));
+    memcpy(bytes.data(), out, sizeof(CUtensorMap));
+    ctx->tmap_cache.emplace(key, std::move(bytes));
+    return ZN_OK;
+}
+
+}   // namespace
+
+zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, bool a_mn, const void *b, int64_t ldb,
+                     bool b_mn, int64_t m, int64_t n, int64_t k, const zn_epilogue &e) {
+    if (!a || !b || (!e.out_f32 && !e.out_t)) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "gemm: null operand");
+    if (m <= 0 || n <= 0 || k <= 0) return zn_fail(ctx, ZN_ERR_SHAPE, "gemm: non-positive dimension");
+    if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return zn_fail(ctx, ZN_ERR_SHAPE, "gemm: dimension too large");
+    const int es = elem_type == 0 ? 2 : 4;
+    const int bk = ROW_BYTES / es, ch = ROW_BYTES / es;
+
+    static uint64_t attr_set_mask = 0;   // cudaFuncSetAttribute is per device
+    const uint64_t dev_bit = 1ull << (ctx->device & 63);
+    if (!(attr_set_mask & dev_bit)) {
+        ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          SMEM_BYTES));
+        ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set_mask |= dev_bit;
+    }
+
+    CUtensorMap tmA, tmB;
+    if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM));      // [m][k]: inner k
+    else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk));            // [k][m]: inner m
+    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, BN));      // [n][k]: inner k
+    else ZN_TRY(make_tmap(ctx, &tmB, es, b, n, k, ldb, ch, bk));            // [k][n]: inner n
+
+    TcParams p;
+    p.M = (int)m; p.N = (int)n; p.K = (int)k;
+    p.num_m_tiles = (int)((m + BM - 1) / BM);
+    p.num_n_tiles = (int)((n + BN - 1) / BN);
+    p.num_k_blocks = (int)((k + bk - 1) / bk);
+    p.a_mn = a_mn ? 1 : 0;
+    p.b_mn = b_mn ? 1 : 0;
+    const uint32_t fmt = elem_type == 0 ? 1u /* bf16 */ : 2u /* tf32 */;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    p.mn_lbo = (uint32_t)(bk * ROW_BYTES);
+    p.mn_sbo = 1024;
+    if (const char *dbg = getenv("ZN_TC_MN_STRIDES")) {   // diagnostic override "lbo,sbo" in bytes
+        unsigned l = 0, sb = 0;
+        if (sscanf(dbg, "%u,%u", &l, &sb) == 2) { p.mn_lbo = l; p.mn_sbo = sb; }
+    }
+    p.bias = e.bias; p.act = e.act; p.mask = e.mask; p.ld_mask = e.ld_mask;
+    p.out_f32 = e.out_f32; p.ld_out_f32 = e.ld_out_f32; p.out_t = e.out_t; p.ld_out_t = e.ld_out_t;
+    p.accumulate = e.accumulate;
+    p.status = ctx->status_dev;
+
+    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    zn_launch_scope scope(ctx, ZN_PROF_GEMM_TC, 2.0 * m * n * k,
+                          (double)es * (m * k + k * n) + (e.out_f32 ? 4.0 : (double)es) * m * n);
+    if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
+    else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}

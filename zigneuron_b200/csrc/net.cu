@@ -1,0 +1,654 @@
+// Device-resident Network of Dense layers: the reference's Network.forward /
+// computeGradients / trainStep / train (src/network.zig:309-616), Dense.forward /
+// backward (src/layer.zig:380-475) and Sgd.step / Adam.step (src/optimizer.zig:
+// 160-164, 209-233) restated as one stream of fused kernels.
+//
+// Per layer and step the stream holds: one GEMM for Y = act(X.W + b); one
+// column reduction for gb; one GEMM for gW = X^T.G; one GEMM for
+// dX = (G.W^T) (*) act'(Y_prev), whose epilogue produces the next layer's G
+// directly; then the global norm (two launches) and one update launch per
+// parameter tensor.  Only the inputs of each layer and the activated outputs are
+// kept, as in the reference's LayerCache (src/network.zig:33-36).
+//
+// HBM layout.  Per layer one parameter block [W (in*out) | pad to 4 | b (out)],
+// with gradient, Adam-m and Adam-v blocks of the same shape, all fp32.  In the
+// tensor-core modes W also has an operand copy (bf16, or fp32 with a pitch TMA
+// accepts) that the optimizer kernel refreshes.  Activations are [rows][ld] in
+// the operand type, ld = width rounded up to 8 elements in tensor-core modes.
+#include <cmath>
+#include <cstring>
+
+#include "zn_internal.h"
+
+zn_status zn_dp_allreduce(zn_ctx *ctx, float *buf, size_t count, cudaStream_t stream);   // dp.cu
+bool zn_dp_active(const zn_ctx *ctx);
+
+namespace {
+
+int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct Layer {
+    size_t in = 0, out = 0;
+    int act = ZN_ACT_LINEAR;
+    size_t b_off = 0, len = 0, blk = 0;   // bias offset, used length, allocated length (multiple of 4) before the tail
+    float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
+    void *w_op = nullptr;                 // operand copy of W (tensor-core modes), null when W itself is usable
+    int64_t ld_w = 0;
+    int opt = 0;                          // 0 sgd, 1 adam
+    float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, wd = 0.f;
+    size_t t = 0;
+    cudaEvent_t grads_ready = nullptr, reduced = nullptr;
+};
+
+struct Slot {                             // one in-flight pipelined step
+    float *x = nullptr, *t = nullptr;     // device staging of the host block
+    size_t x_cap = 0, t_cap = 0;
+    cudaEvent_t copied = nullptr, done = nullptr;
+    float *loss_host = nullptr;           // pinned: [loss_sum, norm, factor]
+    size_t rows = 0;
+    int loss = 0;
+    bool busy = false;
+};
+
+}   // namespace
+
+struct zn_net {
+    zn_ctx *ctx = nullptr;
+    zn_precision prec = ZN_FP32_SIMT;
+    bool tc = false, bf16 = false;
+    std::vector<Layer> layers;
+    size_t cap_rows = 0;
+    std::vector<void *> acts;             // acts[0] = operand copy of the input (or null when the input is used in place)
+    std::vector<int64_t> lds;             // lds[i] = pitch of acts[i]
+    float *out_f32 = nullptr;             // fp32 output of the last layer (tensor-core modes)
+    void *gwork[2] = {nullptr, nullptr};
+    int64_t g_ld_max = 0;
+    float *scalars = nullptr;             // device: [0] norm, [1] clip factor
+    Slot slots[2];
+    int head = 0, inflight = 0;
+    size_t global_rows = 0;               // > 0: data parallel
+    float last_norm = 0.f, last_factor = 1.f;
+    const void *last_input_grad = nullptr;
+    size_t last_rows = 0;
+    uint64_t seed_counter = 0;
+};
+
+namespace {
+
+size_t esize(const zn_net *n) { return n->bf16 ? 2 : 4; }
+
+void free_acts(zn_net *n) {
+    for (void *p : n->acts) cudaFree(p);
+    n->acts.clear();
+    n->lds.clear();
+    cudaFree(n->out_f32); n->out_f32 = nullptr;
+    cudaFree(n->gwork[0]); cudaFree(n->gwork[1]);
+    n->gwork[0] = n->gwork[1] = nullptr;
+    n->cap_rows = 0;
+}
+
+int64_t pitch_of(const zn_net *n, size_t width) { return n->tc ? round_up((int64_t)width, 8) : (int64_t)width; }
+
+// (Re)allocates activation and gradient work buffers for `rows` samples.
+zn_status ensure_rows(zn_net *n, size_t rows) {
+    zn_ctx *ctx = n->ctx;
+    if (rows <= n->cap_rows && n->acts.size() == n->layers.size() + 1) return ZN_OK;
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const size_t keep = rows > n->cap_rows ? rows : n->cap_rows;
+    free_acts(n);
+    const size_t L = n->layers.size();
+    n->acts.assign(L + 1, nullptr);
+    n->lds.assign(L + 1, 0);
+    n->g_ld_max = 0;
+    for (size_t i = 0; i <= L; ++i) {
+        const size_t width = i == 0 ? n->layers[0].in : n->layers[i - 1].out;
+        n->lds[i] = pitch_of(n, width);
+        if (n->lds[i] > n->g_ld_max) n->g_ld_max = n->lds[i];
+        // acts[0] is only materialised when the input must be converted or re-pitched
+        if (i == 0 && !n->tc) continue;
+        ZN_CUDA(ctx, cudaMalloc(&n->acts[i], keep * (size_t)n->lds[i] * esize(n)));
+        ZN_CUDA(ctx, cudaMemsetAsync(n->acts[i], 0, keep * (size_t)n->lds[i] * esize(n), ctx->stream));
+    }
+    if (n->tc) ZN_CUDA(ctx, cudaMalloc((void **)&n->out_f32, keep * n->layers[L - 1].out * sizeof(float)));
+    for (int i = 0; i < 2; ++i) {
+        ZN_CUDA(ctx, cudaMalloc(&n->gwork[i], keep * (size_t)n->g_ld_max * esize(n)));
+        ZN_CUDA(ctx, cudaMemsetAsync(n->gwork[i], 0, keep * (size_t)n->g_ld_max * esize(n), ctx->stream));
+    }
+    n->cap_rows = keep;
+    return ZN_OK;
+}
+
+zn_status refresh_operand_copy(zn_net *n, Layer &l) {
+    if (!l.w_op) return ZN_OK;
+    return zn_k_convert(n->ctx, l.params, (int64_t)l.out, l.w_op, l.ld_w, n->bf16, (int64_t)l.in, (int64_t)l.out);
+}
+
+// One of the three products in the network's precision.  a/b are operand-typed.
+zn_status net_gemm(zn_net *n, int orient /*0 NN,1 TN,2 NT*/, const void *a, int64_t lda, const void *b, int64_t ldb,
+                   int64_t m, int64_t nn, int64_t k, const zn_epilogue &ep) {
+    zn_ctx *ctx = n->ctx;
+    if (!n->tc) {
+        const float *fa = (const float *)a, *fb = (const float *)b;
+        const bool exact = n->prec == ZN_FP32_EXACT;
+        if (orient == 0) return zn_gemm_simt(ctx, fa, lda, 1, fb, ldb, 1, m, nn, k, ep, exact);
+        if (orient == 1) return zn_gemm_simt(ctx, fa, 1, lda, fb, ldb, 1, m, nn, k, ep, exact);
+        return zn_gemm_simt(ctx, fa, lda, 1, fb, 1, ldb, m, nn, k, ep, exact);
+    }
+    const int et = n->bf16 ? 0 : 1;
+    return zn_gemm_tc(ctx, et, a, lda, orient == 1, b, ldb, orient != 2, m, nn, k, ep);
+}
+
+// Forward over `rows` samples whose fp32 input block x_dev is on the device.
+zn_status forward_dev(zn_net *n, const float *x_dev, size_t rows) {
+    zn_ctx *ctx = n->ctx;
+    const size_t L = n->layers.size();
+    ZN_TRY(ensure_rows(n, rows));
+    const void *cur = x_dev;
+    if (n->tc) {
+        ZN_TRY(zn_k_convert(ctx, x_dev, (int64_t)n->layers[0].in, n->acts[0], n->lds[0], n->bf16, (int64_t)rows,
+                            (int64_t)n->layers[0].in));
+        cur = n->acts[0];
+    }
+    for (size_t i = 0; i < L; ++i) {
+        Layer &l = n->layers[i];
+        zn_epilogue ep;
+        ep.bias = l.params + l.b_off;
+        ep.act = l.act;
+        const bool last = i + 1 == L;
+        if (!n->tc) {
+            ep.out_f32 = (float *)n->acts[i + 1];
+            ep.ld_out_f32 = n->lds[i + 1];
+        } else {
+            if (last) { ep.out_f32 = n->out_f32; ep.ld_out_f32 = (int64_t)l.out; }
+            if (!last || l.act != ZN_ACT_LINEAR) { ep.out_t = n->acts[i + 1]; ep.ld_out_t = n->lds[i + 1]; }
+        }
+        const void *w = l.w_op ? l.w_op : (const void *)l.params;
+        const int64_t ldw = l.w_op ? l.ld_w : (int64_t)l.out;
+        ZN_TRY(net_gemm(n, 0, cur, n->lds[i], w, ldw, (int64_t)rows, (int64_t)l.out, (int64_t)l.in, ep));
+        cur = n->acts[i + 1];
+    }
+    return ZN_OK;
+}
+
+float *final_output(zn_net *n) { return n->tc ? n->out_f32 : (float *)n->acts[n->layers.size()]; }
+
+// Everything of one training step after the inputs are on the device.  x_dev / t_dev fp32.
+// The loss SUM lands in the tail slot of the last layer's gradient block.
+zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t rows, float lr, int loss) {
+    zn_ctx *ctx = n->ctx;
+    const size_t L = n->layers.size();
+    const bool exact = n->prec == ZN_FP32_EXACT;
+    const bool dp = n->global_rows > 0 && zn_dp_active(ctx);
+    ZN_TRY(forward_dev(n, x_dev, rows));
+
+    Layer &last = n->layers[L - 1];
+    const size_t out_cols = last.out;
+    const size_t total_rows = dp ? n->global_rows : rows;
+    float *loss_slot = last.grads + last.blk;
+    int cur = 0;
+    ZN_TRY(zn_k_loss(ctx, loss, final_output(n), (int64_t)out_cols, t_dev, n->gwork[cur], n->bf16, n->lds[L],
+                     (int64_t)rows, (int64_t)out_cols, (float)(total_rows * out_cols), loss_slot));
+    if (last.act != ZN_ACT_LINEAR)   // Dense.backward applies the derivative of every layer, the last included
+        ZN_TRY(zn_k_act_backward_t(ctx, last.act, n->acts[L], n->lds[L], n->gwork[cur], n->lds[L], n->bf16,
+                                   (int64_t)rows, (int64_t)out_cols));
+
+    for (size_t idx = L; idx-- > 0;) {
+        Layer &l = n->layers[idx];
+        const void *g = n->gwork[cur];
+        const int64_t ld_g = n->lds[idx + 1];
+        const void *x_in = (idx == 0 && !n->tc) ? (const void *)x_dev : (const void *)n->acts[idx];
+        // gb = column sums of G   (accumulateBias into a cleared gb, src/layer.zig:459)
+        ZN_TRY(zn_k_bias_reduce(ctx, g, n->bf16, ld_g, (int64_t)rows, (int64_t)l.out, l.grads + l.b_off, false, exact));
+        // gW = X^T . G           (matMulTransposeA, src/layer.zig:466)
+        {
+            zn_epilogue ep;
+            ep.out_f32 = l.grads;
+            ep.ld_out_f32 = (int64_t)l.out;
+            ZN_TRY(net_gemm(n, 1, x_in, n->lds[idx], g, ld_g, (int64_t)l.in, (int64_t)l.out, (int64_t)rows, ep));
+        }
+        if (dp) {
+            // this layer's gradients are final: start summing them over ranks while earlier layers run
+            ZN_CUDA(ctx, cudaEventRecord(l.grads_ready, ctx->stream));
+            ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, l.grads_ready, 0));
+            ZN_TRY(zn_dp_allreduce(ctx, l.grads, l.blk + (idx + 1 == L ? 1 : 0), ctx->comm_stream));
+            ZN_CUDA(ctx, cudaEventRecord(l.reduced, ctx->comm_stream));
+        }
+        // dX = G . W^T, masked by the previous layer's activation derivative (src/layer.zig:440-448)
+        {
+            zn_epilogue ep;
+            const int prev_act = idx > 0 ? n->layers[idx - 1].act : ZN_ACT_LINEAR;
+            if (prev_act == ZN_ACT_RELU) { ep.mask = n->acts[idx]; ep.ld_mask = n->lds[idx]; }
+            if (n->tc) { ep.out_t = n->gwork[cur ^ 1]; ep.ld_out_t = n->lds[idx]; }
+            else { ep.out_f32 = (float *)n->gwork[cur ^ 1]; ep.ld_out_f32 = n->lds[idx]; }
+            const void *w = l.w_op ? l.w_op : (const void *)l.params;
+            const int64_t ldw = l.w_op ? l.ld_w : (int64_t)l.out;
+            ZN_TRY(net_gemm(n, 2, g, ld_g, w, ldw, (int64_t)rows, (int64_t)l.in, (int64_t)l.out, ep));
+            if (idx > 0 && prev_act != ZN_ACT_RELU && prev_act != ZN_ACT_LINEAR)
+                ZN_TRY(zn_k_act_backward_t(ctx, prev_act, n->acts[idx], n->lds[idx], n->gwork[cur ^ 1], n->lds[idx],
+                                           n->bf16, (int64_t)rows, (int64_t)l.in));
+        }
+        cur ^= 1;
+    }
+    n->last_input_grad = n->gwork[cur];
+    n->last_rows = rows;
+
+    if (dp)
+        for (size_t i = 0; i < L; ++i) ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, n->layers[i].reduced, 0));
+
+    // global norm over every gradient tensor, weights then bias, layer by layer (src/network.zig:513-521)
+    std::vector<zn_seg> segs;
+    for (size_t i = 0; i < L; ++i) {
+        segs.push_back({n->layers[i].grads, n->layers[i].in * n->layers[i].out});
+        segs.push_back({n->layers[i].grads + n->layers[i].b_off, n->layers[i].out});
+    }
+    ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars));
+
+    // optimizer per layer (src/network.zig:541-549)
+    for (size_t i = 0; i < L; ++i) {
+        Layer &l = n->layers[i];
+        zn_opt_args a{};
+        a.lr = lr; a.wd = l.wd; a.factor_dev = n->scalars + 1;
+        a.beta1 = l.beta1; a.beta2 = l.beta2; a.eps = l.eps;
+        if (l.opt == 1) {
+            l.t += 1;
+            const float tf = (float)l.t;
+            a.bc1 = 1.0f - powf(l.beta1, tf);
+            a.bc2 = 1.0f - powf(l.beta2, tf);
+        }
+        // weights
+        a.w = l.params; a.g = l.grads; a.m = l.m; a.v = l.v; a.count = l.in * l.out; a.w_clamp = 100.0f;
+        a.shadow = l.w_op; a.shadow_bf16 = n->bf16; a.cols = (int64_t)l.out; a.ld_shadow = l.ld_w;
+        if (l.opt == 1) ZN_TRY(zn_k_adam(ctx, a)); else ZN_TRY(zn_k_sgd(ctx, a, false));
+        // bias
+        a.w = l.params + l.b_off; a.g = l.grads + l.b_off; a.count = l.out; a.shadow = nullptr;
+        if (l.opt == 1) { a.m = l.m + l.b_off; a.v = l.v + l.b_off; a.w_clamp = 100.0f; ZN_TRY(zn_k_adam(ctx, a)); }
+        else { a.w_clamp = 50.0f; ZN_TRY(zn_k_sgd(ctx, a, true)); }
+    }
+    return ZN_OK;
+}
+
+float loss_from_sum(const zn_net *n, float sum, size_t rows, int loss) {
+    const size_t total_rows = (n->global_rows > 0 && zn_dp_active(n->ctx)) ? n->global_rows : rows;
+    const size_t cols = n->layers.back().out;
+    if (loss == ZN_LOSS_MSE) return sum / (float)(total_rows * cols);
+    return total_rows > 1 ? sum / (float)total_rows : sum;
+}
+
+zn_status check_net(zn_net *n, bool need_layers) {
+    if (!n || !n->ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (need_layers && n->layers.empty()) return zn_fail(n->ctx, ZN_ERR_NOT_AVAILABLE, "network has no layers");
+    cudaSetDevice(n->ctx->device);
+    return ZN_OK;
+}
+
+zn_status ensure_slot(zn_net *n, Slot &s, size_t x_floats, size_t t_floats) {
+    zn_ctx *ctx = n->ctx;
+    if (!s.copied) {
+        ZN_CUDA(ctx, cudaEventCreateWithFlags(&s.copied, cudaEventDisableTiming));
+        ZN_CUDA(ctx, cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+        ZN_CUDA(ctx, cudaHostAlloc((void **)&s.loss_host, 4 * sizeof(float), cudaHostAllocDefault));
+    }
+    if (s.x_cap < x_floats) {
+        ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(s.x); s.x = nullptr; s.x_cap = 0;
+        ZN_CUDA(ctx, cudaMalloc((void **)&s.x, x_floats * sizeof(float)));
+        s.x_cap = x_floats;
+    }
+    if (s.t_cap < t_floats) {
+        ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(s.t); s.t = nullptr; s.t_cap = 0;
+        ZN_CUDA(ctx, cudaMalloc((void **)&s.t, t_floats * sizeof(float)));
+        s.t_cap = t_floats;
+    }
+    return ZN_OK;
+}
+
+uint64_t splitmix(uint64_t &s) {
+    uint64_t z = (s += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+}   // namespace
+
+extern "C" zn_status zn_net_create(zn_ctx *ctx, zn_precision precision, zn_net **out) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!out) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "net_create: null output");
+    if (precision < ZN_FP32_SIMT || precision > ZN_BF16_TC) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "unknown precision");
+    cudaSetDevice(ctx->device);
+    zn_net *n = new zn_net();
+    n->ctx = ctx;
+    n->prec = precision;
+    n->tc = precision == ZN_TF32_TC || precision == ZN_BF16_TC;
+    n->bf16 = precision == ZN_BF16_TC;
+    cudaError_t e = cudaMalloc((void **)&n->scalars, 16 * sizeof(float));
+    if (e != cudaSuccess) { delete n; return zn_cuda_status(ctx, e, "cudaMalloc"); }
+    cudaMemsetAsync(n->scalars, 0, 16 * sizeof(float), ctx->stream);
+    *out = n;
+    return ZN_OK;
+}
+
+extern "C" void zn_net_destroy(zn_net *n) {
+    if (!n) return;
+    if (n->ctx) {
+        cudaSetDevice(n->ctx->device);
+        cudaStreamSynchronize(n->ctx->stream);
+        cudaStreamSynchronize(n->ctx->copy_stream);
+        cudaStreamSynchronize(n->ctx->comm_stream);
+    }
+    free_acts(n);
+    for (Layer &l : n->layers) {
+        cudaFree(l.params); cudaFree(l.grads); cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
+        if (l.grads_ready) cudaEventDestroy(l.grads_ready);
+        if (l.reduced) cudaEventDestroy(l.reduced);
+    }
+    for (Slot &s : n->slots) {
+        cudaFree(s.x); cudaFree(s.t);
+        if (s.copied) cudaEventDestroy(s.copied);
+        if (s.done) cudaEventDestroy(s.done);
+        if (s.loss_host) cudaFreeHost(s.loss_host);
+    }
+    cudaFree(n->scalars);
+    delete n;
+}
+
+extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t output_size, zn_activation act,
+                                      int32_t *layer_index_out) {
+    ZN_TRY(check_net(n, false));
+    zn_ctx *ctx = n->ctx;
+    if (input_size == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "InvalidInputSize: input_size is 0");     // src/layer.zig:307
+    if (output_size == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "InvalidOutputSize: output_size is 0");  // src/layer.zig:308
+    if (act != ZN_ACT_RELU && act != ZN_ACT_LINEAR && act != ZN_ACT_SIGMOID && act != ZN_ACT_TANH)
+        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "activation %d is not on the Dense path", (int)act);
+    if (!n->layers.empty() && n->layers.back().out != input_size)
+        return zn_fail(ctx, ZN_ERR_SHAPE, "layer input %zu does not match previous output %zu", input_size, n->layers.back().out);
+    if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "steps in flight");
+    Layer l;
+    l.in = input_size; l.out = output_size; l.act = act;
+    l.b_off = (size_t)round_up((int64_t)(input_size * output_size), 4);
+    l.len = l.b_off + output_size;
+    l.blk = (size_t)round_up((int64_t)l.len, 4);
+    const size_t alloc = (l.blk + 4) * sizeof(float);
+    ZN_CUDA(ctx, cudaMalloc((void **)&l.params, alloc));
+    ZN_CUDA(ctx, cudaMalloc((void **)&l.grads, alloc));
+    ZN_CUDA(ctx, cudaMemsetAsync(l.params, 0, alloc, ctx->stream));
+    ZN_CUDA(ctx, cudaMemsetAsync(l.grads, 0, alloc, ctx->stream));
+    ZN_CUDA(ctx, cudaEventCreateWithFlags(&l.grads_ready, cudaEventDisableTiming));
+    ZN_CUDA(ctx, cudaEventCreateWithFlags(&l.reduced, cudaEventDisableTiming));
+    if (n->tc) {
+        const bool direct = !n->bf16 && output_size % 4 == 0;   // tf32 can read W itself when its pitch is TMA-legal
+        if (!direct) {
+            l.ld_w = round_up((int64_t)output_size, 8);
+            const size_t bytes = input_size * (size_t)l.ld_w * esize(n);
+            ZN_CUDA(ctx, cudaMalloc(&l.w_op, bytes));
+            ZN_CUDA(ctx, cudaMemsetAsync(l.w_op, 0, bytes, ctx->stream));
+        }
+    }
+    // Dense.init, src/layer.zig:326-339: U(-1,1) * scale(act), bias 0.  The generator is seeded by a
+    // counter 1,2,3,... like the reference's, but is splitmix64, not Zig's PRNG.
+    {
+        const float scale = (act == ZN_ACT_RELU) ? sqrtf(2.0f / (float)input_size)
+                            : (act == ZN_ACT_LINEAR) ? sqrtf(1.0f / (float)input_size)
+                                                     : sqrtf(2.0f / (float)(input_size + output_size));
+        uint64_t s = ++n->seed_counter;
+        std::vector<float> w(input_size * output_size);
+        for (float &x : w) {
+            const float u = (float)(splitmix(s) >> 40) * (1.0f / 16777216.0f);   // [0,1)
+            x = (u * 2.0f - 1.0f) * scale;
+        }
+        ZN_CUDA(ctx, cudaMemcpyAsync(l.params, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    n->layers.push_back(l);
+    ZN_TRY(refresh_operand_copy(n, n->layers.back()));
+    if (n->cap_rows) { ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); free_acts(n); }
+    if (layer_index_out) *layer_index_out = (int32_t)n->layers.size() - 1;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_layer_count(const zn_net *n, size_t *out) {
+    if (!n || !out) return ZN_ERR_INVALID_VALUE;
+    *out = n->layers.size();
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_set_weights(zn_net *n, size_t layer, const float *weights, const float *bias) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (layer >= n->layers.size()) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "layer %zu out of range", layer);
+    Layer &l = n->layers[layer];
+    if (weights) ZN_CUDA(ctx, cudaMemcpyAsync(l.params, weights, l.in * l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    if (bias) ZN_CUDA(ctx, cudaMemcpyAsync(l.params + l.b_off, bias, l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    if (weights) ZN_TRY(refresh_operand_copy(n, l));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_get_weights(zn_net *n, size_t layer, float *weights, float *bias) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (layer >= n->layers.size()) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "layer %zu out of range", layer);
+    Layer &l = n->layers[layer];
+    if (weights) ZN_CUDA(ctx, cudaMemcpyAsync(weights, l.params, l.in * l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    if (bias) ZN_CUDA(ctx, cudaMemcpyAsync(bias, l.params + l.b_off, l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_net_get_grads(zn_net *n, size_t layer, float *gw, float *gb) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (layer >= n->layers.size()) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "layer %zu out of range", layer);
+    Layer &l = n->layers[layer];
+    if (gw) ZN_CUDA(ctx, cudaMemcpyAsync(gw, l.grads, l.in * l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    if (gb) ZN_CUDA(ctx, cudaMemcpyAsync(gb, l.grads + l.b_off, l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_net_get_input_grad(zn_net *n, float *grad_input, size_t count) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!grad_input) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "null output");
+    if (!n->last_input_grad) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "no training step has run");
+    const size_t in = n->layers[0].in, rows = n->last_rows;
+    if (count != rows * in) return zn_fail(ctx, ZN_ERR_SHAPE, "input gradient has %zu elements", rows * in);
+    const int64_t ld = n->lds[0];
+    std::vector<uint8_t> raw(rows * (size_t)ld * esize(n));
+    ZN_CUDA(ctx, cudaMemcpyAsync(raw.data(), n->last_input_grad, raw.size(), cudaMemcpyDeviceToHost, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t c = 0; c < in; ++c) {
+            if (n->bf16) {
+                const uint16_t h = reinterpret_cast<const uint16_t *>(raw.data())[r * ld + c];
+                const uint32_t u = (uint32_t)h << 16;
+                memcpy(&grad_input[r * in + c], &u, 4);
+            } else {
+                grad_input[r * in + c] = reinterpret_cast<const float *>(raw.data())[r * ld + c];
+            }
+        }
+    return ZN_OK;
+}
+
+static zn_status for_layers(zn_net *n, int32_t layer, size_t *lo, size_t *hi) {
+    if (layer < 0) { *lo = 0; *hi = n->layers.size(); return ZN_OK; }
+    if ((size_t)layer >= n->layers.size()) return zn_fail(n->ctx, ZN_ERR_INVALID_VALUE, "layer %d out of range", layer);
+    *lo = (size_t)layer; *hi = (size_t)layer + 1;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_set_sgd(zn_net *n, int32_t layer, float weight_decay) {
+    ZN_TRY(check_net(n, true));
+    size_t lo, hi;
+    ZN_TRY(for_layers(n, layer, &lo, &hi));
+    for (size_t i = lo; i < hi; ++i) { n->layers[i].opt = 0; n->layers[i].wd = weight_decay; }
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_set_adam(zn_net *n, int32_t layer, float beta1, float beta2, float eps, float weight_decay) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    size_t lo, hi;
+    ZN_TRY(for_layers(n, layer, &lo, &hi));
+    for (size_t i = lo; i < hi; ++i) {
+        Layer &l = n->layers[i];
+        l.opt = 1; l.beta1 = beta1; l.beta2 = beta2; l.eps = eps; l.wd = weight_decay; l.t = 0;
+        const size_t bytes = (l.blk + 4) * sizeof(float);
+        if (!l.m) ZN_CUDA(ctx, cudaMalloc((void **)&l.m, bytes));
+        if (!l.v) ZN_CUDA(ctx, cudaMalloc((void **)&l.v, bytes));
+        ZN_CUDA(ctx, cudaMemsetAsync(l.m, 0, bytes, ctx->stream));
+        ZN_CUDA(ctx, cudaMemsetAsync(l.v, 0, bytes, ctx->stream));
+    }
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_forward(zn_net *n, const float *input, size_t rows, float *output) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!input || !output) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "forward: null operand");
+    if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "forward: zero rows");
+    const size_t in = n->layers[0].in, out = n->layers.back().out;
+    const float *x_dev = input;
+    if (!zn_is_device_ptr(input)) {
+        ZN_TRY(ensure_slot(n, n->slots[0], rows * in, 1));
+        ZN_CUDA(ctx, cudaMemcpyAsync(n->slots[0].x, input, rows * in * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        x_dev = n->slots[0].x;
+    }
+    ZN_TRY(forward_dev(n, x_dev, rows));
+    ZN_CUDA(ctx, cudaMemcpyAsync(output, final_output(n), rows * out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const float *target, size_t rows, float lr,
+                                       zn_loss loss, float *loss_out) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!input || !target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "train_step: null operand");
+    if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "train_step: zero rows");
+    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
+        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
+    if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "pipelined steps in flight; wait for them first");
+    const size_t in = n->layers[0].in, out = n->layers.back().out;
+    Slot &s = n->slots[0];
+    ZN_TRY(ensure_slot(n, s, rows * in, rows * out));
+    const float *x_dev = input, *t_dev = target;
+    if (!zn_is_device_ptr(input)) {
+        ZN_CUDA(ctx, cudaMemcpyAsync(s.x, input, rows * in * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        x_dev = s.x;
+    }
+    if (!zn_is_device_ptr(target)) {
+        ZN_CUDA(ctx, cudaMemcpyAsync(s.t, target, rows * out * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        t_dev = s.t;
+    }
+    ZN_TRY(step_dev(n, x_dev, t_dev, rows, lr, (int)loss));
+    Layer &last = n->layers.back();
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host, last.grads + last.blk, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host + 1, n->scalars, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    n->last_norm = s.loss_host[1];
+    n->last_factor = s.loss_host[2];
+    if (loss_out) *loss_out = loss_from_sum(n, s.loss_host[0], rows, (int)loss);
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_net_submit_step(zn_net *n, const float *host_input, const float *host_target, size_t rows,
+                                        float lr, zn_loss loss) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!host_input || !host_target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "submit_step: null operand");
+    if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "submit_step: zero rows");
+    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
+        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
+    if (n->inflight >= 2) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "two steps already in flight");
+    const size_t in = n->layers[0].in, out = n->layers.back().out;
+    const int idx = (n->head + n->inflight) & 1;
+    Slot &s = n->slots[idx];
+    ZN_TRY(ensure_slot(n, s, rows * in, rows * out));
+    ZN_TRY(ensure_rows(n, rows));
+    // The slot's previous step (two submits ago) has been waited for, so its buffers are free:
+    // copy on the copy stream while the other slot's step computes.
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.x, host_input, rows * in * sizeof(float), cudaMemcpyHostToDevice, ctx->copy_stream));
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.t, host_target, rows * out * sizeof(float), cudaMemcpyHostToDevice, ctx->copy_stream));
+    ZN_CUDA(ctx, cudaEventRecord(s.copied, ctx->copy_stream));
+    ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, s.copied, 0));
+    ZN_TRY(step_dev(n, s.x, s.t, rows, lr, (int)loss));
+    Layer &last = n->layers.back();
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host, last.grads + last.blk, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host + 1, n->scalars, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    ZN_CUDA(ctx, cudaEventRecord(s.done, ctx->stream));
+    s.rows = rows; s.loss = (int)loss; s.busy = true;
+    n->inflight += 1;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_wait_step(zn_net *n, float *loss_out) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (n->inflight == 0) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "no step in flight");
+    Slot &s = n->slots[n->head];
+    ZN_CUDA(ctx, cudaEventSynchronize(s.done));
+    s.busy = false;
+    n->head ^= 1;
+    n->inflight -= 1;
+    n->last_norm = s.loss_host[1];
+    n->last_factor = s.loss_host[2];
+    if (loss_out) *loss_out = loss_from_sum(n, s.loss_host[0], s.rows, s.loss);
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_net_train(zn_net *n, const float *inputs, const float *targets, size_t samples, size_t epochs,
+                                  float lr, zn_loss loss, float *epoch_loss) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!inputs || !targets) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "train: null operand");
+    if (samples == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "train: no samples");
+    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
+        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
+    if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "pipelined steps in flight");
+    const size_t in = n->layers[0].in, out = n->layers.back().out;
+    Slot &s = n->slots[0];
+    ZN_TRY(ensure_slot(n, s, samples * in, samples * out));
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.x, inputs, samples * in * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    ZN_CUDA(ctx, cudaMemcpyAsync(s.t, targets, samples * out * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    float *losses_dev = nullptr;
+    ZN_CUDA(ctx, cudaMalloc((void **)&losses_dev, samples * sizeof(float)));
+    std::vector<float> losses(samples);
+    Layer &last = n->layers.back();
+    zn_status st = ZN_OK;
+    for (size_t e = 0; e < epochs && st == ZN_OK; ++e) {
+        // one trainStep per sample, in order (src/network.zig:613-614)
+        for (size_t i = 0; i < samples && st == ZN_OK; ++i) {
+            st = step_dev(n, s.x + i * in, s.t + i * out, 1, lr, (int)loss);
+            if (st == ZN_OK &&
+                cudaMemcpyAsync(losses_dev + i, last.grads + last.blk, sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
+                st = zn_fail(ctx, ZN_ERR_CUDA, "loss copy failed");
+        }
+        if (st != ZN_OK) break;
+        if (cudaMemcpyAsync(losses.data(), losses_dev, samples * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+            cudaStreamSynchronize(ctx->stream) != cudaSuccess) { st = zn_fail(ctx, ZN_ERR_CUDA, "loss read-back failed"); break; }
+        float total = 0.f;
+        for (size_t i = 0; i < samples; ++i) total += loss_from_sum(n, losses[i], 1, (int)loss);
+        if (epoch_loss) epoch_loss[e] = total / (float)samples;   // src/network.zig:615
+    }
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(losses_dev);
+    if (st != ZN_OK) return st;
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_net_last_clip(zn_net *n, float *norm_out, float *factor_out) {
+    if (!n) return ZN_ERR_NOT_INITIALIZED;
+    if (norm_out) *norm_out = n->last_norm;
+    if (factor_out) *factor_out = n->last_factor;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_set_data_parallel(zn_net *n, size_t global_rows) {
+    ZN_TRY(check_net(n, true));
+    if (global_rows > 0 && !zn_dp_active(n->ctx))
+        return zn_fail(n->ctx, ZN_ERR_NOT_AVAILABLE, "call zn_dp_init on the context first");
+    n->global_rows = global_rows;
+    return ZN_OK;
+}

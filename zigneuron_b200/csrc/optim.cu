@@ -1,0 +1,200 @@
+// Gradient-norm clip and the SGD / Adam parameter updates.
+//
+// Network.trainStep's clip (src/network.zig:513-535) needs the norm of every
+// gradient before any parameter moves, so the step is two passes: (1) sum of
+// squares over all gradient tensors -> norm and clip factor, kept on the device;
+// (2) one pass per parameter tensor that applies the factor, the reference's
+// clamps and the update (cpuSgdUpdate / cpuSgdUpdateBias / cpuAdamUpdate,
+// src/backend.zig:2722-2772) and refreshes the tensor-core operand copy of the
+// weights.  12 bytes per parameter for SGD, 28 for Adam, plus the operand copy.
+#include "zn_internal.h"
+
+namespace {
+
+constexpr int TPB = 256;
+constexpr int MAX_SEGS = 32;
+
+struct SegTable {
+    const float *ptr[MAX_SEGS];
+    unsigned long long count[MAX_SEGS];
+    int first_block[MAX_SEGS + 1];   // blocks [first_block[i], first_block[i+1]) belong to segment i
+    int nseg;
+};
+
+constexpr int ELEMS_PER_BLOCK = TPB * 4 * 8;   // 8 float4 per thread
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void sq_partial_kernel(const __grid_constant__ SegTable tab, float *__restrict__ partial) {
+    __shared__ float part[TPB / 32];
+    int seg = 0;
+    while (seg + 1 < tab.nseg && (int)blockIdx.x >= tab.first_block[seg + 1]) ++seg;
+    const float *p = tab.ptr[seg];
+    const unsigned long long n = tab.count[seg];
+    const unsigned long long base = (unsigned long long)((int)blockIdx.x - tab.first_block[seg]) * ELEMS_PER_BLOCK;
+    const unsigned long long end = min(n, base + ELEMS_PER_BLOCK);
+    float s = 0.f;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+        for (unsigned long long i = base + threadIdx.x * 4ull; i < end; i += TPB * 4ull) {
+            if (i + 4 <= end) {
+                const float4 v = *reinterpret_cast<const float4 *>(p + i);
+                s += v.x * v.x; s += v.y * v.y; s += v.z * v.z; s += v.w * v.w;
+            } else {
+                for (unsigned long long j = i; j < end; ++j) s += p[j] * p[j];
+            }
+        }
+    } else {
+        for (unsigned long long i = base + threadIdx.x; i < end; i += TPB) s += p[i] * p[i];
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < TPB / 32; ++i) t += part[i];
+        partial[blockIdx.x] = t;
+    }
+}
+
+// norm = sqrt(sum); factor = norm > 1 ? 1 / (norm + 1e-6) : 1   (src/network.zig:513-524)
+__global__ void norm_final_kernel(const float *__restrict__ partial, int n, float *__restrict__ out) {
+    __shared__ double sm[TPB];
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partial[i];
+    sm[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = TPB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const float total = sqrtf((float)sm[0]);
+        const float max_norm = 1.0f;
+        out[0] = total;
+        out[1] = total > max_norm ? __fdiv_rn(max_norm, __fadd_rn(total, 1e-6f)) : 1.0f;
+    }
+}
+
+__global__ void scale_kernel(float *p, size_t n, const float *factor) {
+    const float f = *factor;
+    if (f == 1.0f) return;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        p[i] = __fmul_rn(p[i], f);
+}
+
+__device__ __forceinline__ float clamp_grad(float g) {
+    if (isnan(g)) return 0.0f;
+    return fminf(5.0f, fmaxf(-5.0f, g));
+}
+
+template <typename ST>
+__device__ __forceinline__ void store_shadow(ST *shadow, size_t i, long long cols, long long ld, float w) {
+    const size_t idx = (ld == cols) ? i : (i / (size_t)cols) * (size_t)ld + (i % (size_t)cols);
+    if (sizeof(ST) == 2) reinterpret_cast<__nv_bfloat16 *>(shadow)[idx] = __float2bfloat16_rn(w);
+    else reinterpret_cast<float *>(shadow)[idx] = w;
+}
+
+// w -= lr * (g + wd * w), clamps as the reference; bias: no decay, clamp +-50.
+template <typename ST>
+__global__ void sgd_kernel(zn_opt_args a, int is_bias) {
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const bool write_g = f != 1.0f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.count; i += (size_t)gridDim.x * blockDim.x) {
+        float g = a.g[i];
+        if (write_g) { g = __fmul_rn(g, f); a.g[i] = g; }
+        g = clamp_grad(g);
+        float w = a.w[i];
+        if (is_bias) w = __fsub_rn(w, __fmul_rn(a.lr, g));
+        else w = __fsub_rn(w, __fmul_rn(a.lr, __fadd_rn(g, __fmul_rn(a.wd, w))));
+        w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+        a.w[i] = w;
+        if (a.shadow) store_shadow<ST>(static_cast<ST *>(a.shadow), i, a.cols, a.ld_shadow, w);
+    }
+}
+
+// cpuAdamUpdate, src/backend.zig:2760-2772, with Adam.step's L2 term (src/optimizer.zig:221-228) folded in.
+template <typename ST>
+__global__ void adam_kernel(zn_opt_args a) {
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const bool write_g = (f != 1.0f) || (a.wd > 0.0f);
+    const float omb1 = 1.0f - a.beta1, omb2 = 1.0f - a.beta2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.count; i += (size_t)gridDim.x * blockDim.x) {
+        float g = a.g[i];
+        float w = a.w[i];
+        if (f != 1.0f) g = __fmul_rn(g, f);
+        if (a.wd > 0.0f) g = __fadd_rn(g, __fmul_rn(a.wd, w));
+        if (write_g) a.g[i] = g;
+        g = clamp_grad(g);
+        const float m = __fadd_rn(__fmul_rn(a.beta1, a.m[i]), __fmul_rn(omb1, g));
+        const float v = __fadd_rn(__fmul_rn(a.beta2, a.v[i]), __fmul_rn(__fmul_rn(omb2, g), g));
+        a.m[i] = m;
+        a.v[i] = v;
+        const float m_hat = __fdiv_rn(m, a.bc1);
+        const float v_hat = __fdiv_rn(v, a.bc2);
+        w = __fsub_rn(w, __fdiv_rn(__fmul_rn(a.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), a.eps)));
+        w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+        a.w[i] = w;
+        if (a.shadow) store_shadow<ST>(static_cast<ST *>(a.shadow), i, a.cols, a.ld_shadow, w);
+    }
+}
+
+int grid_for(zn_ctx *ctx, size_t n) {
+    size_t blocks = (n + TPB - 1) / TPB;
+    const size_t cap = (size_t)ctx->sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+}   // namespace
+
+zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev) {
+    if (nseg <= 0 || nseg > MAX_SEGS) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "grad norm: 1..%d tensors supported", MAX_SEGS);
+    SegTable tab;
+    int blocks = 0;
+    double bytes = 0;
+    for (int i = 0; i < nseg; ++i) {
+        tab.ptr[i] = segs[i].ptr;
+        tab.count[i] = segs[i].count;
+        tab.first_block[i] = blocks;
+        blocks += (int)((segs[i].count + ELEMS_PER_BLOCK - 1) / ELEMS_PER_BLOCK);
+        bytes += 4.0 * segs[i].count;
+    }
+    tab.first_block[nseg] = blocks;
+    tab.nseg = nseg;
+    if (blocks == 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "grad norm: empty tensors");
+    ZN_TRY(zn_scratch_reserve(ctx, (size_t)blocks));
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 2);
+    sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch);
+    norm_final_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, blocks, norm_factor_dev);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev) {
+    zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, 8.0 * n);
+    scale_kernel<<<grid_for(ctx, n), TPB, 0, ctx->stream>>>(p, n, factor_dev);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_sgd(zn_ctx *ctx, const zn_opt_args &a, bool is_bias) {
+    zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, (12.0 + (a.shadow ? (a.shadow_bf16 ? 2 : 4) : 0)) * a.count);
+    if (a.shadow && a.shadow_bf16) sgd_kernel<__nv_bfloat16><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a, is_bias ? 1 : 0);
+    else sgd_kernel<float><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a, is_bias ? 1 : 0);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_adam(zn_ctx *ctx, const zn_opt_args &a) {
+    zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, (28.0 + (a.shadow ? (a.shadow_bf16 ? 2 : 4) : 0)) * a.count);
+    if (a.shadow && a.shadow_bf16) adam_kernel<__nv_bfloat16><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a);
+    else adam_kernel<float><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}

@@ -1,0 +1,405 @@
+// Bandwidth-bound kernels of the Dense step: operand conversion, bias add,
+// activations, the column reduction behind accumulateBias, and the fused
+// loss value + gradient kernels.  All are sized for coalesced 16-byte accesses
+// and grids that are multiples of the SM count; reductions are two-stage
+// (block partials in the context's scratch, then one block adds them in a fixed
+// order), so results do not depend on scheduling.
+#include "zn_internal.h"
+
+namespace {
+
+constexpr int TPB = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over the block; the result is valid in thread 0.
+__device__ __forceinline__ float block_sum(float v) {
+    __shared__ float part[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) part[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        v = lane < (int)((blockDim.x + 31) >> 5) ? part[lane] : 0.f;
+        v = warp_sum(v);
+    }
+    return v;
+}
+
+__device__ __forceinline__ float act_fwd(int act, float x) {
+    switch (act) {
+    case ZN_ACT_RELU: return x > 0.f ? x : 0.f;
+    case ZN_ACT_SIGMOID:
+        if (x >= 0.f) return 1.f / (1.f + expf(-x));
+        else { const float e = expf(x); return e / (1.f + e); }
+    case ZN_ACT_TANH: return tanhf(x);
+    default: return x;
+    }
+}
+__device__ __forceinline__ float act_bwd(int act, float y, float g) {
+    switch (act) {
+    case ZN_ACT_RELU: return y > 0.f ? g : 0.f;
+    case ZN_ACT_SIGMOID: return __fmul_rn(__fmul_rn(g, y), (1.f - y));
+    case ZN_ACT_TANH: return __fmul_rn(g, (1.f - __fmul_rn(y, y)));
+    default: return g;
+    }
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- f32 -> operand type, with zeroed padding columns --------------------------------
+template <typename T>
+__global__ void convert_kernel(const float *__restrict__ src, int64_t ld_src, T *__restrict__ dst, int64_t ld_dst,
+                               int64_t rows, int64_t cols) {
+    // one thread per group of 8 destination columns
+    const int64_t groups_per_row = ld_dst / 8;
+    const int64_t total = rows * groups_per_row;
+    for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = g / groups_per_row, c0 = (g % groups_per_row) * 8;
+        const float *s = src + r * ld_src + c0;
+        float v[8];
+        if (c0 + 8 <= cols && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
+            const float4 a = *reinterpret_cast<const float4 *>(s), b = *reinterpret_cast<const float4 *>(s + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (c0 + j < cols) ? s[j] : 0.f;
+        }
+        T *d = dst + r * ld_dst + c0;
+        if (sizeof(T) == 2) {
+            uint32_t w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * h], v[2 * h + 1]);
+                w[h] = *reinterpret_cast<const uint32_t *>(&b2);
+            }
+            *reinterpret_cast<uint4 *>(d) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+            float *df = reinterpret_cast<float *>(d);
+            *reinterpret_cast<float4 *>(df) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(df + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    }
+}
+
+__global__ void add_bias_kernel(float *__restrict__ out, int64_t total, int64_t cols, const float *__restrict__ bias) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __fadd_rn(out[i], bias[i % cols]);
+}
+
+__global__ void act_forward_kernel(int act, const float *in, float *out, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = act_fwd(act, in[i]);
+}
+
+__global__ void act_backward_kernel(int act, const float *__restrict__ y, const float *__restrict__ go,
+                                    float *__restrict__ gi, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        gi[i] = act_bwd(act, y[i], go[i]);
+}
+
+// In-place activation derivative on an operand-typed gradient block: g = act'(y) (*) g.
+template <typename T>
+__global__ void act_backward_t_kernel(int act, const T *__restrict__ y, int64_t ld_y, T *__restrict__ g, int64_t ld_g,
+                                      int64_t rows, int64_t cols) {
+    const int64_t total = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i % cols;
+        const float yv = to_f32(y[r * ld_y + c]);
+        const float gv = to_f32(g[r * ld_g + c]);
+        g[r * ld_g + c] = from_f32<T>(act_bwd(act, yv, gv));
+    }
+}
+
+// ---- column sums ------------------------------------------------------------------------
+
+// Exact order: one thread per column, rows ascending (cpuAccumulateBias, src/backend.zig:706-713).
+template <typename T>
+__global__ void bias_reduce_exact_kernel(const T *__restrict__ g, int64_t ld, int64_t rows, int64_t cols,
+                                         float *__restrict__ gb, int accumulate) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = accumulate ? gb[c] : 0.f;
+    for (int64_t r = 0; r < rows; ++r) s = __fadd_rn(s, to_f32(g[r * ld + c]));
+    gb[c] = s;
+}
+
+// Stage 1: block (strip, split) sums rows [split*rows_per, ...) of a 32*VEC-column strip.
+// Each warp walks rows warp, warp+8, ...; a lane owns VEC adjacent columns (16 bytes).
+template <typename T, int VEC>
+__global__ void bias_reduce_partial_kernel(const T *__restrict__ g, int64_t ld, int64_t rows, int64_t cols,
+                                           int64_t rows_per, float *__restrict__ partial) {
+    constexpr int STRIP = 32 * VEC;
+    __shared__ float sm[TPB / 32][STRIP];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t c0 = (int64_t)blockIdx.x * STRIP + lane * VEC;
+    const int64_t r_begin = (int64_t)blockIdx.y * rows_per;
+    const int64_t r_end = min(rows, r_begin + rows_per);
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    const bool vec_ok = (c0 + VEC <= cols) && ((ld * sizeof(T)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(g) & 15) == 0);
+    for (int64_t r = r_begin + w; r < r_end; r += TPB / 32) {
+        const T *p = g + r * ld + c0;
+        if (vec_ok) {
+            const uint4 u = *reinterpret_cast<const uint4 *>(p);
+            if (sizeof(T) == 2) {
+                const uint32_t wv[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    acc[2 * h] += __uint_as_float(wv[h] << 16);
+                    acc[2 * h + 1] += __uint_as_float(wv[h] & 0xFFFF0000u);
+                }
+            } else {
+                acc[0] += __uint_as_float(u.x); acc[1] += __uint_as_float(u.y);
+                acc[2] += __uint_as_float(u.z); acc[3] += __uint_as_float(u.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                if (c0 + j < cols) acc[j] += to_f32(p[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) sm[w][lane * VEC + j] = acc[j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < STRIP; c += TPB) {
+        float s = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < TPB / 32; ++ww) s += sm[ww][c];
+        const int64_t gc = (int64_t)blockIdx.x * STRIP + c;
+        if (gc < cols) partial[(int64_t)blockIdx.y * cols + gc] = s;
+    }
+}
+
+// Stage 2: gb[c] (+)= sum over splits, in split order.
+__global__ void bias_reduce_final_kernel(const float *__restrict__ partial, int64_t cols, int splits,
+                                         float *__restrict__ gb, int accumulate) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int i = 0; i < splits; ++i) s += partial[(int64_t)i * cols + c];
+    gb[c] = accumulate ? gb[c] + s : s;
+}
+
+// ---- losses ---------------------------------------------------------------------------------
+
+// MSE (src/loss.zig:93-109): grad = 2*(o-t)/n, partial[block] = sum (o-t)^2 over the block's elements.
+template <typename T>
+__global__ void mse_kernel(const float *__restrict__ out, int64_t ld_o, const float *__restrict__ target,
+                           T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float n_div,
+                           float *__restrict__ partial) {
+    const int64_t total = rows * cols;
+    float s = 0.f;
+    const bool flat = (ld_o == cols) && (!grad || ld_g == cols);
+    if (flat && (total % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+        ((reinterpret_cast<uintptr_t>(target) & 15) == 0) && (sizeof(T) == 4 ? ((reinterpret_cast<uintptr_t>(grad) & 15) == 0)
+                                                                              : ((reinterpret_cast<uintptr_t>(grad) & 7) == 0))) {
+        const int64_t n4 = total / 4;
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+            const float4 o = reinterpret_cast<const float4 *>(out)[i];
+            const float4 t = reinterpret_cast<const float4 *>(target)[i];
+            const float d0 = o.x - t.x, d1 = o.y - t.y, d2 = o.z - t.z, d3 = o.w - t.w;
+            s += d0 * d0; s += d1 * d1; s += d2 * d2; s += d3 * d3;
+            if (grad) {
+                const float g0 = __fdiv_rn(2.f * d0, n_div), g1 = __fdiv_rn(2.f * d1, n_div);
+                const float g2 = __fdiv_rn(2.f * d2, n_div), g3 = __fdiv_rn(2.f * d3, n_div);
+                if (sizeof(T) == 4) {
+                    reinterpret_cast<float4 *>(grad)[i] = make_float4(g0, g1, g2, g3);
+                } else {
+                    const __nv_bfloat162 a = __floats2bfloat162_rn(g0, g1), b = __floats2bfloat162_rn(g2, g3);
+                    reinterpret_cast<uint2 *>(grad)[i] =
+                        make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+                }
+            }
+        }
+    } else {
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = i / cols, c = i % cols;
+            const float d = out[r * ld_o + c] - target[i];
+            s += d * d;
+            if (grad) grad[r * ld_g + c] = from_f32<T>(__fdiv_rn(2.f * d, n_div));
+        }
+    }
+    s = block_sum(s);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+// Softmax cross-entropy with logits, one warp per row (src/loss.zig:202-254 per row;
+// rows batched as kernels/loss.cu:123-155): grad = exp(l-max)/sum - t, row loss =
+// -(l[target] - (log(sum) + max)) with target = first column whose t > 0.5.
+template <typename T>
+__global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const float *__restrict__ target,
+                          T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float *__restrict__ partial) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    float loss_acc = 0.f;
+    for (int64_t r = (int64_t)blockIdx.x * wpb + w; r < rows; r += (int64_t)gridDim.x * wpb) {
+        const float *l = logits + r * ld_o;
+        const float *t = target + r * cols;
+        float mx = -INFINITY;
+        for (int64_t c = lane; c < cols; c += 32) mx = fmaxf(mx, l[c]);
+        mx = warp_max(mx);
+        float se = 0.f;
+        int64_t first = INT64_MAX;
+        for (int64_t c = lane; c < cols; c += 32) {
+            se += expf(l[c] - mx);
+            if (t[c] > 0.5f && c < first) first = c;
+        }
+        se = warp_sum(se);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+        if (grad) {
+            T *g = grad + r * ld_g;
+            for (int64_t c = lane; c < cols; c += 32)
+                g[c] = from_f32<T>(__fsub_rn(__fdiv_rn(expf(l[c] - mx), se), t[c]));
+        }
+        if (lane == 0 && first != INT64_MAX) loss_acc += -(l[first] - (logf(se) + mx));
+    }
+    loss_acc = block_sum(loss_acc);
+    if (threadIdx.x == 0) partial[blockIdx.x] = loss_acc;
+}
+
+__global__ void sum_partials_kernel(const float *__restrict__ partial, int n, float *__restrict__ out) {
+    // one block; double accumulation in a fixed order
+    __shared__ double sm[TPB];
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partial[i];
+    sm[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = TPB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *out = (float)sm[0];
+}
+
+int grid_for(zn_ctx *ctx, int64_t work_items, int per_sm = 8) {
+    int64_t blocks = (work_items + TPB - 1) / TPB;
+    const int64_t cap = (int64_t)ctx->sm_count * per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+}   // namespace
+
+zn_status zn_k_convert(zn_ctx *ctx, const float *src, int64_t ld_src, void *dst, int64_t ld_dst, bool dst_bf16,
+                       int64_t rows, int64_t cols) {
+    if (ld_dst % 8 != 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "convert: destination pitch must be a multiple of 8");
+    zn_launch_scope scope(ctx, ZN_PROF_CONVERT, 0, (double)rows * cols * (4 + (dst_bf16 ? 2 : 4)));
+    const int grid = grid_for(ctx, rows * (ld_dst / 8));
+    if (dst_bf16)
+        convert_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(src, ld_src, (__nv_bfloat16 *)dst, ld_dst, rows, cols);
+    else
+        convert_kernel<float><<<grid, TPB, 0, ctx->stream>>>(src, ld_src, (float *)dst, ld_dst, rows, cols);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_add_bias(zn_ctx *ctx, float *out, int64_t rows, int64_t cols, const float *bias) {
+    zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, 8.0 * rows * cols);
+    add_bias_kernel<<<grid_for(ctx, rows * cols), TPB, 0, ctx->stream>>>(out, rows * cols, cols, bias);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_act_forward(zn_ctx *ctx, int act, const float *in, float *out, int64_t n) {
+    zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, 8.0 * n);
+    act_forward_kernel<<<grid_for(ctx, n), TPB, 0, ctx->stream>>>(act, in, out, n);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_act_backward(zn_ctx *ctx, int act, const float *y, const float *go, float *gi, int64_t n) {
+    zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, 12.0 * n);
+    act_backward_kernel<<<grid_for(ctx, n), TPB, 0, ctx->stream>>>(act, y, go, gi, n);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_act_backward_t(zn_ctx *ctx, int act, const void *y, int64_t ld_y, void *g, int64_t ld_g, bool bf16,
+                              int64_t rows, int64_t cols) {
+    zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, (double)rows * cols * (bf16 ? 6 : 12));
+    const int grid = grid_for(ctx, rows * cols);
+    if (bf16)
+        act_backward_t_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(act, (const __nv_bfloat16 *)y, ld_y, (__nv_bfloat16 *)g, ld_g, rows, cols);
+    else
+        act_backward_t_kernel<float><<<grid, TPB, 0, ctx->stream>>>(act, (const float *)y, ld_y, (float *)g, ld_g, rows, cols);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, int64_t rows, int64_t cols, float *gb,
+                           bool accumulate, bool exact) {
+    const double bytes = (double)rows * cols * (g_bf16 ? 2 : 4) + 4.0 * cols;
+    if (exact) {
+        zn_launch_scope scope(ctx, ZN_PROF_BIAS_REDUCE, 0, bytes);
+        const int grid = (int)((cols + 127) / 128);
+        if (g_bf16)
+            bias_reduce_exact_kernel<__nv_bfloat16><<<grid, 128, 0, ctx->stream>>>((const __nv_bfloat16 *)g, ld, rows, cols, gb, accumulate);
+        else
+            bias_reduce_exact_kernel<float><<<grid, 128, 0, ctx->stream>>>((const float *)g, ld, rows, cols, gb, accumulate);
+        ZN_CUDA(ctx, cudaGetLastError());
+        return ZN_OK;
+    }
+    const int vec = g_bf16 ? 8 : 4, strip = 32 * vec;
+    const int strips = (int)((cols + strip - 1) / strip);
+    // enough row splits to fill the machine about four times over, at least 64 rows each
+    int64_t splits = ((int64_t)ctx->sm_count * 4 + strips - 1) / strips;
+    const int64_t max_splits = (rows + 63) / 64;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    if (splits > 65535) splits = 65535;
+    const int64_t rows_per = (rows + splits - 1) / splits;
+    splits = (rows + rows_per - 1) / rows_per;
+    ZN_TRY(zn_scratch_reserve(ctx, (size_t)(splits * cols)));
+    zn_launch_scope scope(ctx, ZN_PROF_BIAS_REDUCE, 0, bytes, 2);
+    dim3 grid((unsigned)strips, (unsigned)splits);
+    if (g_bf16)
+        bias_reduce_partial_kernel<__nv_bfloat16, 8><<<grid, TPB, 0, ctx->stream>>>((const __nv_bfloat16 *)g, ld, rows, cols, rows_per, ctx->scratch);
+    else
+        bias_reduce_partial_kernel<float, 4><<<grid, TPB, 0, ctx->stream>>>((const float *)g, ld, rows, cols, rows_per, ctx->scratch);
+    bias_reduce_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(ctx->scratch, cols, (int)splits, gb, accumulate);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const float *target, void *grad, bool grad_bf16,
+                    int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor, float *loss_sum_dev) {
+    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
+        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path (mse and cross_entropy_logits are)", loss);
+    const int64_t total = rows * cols;
+    int grid;
+    if (loss == ZN_LOSS_MSE) grid = grid_for(ctx, (total + 3) / 4, 4);
+    else grid = grid_for(ctx, rows * 32, 8);
+    ZN_TRY(zn_scratch_reserve(ctx, (size_t)grid));
+    zn_launch_scope scope(ctx, ZN_PROF_LOSS, 0, (double)total * (8 + (grad ? (grad_bf16 ? 2 : 4) : 0)), 2);
+    if (loss == ZN_LOSS_MSE) {
+        if (grad_bf16)
+            mse_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+        else
+            mse_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+    } else {
+        if (grad_bf16)
+            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch);
+        else
+            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch);
+    }
+    sum_partials_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, grid, loss_sum_dev);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}

@@ -1,0 +1,313 @@
+// Context, device tensors, copies, error reporting and event-based profiling.
+// Replaces CudaBackend.init / CudaContext.init / the dlopen'd driver table of the
+// reference (src/cuda.zig:163, src/cuda_context.zig:382-497, src/cuda_driver.zig:710).
+#include <cstdarg>
+#include <cstring>
+
+#include "zn_internal.h"
+
+zn_status zn_fail(zn_ctx *ctx, zn_status s, const char *fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, ZN_MAX_ERR, fmt, ap);
+        va_end(ap);
+    }
+    return s;
+}
+
+zn_status zn_cuda_status(zn_ctx *ctx, cudaError_t e, const char *what) {
+    zn_status s = ZN_ERR_CUDA;
+    switch (e) {
+    case cudaErrorMemoryAllocation: s = ZN_ERR_OUT_OF_MEMORY; break;
+    case cudaErrorInvalidValue: s = ZN_ERR_INVALID_VALUE; break;
+    case cudaErrorInvalidDevice: s = ZN_ERR_INVALID_DEVICE; break;
+    case cudaErrorNoDevice:
+    case cudaErrorInsufficientDriver: s = ZN_ERR_NO_DEVICE; break;
+    case cudaErrorInitializationError: s = ZN_ERR_NOT_INITIALIZED; break;
+    default: break;
+    }
+    return zn_fail(ctx, s, "%s: %s", what, cudaGetErrorString(e));
+}
+
+extern "C" const char *zn_status_string(zn_status s) {
+    switch (s) {
+    case ZN_OK: return "ok";
+    case ZN_ERR_INVALID_VALUE: return "invalid value";
+    case ZN_ERR_OUT_OF_MEMORY: return "out of memory";
+    case ZN_ERR_NOT_INITIALIZED: return "not initialized";
+    case ZN_ERR_NO_DEVICE: return "no CUDA device";
+    case ZN_ERR_INVALID_DEVICE: return "invalid device";
+    case ZN_ERR_CUDA: return "CUDA error";
+    case ZN_ERR_SHAPE: return "shape mismatch";
+    case ZN_ERR_UNSUPPORTED: return "unsupported on the Dense path";
+    case ZN_ERR_TIMEOUT: return "device-side wait timed out";
+    case ZN_ERR_NCCL: return "NCCL error";
+    case ZN_ERR_NOT_AVAILABLE: return "not available";
+    default: return "unknown status";
+    }
+}
+
+extern "C" const char *zn_last_error_string(const zn_ctx *ctx) { return ctx ? ctx->err : "null context"; }
+
+extern "C" int32_t zn_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+extern "C" zn_status zn_ctx_create(int32_t device, zn_ctx **out) {
+    if (!out) return ZN_ERR_INVALID_VALUE;
+    *out = nullptr;
+    int n = zn_device_count();
+    if (n == 0) return ZN_ERR_NO_DEVICE;
+    if (device < 0 || device >= n) return ZN_ERR_INVALID_DEVICE;
+    zn_ctx *ctx = new zn_ctx();
+    ctx->device = device;
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess) e = cudaHostAlloc((void **)&ctx->status_host, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *ctx->status_host = 0;
+        e = cudaHostGetDevicePointer((void **)&ctx->status_dev, ctx->status_host, 0);
+    }
+    if (e == cudaSuccess) e = cudaHostAlloc((void **)&ctx->pinned_scalar, 16 * sizeof(float), cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        zn_ctx_destroy(ctx);
+        cudaGetLastError();
+        return e == cudaErrorMemoryAllocation ? ZN_ERR_OUT_OF_MEMORY : ZN_ERR_CUDA;
+    }
+    *out = ctx;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_dp_destroy(zn_ctx *ctx);
+
+extern "C" void zn_ctx_destroy(zn_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->dp) zn_dp_destroy(ctx);
+    for (auto &kv : ctx->tensors) cudaFree(kv.first);
+    for (int i = 0; i < 6; ++i) cudaFree(ctx->stage[i]);
+    cudaFree(ctx->scratch);
+    for (auto &slot : ctx->prof)
+        for (auto &p : slot.pending) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
+    for (auto ev : ctx->event_pool) cudaEventDestroy(ev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->pinned_scalar) cudaFreeHost(ctx->pinned_scalar);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+    if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
+    delete ctx;
+}
+
+extern "C" zn_status zn_ctx_set_precision(zn_ctx *ctx, zn_precision p) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (p < ZN_FP32_SIMT || p > ZN_BF16_TC) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "unknown precision %d", (int)p);
+    ctx->precision = p;
+    return ZN_OK;
+}
+
+zn_status zn_check_device_status(zn_ctx *ctx) {
+    if (ctx->status_host && *ctx->status_host != 0) {
+        int code = *ctx->status_host;
+        *ctx->status_host = 0;
+        return zn_fail(ctx, ZN_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", code);
+    }
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_begin_command_batch(zn_ctx *ctx) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    ctx->batch_depth += 1;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_end_command_batch(zn_ctx *ctx) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (ctx->batch_depth > 0) ctx->batch_depth -= 1;
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return zn_check_device_status(ctx);
+}
+
+bool zn_is_device_ptr(const void *p) {
+    if (!p) return false;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+zn_status zn_scratch_reserve(zn_ctx *ctx, size_t floats) {
+    if (ctx->scratch_floats >= floats) return ZN_OK;
+    // Work already queued may still use the old block: drain before replacing it.
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(ctx->scratch);
+    ctx->scratch = nullptr;
+    ctx->scratch_floats = 0;
+    size_t want = floats < (1u << 16) ? (1u << 16) : floats;
+    ZN_CUDA(ctx, cudaMalloc((void **)&ctx->scratch, want * sizeof(float)));
+    ctx->scratch_floats = want;
+    return ZN_OK;
+}
+
+// ---- tensors ----------------------------------------------------------------------
+
+extern "C" zn_status zn_tensor_alloc(zn_ctx *ctx, size_t count, float **out_dev) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!out_dev || count == 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_tensor_alloc: null output or zero size");
+    if (count > (SIZE_MAX / sizeof(float))) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_tensor_alloc: size overflow");
+    cudaSetDevice(ctx->device);
+    float *p = nullptr;
+    ZN_CUDA(ctx, cudaMalloc((void **)&p, count * sizeof(float)));
+    cudaError_t e = cudaMemsetAsync(p, 0, count * sizeof(float), ctx->stream);
+    if (e != cudaSuccess) { cudaFree(p); return zn_cuda_status(ctx, e, "cudaMemsetAsync"); }
+    ctx->tensors[p] = count;
+    *out_dev = p;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_tensor_free(zn_ctx *ctx, float *dev) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!dev) return ZN_OK;
+    auto it = ctx->tensors.find(dev);
+    if (it == ctx->tensors.end()) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_tensor_free: not a tensor of this context");
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ZN_CUDA(ctx, cudaFree(dev));
+    ctx->tensors.erase(it);
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_tensor_upload(zn_ctx *ctx, float *dev, const float *host, size_t count) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!dev || !host) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_tensor_upload: null pointer");
+    ZN_CUDA(ctx, cudaMemcpyAsync(dev, host, count * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_tensor_download(zn_ctx *ctx, float *host, const float *dev, size_t count) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!dev || !host) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_tensor_download: null pointer");
+    ZN_CUDA(ctx, cudaMemcpyAsync(host, dev, count * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return zn_check_device_status(ctx);
+}
+
+extern "C" zn_status zn_copy_data(zn_ctx *ctx, const float *src, float *dst, size_t count) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!src || !dst) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_copy_data: null pointer");
+    if (src == dst || count == 0) return ZN_OK;
+    ZN_CUDA(ctx, cudaMemcpyAsync(dst, src, count * sizeof(float), cudaMemcpyDefault, ctx->stream));
+    if (!(zn_is_device_ptr(src) && zn_is_device_ptr(dst))) ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_host_alloc(zn_ctx *ctx, size_t count, float **out_host) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!out_host || count == 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "zn_host_alloc: null output or zero size");
+    ZN_CUDA(ctx, cudaHostAlloc((void **)out_host, count * sizeof(float), cudaHostAllocDefault));
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_host_free(zn_ctx *ctx, float *host) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (host) ZN_CUDA(ctx, cudaFreeHost(host));
+    return ZN_OK;
+}
+
+// ---- profiling ----------------------------------------------------------------------
+
+static cudaEvent_t take_event(zn_ctx *ctx) {
+    if (!ctx->event_pool.empty()) {
+        cudaEvent_t e = ctx->event_pool.back();
+        ctx->event_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
+zn_launch_scope::zn_launch_scope(zn_ctx *c, int fam, double flops, double bytes, int n_launches) : ctx(c), family(fam) {
+    ctx->launches += (uint64_t)n_launches;
+    if (!ctx->profiling) return;
+    zn_prof_slot &s = ctx->prof[family];
+    s.launches += (uint64_t)n_launches;
+    s.flops += flops;
+    s.bytes += bytes;
+    e0 = take_event(ctx);
+    e1 = take_event(ctx);
+    cudaEventRecord(e0, ctx->stream);
+}
+
+zn_launch_scope::~zn_launch_scope() {
+    if (!e0) return;
+    cudaEventRecord(e1, ctx->stream);
+    ctx->prof[family].pending.emplace_back(e0, e1);
+}
+
+static void drain_profile(zn_ctx *ctx) {
+    cudaStreamSynchronize(ctx->stream);
+    for (auto &slot : ctx->prof) {
+        for (auto &p : slot.pending) {
+            float ms = 0;
+            if (cudaEventElapsedTime(&ms, p.first, p.second) == cudaSuccess) slot.ms += ms;
+            ctx->event_pool.push_back(p.first);
+            ctx->event_pool.push_back(p.second);
+        }
+        slot.pending.clear();
+    }
+}
+
+extern "C" zn_status zn_profile_enable(zn_ctx *ctx, int32_t on) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!on && ctx->profiling) drain_profile(ctx);
+    ctx->profiling = on != 0;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_profile_reset(zn_ctx *ctx) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    drain_profile(ctx);
+    for (auto &slot : ctx->prof) { slot.ms = slot.flops = slot.bytes = 0; slot.launches = 0; }
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_profile_get(zn_ctx *ctx, zn_prof_family family, double *ms, uint64_t *launches, double *flops,
+                                    double *bytes) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (family < 0 || family >= ZN_PROF_FAMILY_COUNT) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "unknown kernel family");
+    drain_profile(ctx);
+    const zn_prof_slot &s = ctx->prof[family];
+    if (ms) *ms = s.ms;
+    if (launches) *launches = s.launches;
+    if (flops) *flops = s.flops;
+    if (bytes) *bytes = s.bytes;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_launch_count(zn_ctx *ctx, uint64_t *out) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!out) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "null output");
+    *out = ctx->launches;
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_distribute_workload(size_t total, size_t parts, size_t index, size_t *start, size_t *end) {
+    if (!start || !end || parts == 0 || index >= parts) return ZN_ERR_INVALID_VALUE;
+    const size_t base = total / parts, rem = total % parts;
+    const size_t lo = index * base + (index < rem ? index : rem);
+    *start = lo;
+    *end = lo + base + (index < rem ? 1 : 0);
+    return ZN_OK;
+}

@@ -1,0 +1,146 @@
+// Internal declarations shared by the translation units of libzn_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "zn_b200.h"
+
+#define ZN_MAX_ERR 512
+
+struct zn_prof_slot {
+    double ms = 0, flops = 0, bytes = 0;
+    uint64_t launches = 0;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;   // recorded, not yet read back
+};
+
+struct zn_dp_state;   // dp.cu
+
+struct zn_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;        // every kernel of this library runs here
+    cudaStream_t copy_stream = nullptr;   // host<->device copies of the pipelined step
+    cudaStream_t comm_stream = nullptr;   // gradient all-reduces
+    zn_precision precision = ZN_FP32_SIMT;
+    int batch_depth = 0;
+    char err[ZN_MAX_ERR] = {0};
+
+    // One pinned word the kernels' bounded waits write into when they give up.
+    int *status_host = nullptr;           // cudaHostAlloc'd, mapped
+    int *status_dev = nullptr;            // device alias of status_host
+
+    // Scratch for two-stage reductions (block partials); grown on demand.
+    float *scratch = nullptr;
+    size_t scratch_floats = 0;
+    // Staging for ops called with host pointers; grown on demand.
+    float *stage[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t stage_floats[6] = {0, 0, 0, 0, 0, 0};
+    float *pinned_scalar = nullptr;       // 16 floats of pinned host memory for scalar read-backs
+
+    std::unordered_map<float *, size_t> tensors;   // zn_tensor_alloc registry (ptr -> count)
+    std::unordered_map<std::string, std::vector<uint8_t>> tmap_cache;   // encoded TMA descriptors
+
+    uint64_t launches = 0;
+    bool profiling = false;
+    zn_prof_slot prof[ZN_PROF_FAMILY_COUNT];
+    std::vector<cudaEvent_t> event_pool;
+
+    zn_dp_state *dp = nullptr;
+};
+
+zn_status zn_fail(zn_ctx *ctx, zn_status s, const char *fmt, ...);
+zn_status zn_cuda_status(zn_ctx *ctx, cudaError_t e, const char *what);
+#define ZN_CUDA(ctx, call)                                                            \
+    do {                                                                              \
+        cudaError_t e__ = (call);                                                     \
+        if (e__ != cudaSuccess) return zn_cuda_status((ctx), e__, #call);             \
+    } while (0)
+#define ZN_TRY(call)                                                                  \
+    do {                                                                              \
+        zn_status s__ = (call);                                                       \
+        if (s__ != ZN_OK) return s__;                                                 \
+    } while (0)
+
+// Launch bookkeeping: counts the launch and, when profiling, brackets it with events.
+struct zn_launch_scope {
+    zn_ctx *ctx;
+    int family;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    zn_launch_scope(zn_ctx *c, int fam, double flops, double bytes, int n_launches = 1);
+    ~zn_launch_scope();
+};
+
+zn_status zn_scratch_reserve(zn_ctx *ctx, size_t floats);
+zn_status zn_check_device_status(zn_ctx *ctx);   // reads the pinned status word after a sync
+bool zn_is_device_ptr(const void *p);
+
+// ---- kernels (each launcher enqueues on ctx->stream and returns) ------------------
+
+// Epilogue applied by both GEMM families to the fp32 accumulator v of C[r][c]:
+//   v += bias[c]; v = act(v); if (mask) v = mask[r][c] > 0 ? v : 0; if (accumulate) v += C_old[r][c]
+// and stored as fp32 (out_f32) and/or as the activation type (out_t).
+struct zn_epilogue {
+    const float *bias = nullptr;
+    int act = ZN_ACT_LINEAR;
+    const void *mask = nullptr;        // activation type of the GEMM (float for SIMT/TF32, bf16 for BF16)
+    int64_t ld_mask = 0;
+    float *out_f32 = nullptr;
+    int64_t ld_out_f32 = 0;
+    void *out_t = nullptr;             // only the tensor-core path: output in the operand type
+    int64_t ld_out_t = 0;
+    int accumulate = 0;                // += into out_f32
+};
+
+// fp32 CUDA-core GEMM.  A(i,p) = a[i*a_rs + p*a_cs], B(p,j) = b[p*b_rs + j*b_cs].
+zn_status zn_gemm_simt(zn_ctx *ctx, const float *a, int64_t a_rs, int64_t a_cs, const float *b, int64_t b_rs,
+                       int64_t b_cs, int64_t m, int64_t n, int64_t k, const zn_epilogue &ep, bool exact);
+
+// tcgen05 GEMM.  Operand element type: 0 = bf16, 1 = tf32 (fp32 storage).
+// A is K-major when a_mn_major == false (memory [m][lda]) and M-major otherwise ([k][lda]);
+// B is K-major when b_mn_major == false (memory [n][ldb]) and N-major otherwise ([k][ldb]).
+// lda/ldb are in elements and must make the row pitch a multiple of 16 bytes.
+zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, bool a_mn_major, const void *b,
+                     int64_t ldb, bool b_mn_major, int64_t m, int64_t n, int64_t k, const zn_epilogue &ep);
+
+// Row-major helpers.  T = float or __nv_bfloat16 selected by is_bf16.
+zn_status zn_k_convert(zn_ctx *ctx, const float *src, int64_t ld_src, void *dst, int64_t ld_dst, bool dst_bf16,
+                       int64_t rows, int64_t cols);   // pads columns [cols, ld_dst) with zeros
+zn_status zn_k_add_bias(zn_ctx *ctx, float *out, int64_t rows, int64_t cols, const float *bias);
+zn_status zn_k_act_forward(zn_ctx *ctx, int act, const float *in, float *out, int64_t n);
+zn_status zn_k_act_backward(zn_ctx *ctx, int act, const float *y, const float *go, float *gi, int64_t n);
+// In place g = act'(y) (*) g on operand-typed blocks (activations whose derivative is not fused in a GEMM epilogue).
+zn_status zn_k_act_backward_t(zn_ctx *ctx, int act, const void *y, int64_t ld_y, void *g, int64_t ld_g, bool bf16,
+                              int64_t rows, int64_t cols);
+// gb[c] (+)= sum_r g[r][c]; exact = one thread per column, rows ascending.
+zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, int64_t rows, int64_t cols,
+                           float *gb, bool accumulate, bool exact);
+// Loss value and gradient in one pass over output (fp32, row pitch ld_o) and target (fp32, dense).
+// grad (type by grad_bf16, pitch ld_g) may be null (value only).  loss_sum_dev gets the SUM (squared errors
+// for MSE, row losses for CE); the caller divides.  mse_divisor is the n of 2(o-t)/n.
+zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const float *target, void *grad,
+                    bool grad_bf16, int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor,
+                    float *loss_sum_dev);
+
+struct zn_seg { const float *ptr; size_t count; };
+// norm_factor_dev[0] = sqrt(sum g^2), [1] = clip factor (1 when norm <= 1); extra_sq_dev optional.
+zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev);
+zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev);
+
+struct zn_opt_args {
+    float *w; float *g; float *m; float *v; size_t count;
+    float lr, wd, beta1, beta2, eps, bc1, bc2;
+    float w_clamp;                  // 100 for weights, 50 for SGD bias
+    const float *factor_dev;        // clip factor on the device, or null
+    void *shadow;                   // operand-type copy of w for the tensor-core GEMMs, or null
+    bool shadow_bf16;
+    int64_t cols, ld_shadow;        // shadow[(i / cols) * ld_shadow + i % cols]
+};
+zn_status zn_k_sgd(zn_ctx *ctx, const zn_opt_args &a, bool is_bias);
+zn_status zn_k_adam(zn_ctx *ctx, const zn_opt_args &a);

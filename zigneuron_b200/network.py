@@ -1,0 +1,136 @@
+"""Network: the reference's `Network` (src/network.zig) restricted to Dense
+layers, resident on the GPU.  Names follow the reference: addDense, forward,
+trainStep, train; per-layer optimizers as in `Network.optimizers`."""
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from ._lib import check, lib, ptr
+from .backend import Activation, Backend, Loss, Precision
+
+
+@dataclass
+class Sgd:                      # src/optimizer.zig:81-85 (momentum 0 only on this path)
+    momentum: float = 0.0
+    weight_decay: float = 0.0
+
+
+@dataclass
+class Adam:                     # src/optimizer.zig:169-184
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+
+
+class Network:
+    def __init__(self, backend: Backend, precision=None):
+        self.backend = backend
+        self.precision = Precision(precision if precision is not None else backend.precision)
+        h = C.c_void_p()
+        check(lib.zn_net_create(backend.handle, int(self.precision), C.byref(h)), backend.handle)
+        self.handle = h.value
+        self.shapes = []
+
+    def deinit(self):
+        if getattr(self, "handle", None) and self.backend.handle:
+            lib.zn_net_destroy(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.deinit()
+        except Exception:
+            pass
+
+    def _ck(self, status):
+        check(status, self.backend.handle)
+
+    # Network.addDense, src/network.zig:104-122
+    def addDense(self, input_size, output_size, act):
+        idx = C.c_int32()
+        self._ck(lib.zn_net_add_dense(self.handle, input_size, output_size, int(Activation[act] if isinstance(act, str) else act),
+                                      C.byref(idx)))
+        self.shapes.append((input_size, output_size))
+        return idx.value
+
+    def setOptimizer(self, opt, layer=-1):
+        if isinstance(opt, Adam):
+            self._ck(lib.zn_net_set_adam(self.handle, layer, opt.beta1, opt.beta2, opt.eps, opt.weight_decay))
+        elif isinstance(opt, Sgd):
+            if opt.momentum != 0.0:
+                raise NotImplementedError("momentum SGD is outside the Dense hot path")
+            self._ck(lib.zn_net_set_sgd(self.handle, layer, opt.weight_decay))
+        else:
+            raise TypeError(opt)
+
+    def setWeights(self, layer, weights=None, bias=None):
+        w = None if weights is None else np.ascontiguousarray(weights, np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        self._ck(lib.zn_net_set_weights(self.handle, layer, ptr(w), ptr(b)))
+
+    def getWeights(self, layer):
+        i, o = self.shapes[layer]
+        w, b = np.empty((i, o), np.float32), np.empty(o, np.float32)
+        self._ck(lib.zn_net_get_weights(self.handle, layer, ptr(w), ptr(b)))
+        return w, b
+
+    def getGrads(self, layer):
+        i, o = self.shapes[layer]
+        w, b = np.empty((i, o), np.float32), np.empty(o, np.float32)
+        self._ck(lib.zn_net_get_grads(self.handle, layer, ptr(w), ptr(b)))
+        return w, b
+
+    def getInputGrad(self, rows):
+        g = np.empty((rows, self.shapes[0][0]), np.float32)
+        self._ck(lib.zn_net_get_input_grad(self.handle, ptr(g), g.size))
+        return g
+
+    # Network.forward, src/network.zig:309
+    def forward(self, input, rows=None):
+        x = np.ascontiguousarray(input, np.float32)
+        rows = rows if rows is not None else x.size // self.shapes[0][0]
+        out = np.empty((rows, self.shapes[-1][1]), np.float32)
+        self._ck(lib.zn_net_forward(self.handle, ptr(x), rows, ptr(out)))
+        return out
+
+    # Network.trainStep, src/network.zig:481
+    def trainStep(self, input, target, learning_rate, loss_fn, rows=None):
+        if rows is None:
+            rows = input.size // self.shapes[0][0]
+        if isinstance(input, np.ndarray):
+            input = np.ascontiguousarray(input, np.float32)
+        if isinstance(target, np.ndarray):
+            target = np.ascontiguousarray(target, np.float32)
+        out = C.c_float()
+        self._ck(lib.zn_net_train_step(self.handle, ptr(input), ptr(target), rows, learning_rate, int(loss_fn), C.byref(out)))
+        return out.value
+
+    def submitStep(self, host_input, host_target, rows, learning_rate, loss_fn):
+        self._ck(lib.zn_net_submit_step(self.handle, ptr(host_input), ptr(host_target), rows, learning_rate, int(loss_fn)))
+
+    def waitStep(self):
+        out = C.c_float()
+        self._ck(lib.zn_net_wait_step(self.handle, C.byref(out)))
+        return out.value
+
+    # Network.train, src/network.zig:596 (constant scheduler, no early stopping)
+    def train(self, inputs, targets, epochs, learning_rate, loss_fn):
+        x = np.ascontiguousarray(inputs, np.float32)
+        t = np.ascontiguousarray(targets, np.float32)
+        samples = x.shape[0]
+        losses = np.zeros(epochs, np.float32)
+        self._ck(lib.zn_net_train(self.handle, ptr(x), ptr(t), samples, epochs, learning_rate, int(loss_fn), ptr(losses)))
+        return losses
+
+    def lastClip(self):
+        a, b = C.c_float(), C.c_float()
+        self._ck(lib.zn_net_last_clip(self.handle, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def setDataParallel(self, global_rows):
+        self._ck(lib.zn_net_set_data_parallel(self.handle, global_rows))
+
+
+__all__ = ["Network", "Sgd", "Adam", "Loss", "Activation"]
