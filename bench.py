@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the Dense-layer training step.
+
+    python bench.py --gpus N --steps K --warmup W            # this library, N ranks (torchrun for N > 1)
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU path (oracle port), host cores
+
+Workload (config.workload): BASELINE configs[3], the data-parallel wide MLP
+4096-8192-8192-8192-4096 (ReLU hidden, linear output), bf16 operands with fp32
+accumulation and fp32 master weights, MSE against N(0,1) targets, Adam, GLOBAL
+batch 65536 split evenly over the ranks (strong scaling), one fp32 gradient
+all-reduce per layer per step.  Inputs are seeded synthetic N(0,1) blocks; the
+weights are drawn in the reference's distribution, U(-1,1)*scale(act).
+
+One JSON line on stdout (rank 0).  `value` times steps whose inputs already sit in
+HBM; `e2e` times the same steps fed from pinned host memory through the pipelined
+C-ABI call (host->device copies and the loss read-back inside the timed region).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DIMS = [(4096, 8192), (8192, 8192), (8192, 8192), (8192, 4096)]
+ACTS = ["relu", "relu", "relu", "linear"]
+GLOBAL_BATCH = 65536
+SEED = 3
+LR = 1e-3
+BLOCK_ROWS = 1024                     # data is generated in blocks of rows keyed by (seed, stream, block)
+SUM_IO = sum(a * b for a, b in DIMS)  # 201,326,592
+PARAMS = SUM_IO + sum(b for _, b in DIMS)
+FLOP_PER_SAMPLE = 6.0 * SUM_IO        # forward + dX + dW GEMMs, the reference's dX of layer 0 included
+
+
+def layer_weights(layer):
+    """U(-1,1) * scale(act): sqrt(2/in) for relu, sqrt(1/in) for linear (src/layer.zig:330-338)."""
+    (n_in, n_out), act = DIMS[layer], ACTS[layer]
+    rng = np.random.default_rng([SEED, 100 + layer])
+    scale = np.float32(np.sqrt((2.0 if act == "relu" else 1.0) / n_in))
+    w = rng.random((n_in, n_out), dtype=np.float32)
+    w *= np.float32(2.0)
+    w -= np.float32(1.0)
+    w *= scale
+    return w
+
+
+def fill_rows(dst, stream, row0):
+    """dst[i] = global row row0+i of N(0,1) stream `stream` (0 inputs, 1 targets); same data for any rank count."""
+    rows, cols = dst.shape
+    assert row0 % BLOCK_ROWS == 0
+    for off in range(0, rows, BLOCK_ROWS):
+        n = min(BLOCK_ROWS, rows - off)
+        rng = np.random.default_rng([SEED, stream, (row0 + off) // BLOCK_ROWS])
+        dst[off:off + n] = rng.standard_normal((BLOCK_ROWS, cols), dtype=np.float32)[:n]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        d = json.load(open(path))
+        return {"bf16_sustained": float(d["bf16_tflops_sustained"]), "bf16_burst": float(d["bf16_tflops"]),
+                "hbm": float(d["hbm_gbs"]), "source": "measured"}
+    except Exception:
+        return {"bf16_sustained": 1400.0, "bf16_burst": 1590.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, device):
+        super().__init__(daemon=True)
+        self.device, self.samples, self.reasons, self.max_mhz, self.stop_flag = device, [], set(), None, False
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(device)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            pass
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self.stop_flag:
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# --------------------------------------------------------------------------------------- CPU side
+
+def oracle_net():
+    from oracle import zn_oracle as zo
+    net = zo.Net()
+    for i, ((a, b), act) in enumerate(zip(DIMS, ACTS)):
+        net.add_dense(a, b, zo.RELU if act == "relu" else zo.LINEAR)
+        net.set_params(i, layer_weights(i), np.zeros(b, np.float32))
+        net.set_adam(i)
+    return net, zo
+
+
+def cpu_sample(net, zo, rows, x, t):
+    """One bounded sample of the workload on one host core: gradients of `rows` rows of the global batch
+    (the per-row part of a step) and one clip + Adam pass over all parameters (the per-step part).
+    Returns (seconds per row, seconds per step-fixed part)."""
+    t0 = time.perf_counter()
+    net.shard_gradients(x[:rows], t[:rows], rows, GLOBAL_BATCH, zo.MSE)
+    t1 = time.perf_counter()
+    net.clip_and_update(LR)
+    t2 = time.perf_counter()
+    return (t1 - t0) / rows, t2 - t1
+
+
+def cpu_rows_for_budget(net, zo, x, t, seconds):
+    per_row, _ = cpu_sample(net, zo, 2, x, t)
+    return int(max(2, min(x.shape[0], round(seconds / max(per_row, 1e-3)))))
+
+
+def cpu_baseline(budget_s=12.0):
+    net, zo = oracle_net()
+    x = np.empty((64, DIMS[0][0]), np.float32)
+    t = np.empty((64, DIMS[-1][1]), np.float32)
+    fill_rows(x, 0, 0)
+    fill_rows(t, 1, 0)
+    rows = cpu_rows_for_budget(net, zo, x, t, budget_s)
+    per_row, fixed = cpu_sample(net, zo, rows, x, t)
+    value = GLOBAL_BATCH / (GLOBAL_BATCH * per_row + fixed)
+    return {"value": value, "unit": "samples/s", "cores": 1, "kind": "port",
+            "sample": f"oracle (single-threaded restatement of the reference CPU path): forward+backward of {rows} rows "
+                      f"of the global batch ({per_row * 1e3:.1f} ms/row) plus one clip+Adam pass over {PARAMS} parameters "
+                      f"({fixed:.2f} s); extrapolated to a {GLOBAL_BATCH}-row step as rows*per_row + fixed"}
+
+
+def run_reference(args):
+    """--impl reference: the reference's own CPU Dense path (its restatement in oracle/, the reference being
+    Zig with no toolchain here), on the host cores it can use: one, the path has no threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    net, zo = oracle_net()
+    x = np.empty((64, DIMS[0][0]), np.float32)
+    t = np.empty((64, DIMS[-1][1]), np.float32)
+    fill_rows(x, 0, 0)
+    fill_rows(t, 1, 0)
+    total_budget = 150.0
+    rows = cpu_rows_for_budget(net, zo, x, t, total_budget / (args.steps + args.warmup) * 0.6)
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_sample(net, zo, rows, x, t)
+    step_s = []
+    for _ in range(args.steps):
+        per_row, fixed = cpu_sample(net, zo, rows, x, t)
+        step_s.append(GLOBAL_BATCH * per_row + fixed)
+    ms = 1e3 * float(np.mean(step_s))
+    value = GLOBAL_BATCH / (ms / 1e3)
+    sample = (f"each step = gradients of {rows} rows of the global batch + one clip+Adam pass over all parameters, "
+              f"extrapolated to {GLOBAL_BATCH} rows (rows are independent in the reference loops)")
+    line = {
+        "impl": "reference", "metric": "train_samples_per_sec", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 1, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "wide_mlp_dp: BASELINE configs[3], MLP 4096-8192-8192-8192-4096 relu/linear, MSE, Adam lr 1e-3, seed 3",
+            "global_batch": GLOBAL_BATCH, "per_gpu_batch": GLOBAL_BATCH // n_gpus, "parallelism": f"dp{n_gpus}",
+            "params": PARAMS, "allreduce_bytes_per_step": 4 * PARAMS if n_gpus > 1 else 0,
+            "l2": "inputs (>= 256 MB per rank and step) and weights (805 MB) exceed the 126 MB L2; no flush needed"}
+
+
+# --------------------------------------------------------------------------------------- GPU side
+
+def run_ours(args):
+    import zigneuron_b200 as zn
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def barrier():
+        if dist:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if not dist:
+            return v
+        import torch
+        tt = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt[0])
+
+    be = zn.Backend(local, zn.Precision.BF16_TC)
+    if world > 1:
+        ids = [zn.Backend.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        be.dp_init(rank, world, ids[0])
+
+    net = zn.Network(be, zn.Precision.BF16_TC)
+    for i, ((a, b), act) in enumerate(zip(DIMS, ACTS)):
+        net.addDense(a, b, act)
+        net.setWeights(i, layer_weights(i), np.zeros(b, np.float32))
+    net.setOptimizer(zn.Adam(beta1=0.9, beta2=0.999, eps=1e-8))
+    if world > 1:
+        net.setDataParallel(GLOBAL_BATCH)
+
+    lo, hi = zn.Backend.distributeWorkload(GLOBAL_BATCH, world, rank)
+    rows = hi - lo
+    hx = be.host_alloc((rows, DIMS[0][0]))
+    ht = be.host_alloc((rows, DIMS[-1][1]))
+    fill_rows(hx, 0, lo)
+    fill_rows(ht, 1, lo)
+    dx, dt = be.tensor(hx), be.tensor(ht)
+
+    sampler = ClockSampler(local)
+    loss = zn.Loss.mse
+
+    # ---- leg 1: inputs resident in HBM
+    for _ in range(args.warmup):
+        net.trainStep(dx, dt, LR, loss, rows=rows)
+    barrier()
+    be.endCommandBatch()
+    sampler.start()
+    be.profile(True)
+    be.profile_reset()
+    launches0 = be.launch_count()
+    be.timer_start()
+    last_loss = None
+    for _ in range(args.steps):
+        last_loss = net.trainStep(dx, dt, LR, loss, rows=rows)
+    ms_total = be.timer_stop()
+    barrier()
+    launches = be.launch_count() - launches0
+    prof = {name: be.profile_get(fam) for name, fam in
+            [("gemm", 0), ("loss", 2), ("bias_reduce", 3), ("grad_norm", 4), ("optimizer", 5), ("convert", 6)]}
+    be.profile(False)
+    ms_total = max_over_ranks(ms_total)
+    ms_per_step = ms_total / args.steps
+    value = GLOBAL_BATCH / (ms_per_step / 1e3)
+
+    # ---- leg 2: end to end from pinned host memory, two steps in flight
+    e2e_warm = max(1, min(2, args.warmup))
+    for _ in range(e2e_warm):
+        net.submitStep(hx, ht, rows, LR, loss)
+        net.waitStep()
+    barrier()
+    t0 = time.perf_counter()
+    net.submitStep(hx, ht, rows, LR, loss)
+    for _ in range(args.steps - 1):
+        net.submitStep(hx, ht, rows, LR, loss)
+        net.waitStep()
+    e2e_loss = net.waitStep()
+    be.endCommandBatch()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    sampler.stop_flag = True
+    if sampler.is_alive():
+        sampler.join(timeout=2)
+    e2e_value = GLOBAL_BATCH * args.steps / e2e_s
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    g = prof["gemm"]
+    achieved = g["flops"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else 0.0
+    peak = peaks["bf16_sustained"]
+    line = {
+        "metric": "train_samples_per_sec", "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "step_tflops": FLOP_PER_SAMPLE * value / 1e12 / world,
+        "step_frac_of_bf16_peak": {"per_gpu_tflops": FLOP_PER_SAMPLE * value / 1e12 / world,
+                                   "of_measured_sustained": FLOP_PER_SAMPLE * value / 1e12 / world / peaks["bf16_sustained"],
+                                   "of_measured_burst": FLOP_PER_SAMPLE * value / 1e12 / world / peaks["bf16_burst"],
+                                   "of_datasheet_2250": FLOP_PER_SAMPLE * value / 1e12 / world / 2250.0},
+        "roofline": {"kernel": "gemm_tc_kernel<bf16> (tcgen05, 12 launches per step: NN, TN, NT per layer)",
+                     "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak if peak else None, "peak_source": f"{peaks['source']}, sustained bf16",
+                     "launches": g["launches"], "avg_launch_ms": g["ms"] / max(1, g["launches"]), "traffic": None},
+        "kernel_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
+        "hbm_kernels": {k: {"achieved_gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] > 0 else None,
+                            "frac_of_measured_hbm": (v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm"]) if v["ms"] > 0 else None}
+                        for k, v in prof.items() if k != "gemm"},
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(hx.nbytes + ht.nbytes) * world,
+                "d2h_bytes_per_step": 12 * world, "ms_per_step": 1e3 * e2e_s / args.steps,
+                "how": "zn_net_submit_step / zn_net_wait_step from pinned host buffers, two steps in flight"},
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(),
+        "loss": {"resident_last": last_loss, "e2e_last": e2e_loss},
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+def run_gemm_sweep(args):
+    """BASELINE configs[4]: standalone Dense GEMMs, NN/NT/TN, fused bias+ReLU on NN, operands N(0,1) seed 4.
+    Not the headline line: prints one JSON line per (size, orientation, precision) for the results table and is
+    the small case the ncu captures run."""
+    import zigneuron_b200 as zn
+    be = zn.Backend(0)
+    peaks = measured_peaks()
+    sizes = [tuple(int(v) for v in s.split("x")) for s in args.sizes.split(",")]
+    precs = {"bf16": zn.Precision.BF16_TC, "tf32": zn.Precision.TF32_TC, "fp32": zn.Precision.FP32_SIMT}
+    rng = np.random.default_rng(4)
+    for (m, n, k) in sizes:
+        a = be.tensor(rng.standard_normal(m * k, dtype=np.float32))
+        b = be.tensor(rng.standard_normal(k * n, dtype=np.float32))
+        bias = be.tensor(rng.uniform(-0.1, 0.1, n).astype(np.float32))
+        c = be.tensor(m * n)
+        for pname in args.precisions.split(","):
+            be.set_precision(precs[pname])
+            fam = 1 if pname == "fp32" else 0
+            calls = {"NN+bias+relu": lambda: be.matMulBiasRelu(a, b, bias, c, m, n, k),
+                     "NT": lambda: be.matMulTransposeB(a, b, c, m, n, k), "TN": lambda: be.matMulTransposeA(a, b, c, m, n, k)}
+            for oname, call in calls.items():
+                for _ in range(args.warmup):
+                    call()
+                be.endCommandBatch()
+                be.profile(True)
+                be.profile_reset()
+                for _ in range(args.steps):
+                    call()
+                p = be.profile_get(fam)
+                be.profile(False)
+                tf = p["flops"] / (p["ms"] * 1e-3) / 1e12
+                peak = peaks["bf16_burst"] if pname == "bf16" else None
+                print(json.dumps({"workload": "gemm_sweep", "mnk": [m, n, k], "orient": oname, "precision": pname,
+                                  "ms": p["ms"] / p["launches"], "tflops": tf,
+                                  "frac_of_measured_bf16_burst": tf / peak if peak else None}), flush=True)
+        for t in (a, b, bias, c):
+            t.free()
+    be.deinit()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="wide_mlp_dp", choices=["wide_mlp_dp", "gemm_sweep"])
+    ap.add_argument("--sizes", default="1024x1024x1024,4096x4096x4096,8192x8192x8192,65536x512x512")
+    ap.add_argument("--precisions", default="bf16,tf32,fp32")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.workload == "gemm_sweep":
+        run_gemm_sweep(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

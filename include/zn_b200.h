@@ -234,6 +234,10 @@ ZN_API zn_status zn_profile_reset(zn_ctx *ctx);
  * flops and algorithmic bytes of that family (synchronizes the stream). */
 ZN_API zn_status zn_profile_get(zn_ctx *ctx, zn_prof_family family, double *ms, uint64_t *launches,
                                 double *flops, double *bytes);
+/* CUDA-event stopwatch on the context's compute stream: stop waits for the stream and returns the
+ * device time between the two records. */
+ZN_API zn_status zn_timer_start(zn_ctx *ctx);
+ZN_API zn_status zn_timer_stop(zn_ctx *ctx, float *ms_out);
 /* Kernels this library launched on the context since creation. */
 ZN_API zn_status zn_launch_count(zn_ctx *ctx, uint64_t *out);
 

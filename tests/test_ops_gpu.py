@@ -124,7 +124,7 @@ def test_matmul_bias_act(be, prec, act):
     batch, n, k = 200, 96, 72
     rng = np.random.default_rng(4)
     a = rng.standard_normal((batch, k)).astype(np.float32)
-    w = rng.standard_normal((k, n)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)     # pre-activations of order 1
     bias = rng.uniform(-0.1, 0.1, n).astype(np.float32)
     want = zo.activation_forward(getattr(zo, act.upper()), zo.add_bias(zo.matmul(a, w, batch, n, k), bias))
     be.set_precision(prec)
@@ -209,7 +209,7 @@ def test_losses(be):
         exact = float(np.mean((o.astype(np.float64) - tm) ** 2))
         assert abs(got - exact) <= 1e-6 * exact
         # the oracle's single running f32 sum loses digits on long inputs; allow for ITS error there
-        assert abs(got - zo.loss_forward(zo.MSE, o, tm, rows, cols)) <= (1e-5 if rows * cols <= 200000 else 5e-4) * exact
+        assert abs(got - zo.loss_forward(zo.MSE, o, tm, rows, cols)) <= (1e-5 if rows * cols <= 50000 else 5e-3) * exact
         be.lossBackward(zn.Loss.cross_entropy_logits, o, t, g, rows)
         assert_close(g, zo.loss_backward(zo.CE_LOGITS, o, t, rows, cols), 1e-5, f"ce grad {rows}x{cols}")
         got = be.lossForward(zn.Loss.cross_entropy_logits, o, t, rows)

@@ -50,3 +50,33 @@ def iris_style(seed=0):
     for c in range(3):
         t[50 * c:50 * (c + 1), c] = 1.0
     return x, t
+
+
+def emulate_bf16_mse_step(x, t, Ws, bs, acts):
+    """What a CORRECT bf16-operand / fp32-accumulate implementation of one MSE training step computes:
+    float64 arithmetic with a bfloat16 rounding at every point where the GPU path stores an operand
+    (input, weight copies, hidden activations, every gradient block).  Separates the kernel's own error
+    from the rounding the precision mode implies.  Returns (loss, [gW], [gb])."""
+    rb = round_bf16
+    L = len(Ws)
+    h = [rb(x)]
+    for i in range(L):
+        z = h[-1].astype(np.float64) @ rb(Ws[i]).astype(np.float64) + bs[i]
+        if acts[i] == "relu":
+            z = np.maximum(z, 0)
+        z = z.astype(np.float32)
+        h.append(rb(z) if i + 1 < L else z)          # the last output stays fp32
+    n = h[-1].size
+    d = h[-1].astype(np.float64) - t
+    loss = float((d ** 2).sum() / n)
+    g = rb((2 * (h[-1] - t) / np.float32(n)).astype(np.float32))
+    gWs, gbs = [None] * L, [None] * L
+    for i in range(L - 1, -1, -1):
+        gWs[i] = (h[i].astype(np.float64).T @ g.astype(np.float64)).astype(np.float32)
+        gbs[i] = g.astype(np.float64).sum(0).astype(np.float32)
+        if i > 0:
+            dx = g.astype(np.float64) @ rb(Ws[i]).astype(np.float64).T
+            if acts[i - 1] == "relu":
+                dx = dx * (h[i] > 0)
+            g = rb(dx.astype(np.float32))
+    return loss, gWs, gbs

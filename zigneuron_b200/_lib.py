@@ -27,7 +27,7 @@ class ZnError(RuntimeError):
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m zigneuron_b200.build` "
+        f"{LIB_PATH} is missing: build it with `python zigneuron_b200/build.py` "
         "(there is no CPU implementation to fall back to)")
 
 lib = C.CDLL(LIB_PATH)
@@ -91,6 +91,8 @@ SIGNATURES = {
     "zn_profile_enable": (i32, [vp, i32]),
     "zn_profile_reset": (i32, [vp]),
     "zn_profile_get": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "zn_timer_start": (i32, [vp]),
+    "zn_timer_stop": (i32, [vp, pf]),
     "zn_launch_count": (i32, [vp, C.POINTER(u64)]),
 }
 

@@ -205,6 +205,23 @@ class Backend:
         self._ck(lib.zn_profile_get(self.handle, int(family), C.byref(ms), C.byref(n), C.byref(fl), C.byref(by)))
         return {"ms": ms.value, "launches": n.value, "flops": fl.value, "bytes": by.value}
 
+    def timer_start(self):
+        self._ck(lib.zn_timer_start(self.handle))
+
+    def timer_stop(self):
+        ms = C.c_float()
+        self._ck(lib.zn_timer_stop(self.handle, C.byref(ms)))
+        return ms.value
+
+    def host_alloc(self, shape):
+        """Pinned host memory as a float32 numpy array (for the pipelined step's inputs)."""
+        count = int(np.prod(shape))
+        p = C.c_void_p()
+        self._ck(lib.zn_host_alloc(self.handle, count, C.byref(p)))
+        buf = (C.c_float * count).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=np.float32).reshape(shape)
+        return arr
+
     def launch_count(self):
         n = C.c_uint64()
         self._ck(lib.zn_launch_count(self.handle, C.byref(n)))

@@ -1,7 +1,7 @@
 """Builds libzn_b200.so in-tree from csrc/*.cu with nvcc for sm_100a.
 
-    python -m zigneuron_b200.build        # incremental
-    python -m zigneuron_b200.build -f     # from scratch
+    python zigneuron_b200/build.py        # incremental (run by path: importing the package needs the built library)
+    python zigneuron_b200/build.py -f     # from scratch
 """
 import os
 import subprocess

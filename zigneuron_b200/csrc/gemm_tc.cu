@@ -147,15 +147,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
-// lbo / sbo in bytes.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor, descriptor version 1.  layout_type 2 = 128-byte swizzle on 16-byte
+// units; 1 = 128-byte swizzle on 32-byte units, the only swizzled layout the tensor cores accept for an
+// MN-major operand of a 32-bit type (tf32).  lbo / sbo in bytes.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout_type = 2) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFF);
     d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
     d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)layout_type << 61;
     return d;
 }
 
@@ -269,10 +270,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             // Byte strides of the canonical 128B-swizzle layouts:
             //   K-major : 8-row groups 1024 B apart (SBO); LBO unused.  k advances 32 B inside the row.
-            //   MN-major: 8-row (k) groups 1024 B apart (SBO); 128-byte MN chunks BK*128 B apart (LBO).
+            //   MN-major: 8-row (k) groups 1024 B apart (SBO) -- 4-row groups, 512 B, in the 32-byte-unit
+            //             swizzle tf32 needs; 128-byte MN chunks BK*128 B apart (LBO).
             //             k advances by whole rows: UMMA_K rows * 128 B.
             const uint32_t a_lbo = p.a_mn ? p.mn_lbo : 16, b_lbo = p.b_mn ? p.mn_lbo : 16;
             const uint32_t a_sbo = p.a_mn ? p.mn_sbo : 1024, b_sbo = p.b_mn ? p.mn_sbo : 1024;
+            const uint32_t a_lt = (TF32 && p.a_mn) ? 1u : 2u, b_lt = (TF32 && p.b_mn) ? 1u : 2u;
             const uint32_t a_kstep = p.a_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
             const uint32_t b_kstep = p.b_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
             int it = 0;
@@ -288,8 +291,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
-                        const uint64_t ad = make_desc(sa + ks * a_kstep, a_lbo, a_sbo);
-                        const uint64_t bd = make_desc(sb + ks * b_kstep, b_lbo, b_sbo);
+                        const uint64_t ad = make_desc(sa + ks * a_kstep, a_lbo, a_sbo, a_lt);
+                        const uint64_t bd = make_desc(sb + ks * b_kstep, b_lbo, b_sbo, b_lt);
                         tc_mma<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty_bar(s));          // frees the stage when these MMAs have read it
@@ -453,13 +456,13 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// 2-D row-major tensor [outer][inner], row pitch ld elements; box {box_inner, box_outer}; 128B swizzle;
-// out-of-bounds elements read as zero.
+// 2-D row-major tensor [outer][inner], row pitch ld elements; box {box_inner, box_outer}; 128B swizzle
+// (on 32-byte units when swizzle_32b_units, to match descriptor layout type 1); out-of-bounds reads zero.
 zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int64_t inner, int64_t outer, int64_t ld,
-                    int box_inner, int box_outer) {
+                    int box_inner, int box_outer, bool swizzle_32b_units) {
     char key[160];
-    snprintf(key, sizeof key, "%p|%d|%lld|%lld|%lld|%d|%d", ptr, es, (long long)inner, (long long)outer,
-             (long long)ld, box_inner, box_outer);
+    snprintf(key, sizeof key, "%p|%d|%lld|%lld|%lld|%d|%d|%d", ptr, es, (long long)inner, (long long)outer,
+             (long long)ld, box_inner, box_outer, (int)swizzle_32b_units);
     auto it = ctx->tmap_cache.find(key);
     if (it != ctx->tmap_cache.end()) {
         memcpy(out, it->second.data(), sizeof(CUtensorMap));
@@ -475,7 +478,8 @@ zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int6
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     CUresult r = enc(out, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return zn_fail(ctx, ZN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
     if (ctx->tmap_cache.size() > 4096) ctx->tmap_cache.clear();
     std::vector<uint8_t> bytes(sizeof(CUtensorMap));
@@ -504,10 +508,11 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     }
 
     CUtensorMap tmA, tmB;
-    if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM));      // [m][k]: inner k
-    else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk));            // [k][m]: inner m
-    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, BN));      // [n][k]: inner k
-    else ZN_TRY(make_tmap(ctx, &tmB, es, b, n, k, ldb, ch, bk));            // [k][n]: inner n
+    const bool tf32 = elem_type != 0;
+    if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM, false));     // [m][k]: inner k
+    else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk, tf32));            // [k][m]: inner m
+    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, BN, false));     // [n][k]: inner k
+    else ZN_TRY(make_tmap(ctx, &tmB, es, b, n, k, ldb, ch, bk, tf32));            // [k][n]: inner n
 
     TcParams p;
     p.M = (int)m; p.N = (int)n; p.K = (int)k;
@@ -520,7 +525,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
               ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     p.mn_lbo = (uint32_t)(bk * ROW_BYTES);
-    p.mn_sbo = 1024;
+    p.mn_sbo = tf32 ? 512 : 1024;
     if (const char *dbg = getenv("ZN_TC_MN_STRIDES")) {   // diagnostic override "lbo,sbo" in bytes
         unsigned l = 0, sb = 0;
         if (sscanf(dbg, "%u,%u", &l, &sb) == 2) { p.mn_lbo = l; p.mn_sbo = sb; }

@@ -187,7 +187,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     float *loss_slot = last.grads + last.blk;
     int cur = 0;
     ZN_TRY(zn_k_loss(ctx, loss, final_output(n), (int64_t)out_cols, t_dev, n->gwork[cur], n->bf16, n->lds[L],
-                     (int64_t)rows, (int64_t)out_cols, (float)(total_rows * out_cols), loss_slot));
+                     (int64_t)rows, (int64_t)out_cols, (float)(total_rows * out_cols), loss_slot, exact));
     if (last.act != ZN_ACT_LINEAR)   // Dense.backward applies the derivative of every layer, the last included
         ZN_TRY(zn_k_act_backward_t(ctx, last.act, n->acts[L], n->lds[L], n->gwork[cur], n->lds[L], n->bf16,
                                    (int64_t)rows, (int64_t)out_cols));
@@ -241,7 +241,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         segs.push_back({n->layers[i].grads, n->layers[i].in * n->layers[i].out});
         segs.push_back({n->layers[i].grads + n->layers[i].b_off, n->layers[i].out});
     }
-    ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars));
+    ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars, exact));
 
     // optimizer per layer (src/network.zig:541-549)
     for (size_t i = 0; i < L; ++i) {

@@ -211,7 +211,7 @@ extern "C" zn_status zn_loss_forward(zn_ctx *ctx, zn_loss loss, const float *out
     ZN_TRY(resolve(ctx, 1, target, rows * cols, true, &T));
     ZN_TRY(stage_reserve(ctx, 3, 16));
     ZN_TRY(zn_k_loss(ctx, loss, O.dev, (int64_t)cols, T.dev, nullptr, false, 0, (int64_t)rows, (int64_t)cols,
-                     (float)(rows * cols), ctx->stage[3]));
+                     (float)(rows * cols), ctx->stage[3], ctx->precision == ZN_FP32_EXACT));
     ZN_CUDA(ctx, cudaMemcpyAsync(ctx->pinned_scalar, ctx->stage[3], sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     const float sum = ctx->pinned_scalar[0];
@@ -230,7 +230,7 @@ extern "C" zn_status zn_loss_backward(zn_ctx *ctx, zn_loss loss, const float *ou
     ZN_TRY(resolve(ctx, 2, grad_out, rows * cols, false, &G));
     ZN_TRY(stage_reserve(ctx, 3, 16));
     ZN_TRY(zn_k_loss(ctx, loss, O.dev, (int64_t)cols, T.dev, G.dev, false, (int64_t)cols, (int64_t)rows, (int64_t)cols,
-                     (float)(rows * cols), ctx->stage[3]));
+                     (float)(rows * cols), ctx->stage[3], ctx->precision == ZN_FP32_EXACT));
     return finish(ctx, &G, O.host || T.host || G.host);
 }
 
@@ -308,7 +308,7 @@ extern "C" zn_status zn_clip_grad_norm(zn_ctx *ctx, float *const *grads, const s
             off += (counts[i] + 3) / 4 * 4;
         }
     }
-    ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)tensor_count, ctx->stage[3]));
+    ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)tensor_count, ctx->stage[3], ctx->precision == ZN_FP32_EXACT));
     for (size_t i = 0; i < tensor_count; ++i) ZN_TRY(zn_k_scale(ctx, dptr[i], counts[i], ctx->stage[3] + 1));
     if (!dev)
         for (size_t i = 0; i < tensor_count; ++i)

@@ -80,6 +80,29 @@ __global__ void norm_final_kernel(const float *__restrict__ partial, int n, floa
     }
 }
 
+// The reference's own order: one running f32 sum over every tensor in turn (src/network.zig:513-521).
+// One thread; used only by the FP32_EXACT mode, where matching the reference's rounding matters more
+// than speed.
+__global__ void norm_exact_kernel(const __grid_constant__ SegTable tab, float *__restrict__ out) {
+    float total = 0.f;
+    for (int s = 0; s < tab.nseg; ++s) {
+        const float *p = tab.ptr[s];
+        const unsigned long long n = tab.count[s];
+        unsigned long long i = 0;
+        for (; i + 4 <= n; i += 4) {
+            const float a = p[i], b = p[i + 1], c = p[i + 2], d = p[i + 3];
+            total = __fadd_rn(total, __fmul_rn(a, a));
+            total = __fadd_rn(total, __fmul_rn(b, b));
+            total = __fadd_rn(total, __fmul_rn(c, c));
+            total = __fadd_rn(total, __fmul_rn(d, d));
+        }
+        for (; i < n; ++i) total = __fadd_rn(total, __fmul_rn(p[i], p[i]));
+    }
+    total = sqrtf(total);
+    out[0] = total;
+    out[1] = total > 1.0f ? __fdiv_rn(1.0f, __fadd_rn(total, 1e-6f)) : 1.0f;
+}
+
 __global__ void scale_kernel(float *p, size_t n, const float *factor) {
     const float f = *factor;
     if (f == 1.0f) return;
@@ -153,7 +176,7 @@ int grid_for(zn_ctx *ctx, size_t n) {
 
 }   // namespace
 
-zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev) {
+zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev, bool exact) {
     if (nseg <= 0 || nseg > MAX_SEGS) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "grad norm: 1..%d tensors supported", MAX_SEGS);
     SegTable tab;
     int blocks = 0;
@@ -168,6 +191,12 @@ zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_
     tab.first_block[nseg] = blocks;
     tab.nseg = nseg;
     if (blocks == 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "grad norm: empty tensors");
+    if (exact) {
+        zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 1);
+        norm_exact_kernel<<<1, 1, 0, ctx->stream>>>(tab, norm_factor_dev);
+        ZN_CUDA(ctx, cudaGetLastError());
+        return ZN_OK;
+    }
     ZN_TRY(zn_scratch_reserve(ctx, (size_t)blocks));
     zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 2);
     sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch);

@@ -244,7 +244,8 @@ __global__ void mse_kernel(const float *__restrict__ out, int64_t ld_o, const fl
 // -(l[target] - (log(sum) + max)) with target = first column whose t > 0.5.
 template <typename T>
 __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const float *__restrict__ target,
-                          T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float *__restrict__ partial) {
+                          T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float *__restrict__ partial,
+                          int exact) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     float loss_acc = 0.f;
     for (int64_t r = (int64_t)blockIdx.x * wpb + w; r < rows; r += (int64_t)gridDim.x * wpb) {
@@ -260,6 +261,10 @@ __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const 
             if (t[c] > 0.5f && c < first) first = c;
         }
         se = warp_sum(se);
+        if (exact) {   // the reference's order: one running sum over the columns (src/loss.zig:243-247)
+            se = 0.f;
+            for (int64_t c = 0; c < cols; ++c) se = __fadd_rn(se, expf(__fsub_rn(l[c], mx)));
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
         if (grad) {
@@ -271,6 +276,32 @@ __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const 
     }
     loss_acc = block_sum(loss_acc);
     if (threadIdx.x == 0) partial[blockIdx.x] = loss_acc;
+}
+
+// FP32_EXACT mode: the loss SUM in the reference's order.  MSE: one running f32 sum of (o-t)^2 over all
+// elements (src/loss.zig:93-101).  CE: row losses added row by row (kernels/loss.cu:175-213).
+__global__ void loss_sum_exact_kernel(int loss, const float *__restrict__ out, int64_t ld_o, const float *__restrict__ target,
+                                      int64_t rows, int64_t cols, float *__restrict__ result) {
+    float total = 0.f;
+    for (int64_t r = 0; r < rows; ++r) {
+        const float *o = out + r * ld_o, *t = target + r * cols;
+        if (loss == ZN_LOSS_MSE) {
+            for (int64_t c = 0; c < cols; ++c) {
+                const float d = __fsub_rn(o[c], t[c]);
+                total = __fadd_rn(total, __fmul_rn(d, d));
+            }
+        } else {
+            float mx = o[0];
+            for (int64_t c = 1; c < cols; ++c) if (o[c] > mx) mx = o[c];
+            float se = 0.f;
+            for (int64_t c = 0; c < cols; ++c) se = __fadd_rn(se, expf(__fsub_rn(o[c], mx)));
+            const float lse = __fadd_rn(logf(se), mx);
+            float l = 0.f;
+            for (int64_t c = 0; c < cols; ++c) if (t[c] > 0.5f) { l = -(__fsub_rn(o[c], lse)); break; }
+            total = __fadd_rn(total, l);
+        }
+    }
+    *result = total;
 }
 
 __global__ void sum_partials_kernel(const float *__restrict__ partial, int n, float *__restrict__ out) {
@@ -379,7 +410,7 @@ zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, 
 }
 
 zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const float *target, void *grad, bool grad_bf16,
-                    int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor, float *loss_sum_dev) {
+                    int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor, float *loss_sum_dev, bool exact) {
     if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
         return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path (mse and cross_entropy_logits are)", loss);
     const int64_t total = rows * cols;
@@ -395,11 +426,12 @@ zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const
             mse_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
     } else {
         if (grad_bf16)
-            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch);
+            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0);
         else
-            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch);
+            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0);
     }
-    sum_partials_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, grid, loss_sum_dev);
+    if (exact) loss_sum_exact_kernel<<<1, 1, 0, ctx->stream>>>(loss, out, ld_o, target, rows, cols, loss_sum_dev);
+    else sum_partials_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, grid, loss_sum_dev);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }

@@ -100,6 +100,8 @@ extern "C" void zn_ctx_destroy(zn_ctx *ctx) {
     for (auto &slot : ctx->prof)
         for (auto &p : slot.pending) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
     for (auto ev : ctx->event_pool) cudaEventDestroy(ev);
+    if (ctx->timer0) cudaEventDestroy(ctx->timer0);
+    if (ctx->timer1) cudaEventDestroy(ctx->timer1);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->pinned_scalar) cudaFreeHost(ctx->pinned_scalar);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -294,6 +296,25 @@ extern "C" zn_status zn_profile_get(zn_ctx *ctx, zn_prof_family family, double *
     if (flops) *flops = s.flops;
     if (bytes) *bytes = s.bytes;
     return ZN_OK;
+}
+
+extern "C" zn_status zn_timer_start(zn_ctx *ctx) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!ctx->timer0) {
+        ZN_CUDA(ctx, cudaEventCreate(&ctx->timer0));
+        ZN_CUDA(ctx, cudaEventCreate(&ctx->timer1));
+    }
+    ZN_CUDA(ctx, cudaEventRecord(ctx->timer0, ctx->stream));
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_timer_stop(zn_ctx *ctx, float *ms_out) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!ctx->timer0 || !ms_out) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "timer not started or null output");
+    ZN_CUDA(ctx, cudaEventRecord(ctx->timer1, ctx->stream));
+    ZN_CUDA(ctx, cudaEventSynchronize(ctx->timer1));
+    ZN_CUDA(ctx, cudaEventElapsedTime(ms_out, ctx->timer0, ctx->timer1));
+    return zn_check_device_status(ctx);
 }
 
 extern "C" zn_status zn_launch_count(zn_ctx *ctx, uint64_t *out) {

@@ -51,6 +51,7 @@ struct zn_ctx {
     bool profiling = false;
     zn_prof_slot prof[ZN_PROF_FAMILY_COUNT];
     std::vector<cudaEvent_t> event_pool;
+    cudaEvent_t timer0 = nullptr, timer1 = nullptr;
 
     zn_dp_state *dp = nullptr;
 };
@@ -126,11 +127,11 @@ zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, 
 // for MSE, row losses for CE); the caller divides.  mse_divisor is the n of 2(o-t)/n.
 zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const float *target, void *grad,
                     bool grad_bf16, int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor,
-                    float *loss_sum_dev);
+                    float *loss_sum_dev, bool exact = false);   // exact: sums in the reference's order, one thread
 
 struct zn_seg { const float *ptr; size_t count; };
 // norm_factor_dev[0] = sqrt(sum g^2), [1] = clip factor (1 when norm <= 1); extra_sq_dev optional.
-zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev);
+zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev, bool exact = false);
 zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev);
 
 struct zn_opt_args {
