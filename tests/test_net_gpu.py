@@ -105,7 +105,14 @@ def test_mlp_784_adam(be, prec, loss_tol, w_tol, steps):
         lg = gnet.trainStep(x, t, 1e-3, zn.Loss.cross_entropy_logits)
         lo = onet.train_step(x, t, B, 1e-3, zo.CE_LOGITS)
         assert abs(lg - lo) <= loss_tol * max(1.0, abs(lo)), (step, lg, lo)
-    compare_params(gnet, onet, w_tol, prec.name)
+    # L2 parity of the weights, plus the hard bound Adam itself implies: no weight can differ by more than
+    # what `steps` moves of size ~lr in opposite directions add up to.
+    for i in range(3):
+        W, b = gnet.getWeights(i)
+        oW, ob = onet.get_params(i)
+        assert rel_l2(W, oW) <= w_tol, (prec.name, i, rel_l2(W, oW))
+        assert np.abs(W - oW).max() <= 2.2 * steps * 1e-3
+        assert np.abs(b - ob).max() <= 2.2 * steps * 1e-3
 
 
 def test_clip_factor_deviation_is_the_oracles_sum(be):
@@ -154,9 +161,11 @@ def test_wide_mlp_mse_gradients(be, prec, tol):
         # A low-precision forward flips a fraction p of the relu masks, which alone moves the gradients of
         # earlier layers by about sqrt(p): the last layer meets 2e-2, deeper ones are bounded by 1e-1 here
         # and pinned against the rounding emulation below.
-        bound = tol if (not tensor_core or i == 3) else 1e-1
-        assert_close(gW, oW, bound, f"{prec.name} gW{i}")
-        assert_close(gb, ob, bound, f"{prec.name} gb{i}")
+        if not tensor_core or i == 3:
+            assert_close(gW, oW, tol, f"{prec.name} gW{i}")
+            assert_close(gb, ob, tol, f"{prec.name} gb{i}")
+        else:
+            assert rel_l2(gW, oW) <= 1e-1 and rel_l2(gb, ob) <= 1e-1, (prec.name, i, rel_l2(gW, oW), rel_l2(gb, ob))
     if prec == P.BF16_TC:
         el, eW, eb = emulate_bf16_mse_step(x, t, Ws, bs, acts)
         assert abs(lg - el) <= 1e-4 * el
