@@ -126,6 +126,18 @@ ZN_API zn_status zn_matmul_bias_act(zn_ctx *ctx, const float *a, const float *b,
 ZN_API zn_status zn_add_bias(zn_ctx *ctx, float *out, size_t out_len, const float *bias, size_t bias_len);
 /* Backend.accumulateBias, src/backend.zig:649-655 -> :706-713: grad_bias[i] += sum over rows of g[r][i]. */
 ZN_API zn_status zn_accumulate_bias(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g, size_t g_len);
+/* No counterpart in the reference.  The same accumulation as zn_accumulate_bias (fp32, blocked sums, the
+ * same order of additions) for callers that must not trigger a device allocation: programs whose own pool
+ * already owns all device memory, and loops that cannot take the device-wide stall of cudaMalloc/cudaFree.
+ * It calls no allocator: the per-split partial sums live in a fixed 4 MiB block (1,048,576 floats) that is
+ * part of the library image on every GPU that loads it.  Both pointers must be DEVICE pointers.  A problem
+ * whose partial sums do not fit (row splits x bias_len > 1,048,576; the split count shrinks as bias_len
+ * grows, so this means a bias_len of roughly a million or more) is rejected with ZN_ERR_INVALID_VALUE and a
+ * message giving the sizes.  The first call on
+ * each device looks up the block's device address; make that call before starting any stream capture.  All
+ * calls on a GPU share the block: calls that overlap in time on one GPU race and must be ordered by the
+ * caller; nothing in the block needs clearing between calls. */
+ZN_API zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g, size_t g_len);
 /* Backend.activationForward, src/backend.zig:367-386 (in == out allowed). */
 ZN_API zn_status zn_activation_forward(zn_ctx *ctx, zn_activation act, const float *in, float *out, size_t count);
 /* Backend.activationBackward, src/backend.zig:390-399 -> :2649-2669; `y` is the ACTIVATED output. */

@@ -57,6 +57,7 @@ SIGNATURES = {
     "zn_matmul_bias_act": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, i32]),
     "zn_add_bias": (i32, [vp, vp, sz, vp, sz]),
     "zn_accumulate_bias": (i32, [vp, vp, sz, vp, sz]),
+    "zn_accumulate_bias_noalloc": (i32, [vp, vp, sz, vp, sz]),
     "zn_activation_forward": (i32, [vp, i32, vp, vp, sz]),
     "zn_activation_backward": (i32, [vp, i32, vp, vp, vp, sz]),
     "zn_loss_forward": (i32, [vp, i32, vp, vp, sz, sz, pf]),

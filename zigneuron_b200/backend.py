@@ -155,6 +155,12 @@ class Backend:
         self._ck(lib.zn_accumulate_bias(self.handle, ptr(grad_bias), self._len(grad_bias), ptr(grad_after_act),
                                         self._len(grad_after_act)))
 
+    def accumulateBiasNoAlloc(self, grad_bias, grad_after_act):
+        """accumulateBias for callers that must not allocate device memory (device tensors only; the partial
+        sums live in a fixed block inside the library instead of the context's growable scratch)."""
+        self._ck(lib.zn_accumulate_bias_noalloc(self.handle, ptr(grad_bias), self._len(grad_bias), ptr(grad_after_act),
+                                                self._len(grad_after_act)))
+
     def activationForward(self, act, input, output):
         self._ck(lib.zn_activation_forward(self.handle, int(act), ptr(input), ptr(output), self._len(input)))
 

@@ -409,6 +409,83 @@ zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, 
     return ZN_OK;
 }
 
+// ---- bias-gradient accumulation that never allocates ------------------------------------------
+//
+// zn_accumulate_bias keeps its per-split partial sums in a scratch block that the context grows with
+// cudaMalloc when a larger problem arrives.  Some users of this library cannot afford that call: a host
+// program that has already handed every byte of device memory to its own pool (so cudaMalloc fails), or a
+// training loop that must not stall on the device-wide synchronisation cudaMalloc/cudaFree imply.  For them
+// the same two kernels run here with their partial sums in a fixed block that is part of the library image:
+// ZN_NOALLOC_SCRATCH_FLOATS floats (4 MiB) of global memory that every GPU loading the library holds until
+// the process exits.
+//
+// The block is shared by every call on a device and keeps whatever the previous call left in it.  Nothing
+// in it has to start at zero: the first kernel writes every slot (split, column) that the second one reads.
+// Two calls that run on the same GPU at the same time (different streams or contexts) would overwrite each
+// other's partial sums; callers must order them.
+constexpr size_t ZN_NOALLOC_SCRATCH_FLOATS = (size_t)1 << 20;
+static __device__ __align__(256) float zn_noalloc_scratch[ZN_NOALLOC_SCRATCH_FLOATS];
+
+// In host code `zn_noalloc_scratch` is only a stand-in for the symbol, not an address a kernel can use; the
+// device address is looked up once per device, with that device current, and cached here.
+static float *noalloc_scratch_address(zn_ctx *ctx, zn_status *status) {
+    static float *per_device[64] = {nullptr};
+    *status = ZN_OK;
+    if (ctx->device < 0 || ctx->device >= 64) {
+        *status = zn_fail(ctx, ZN_ERR_INVALID_DEVICE, "device index %d outside the supported range", ctx->device);
+        return nullptr;
+    }
+    if (!per_device[ctx->device]) {
+        float *p = nullptr;
+        cudaError_t e = cudaSetDevice(ctx->device);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&p, zn_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            *status = zn_cuda_status(ctx, e == cudaSuccess ? cudaErrorInvalidSymbol : e, "cudaGetSymbolAddress(zn_noalloc_scratch)");
+            return nullptr;
+        }
+        per_device[ctx->device] = p;
+    }
+    return per_device[ctx->device];
+}
+
+extern "C" zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g,
+                                                size_t g_len) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!grad_bias || !g) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "accumulate_bias_noalloc: null operand");
+    if (bias_len == 0 || g_len % bias_len != 0)
+        return zn_fail(ctx, ZN_ERR_SHAPE, "accumulate_bias_noalloc: gradient is not rows x bias_len");
+    if (g_len == 0) return ZN_OK;
+    if (!zn_is_device_ptr(grad_bias) || !zn_is_device_ptr(g))
+        return zn_fail(ctx, ZN_ERR_INVALID_VALUE,
+                       "accumulate_bias_noalloc: operands must be device pointers (staging host memory would allocate)");
+    const int64_t cols = (int64_t)bias_len, rows = (int64_t)(g_len / bias_len);
+    // same split of the rows as zn_accumulate_bias, so both entry points add in the same order
+    const int strip = 32 * 4;
+    const int strips = (int)((cols + strip - 1) / strip);
+    int64_t splits = ((int64_t)ctx->sm_count * 4 + strips - 1) / strips;
+    const int64_t max_splits = (rows + 63) / 64;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    if (splits > 65535) splits = 65535;
+    const int64_t rows_per = (rows + splits - 1) / splits;
+    splits = (rows + rows_per - 1) / rows_per;
+    const size_t need = (size_t)(splits * cols);
+    if (need > ZN_NOALLOC_SCRATCH_FLOATS)
+        return zn_fail(ctx, ZN_ERR_INVALID_VALUE,
+                       "accumulate_bias_noalloc: %zu rows x %zu columns needs %zu floats of scratch, the fixed block holds %zu; "
+                       "use zn_accumulate_bias or fewer columns",
+                       (size_t)rows, (size_t)cols, need, ZN_NOALLOC_SCRATCH_FLOATS);
+    zn_status st;
+    float *scratch = noalloc_scratch_address(ctx, &st);
+    if (!scratch) return st;
+    ctx->launches += 2;
+    dim3 grid((unsigned)strips, (unsigned)splits);
+    bias_reduce_partial_kernel<float, 4><<<grid, TPB, 0, ctx->stream>>>(g, cols, rows, cols, rows_per, scratch);
+    bias_reduce_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(scratch, cols, (int)splits, grad_bias, 1);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
 zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const float *target, void *grad, bool grad_bf16,
                     int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor, float *loss_sum_dev, bool exact) {
     if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
