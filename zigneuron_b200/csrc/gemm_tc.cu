@@ -2,7 +2,7 @@
 //
 // One persistent CTA per SM walks 128 x 256 output tiles.  Warp 0 feeds a
 // 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
-// no multicast); one thread of warp 1 issues tcgen05.mma (cta_group::1, M=128,
+// every CTA loads its own tiles); one thread of warp 1 issues tcgen05.mma (cta_group::1, M=128,
 // N=256) into one of two 256-column fp32 accumulators in tensor memory; warps
 // 2..5 drain the other accumulator with tcgen05.ld and apply the fused epilogue
 // (bias, activation, activation-derivative mask, accumulate, down-convert), so
