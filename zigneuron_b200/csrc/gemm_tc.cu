@@ -31,6 +31,7 @@ namespace {
 
 constexpr int BM = 128, BN = 256;
 constexpr int STAGES = 4;
+constexpr int TQ = 4;                               // depth of the tile-index ring inside a CTA
 constexpr int ROW_BYTES = 128;                    // one swizzle row
 constexpr int A_STAGE = BM * ROW_BYTES;           // 16 KiB
 constexpr int B_STAGE = BN * ROW_BYTES;           // 32 KiB
@@ -57,6 +58,9 @@ struct TcParams {
     long long ld_out_t;
     int accumulate;
     int *status;
+    // Dynamic tile scheduling: a CTA takes tile blockIdx.x first, then gridDim.x + atomicAdd(tile_counter).
+    // Each launch also clears the counter the NEXT launch on the stream will use.
+    unsigned int *tile_counter, *next_counter;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -197,13 +201,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
     const uint32_t bars = base + STAGES * STAGE_BYTES;
-    // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2]; then tmem ptr, abort flag
+    // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], sched_full[TQ],
+    // sched_empty[TQ]; then tmem ptr, abort flag, and the ring of tile indices the producer publishes
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    auto sfull_bar = [&](int q) { return bars + 8u * (2 * STAGES + 4 + q); };
+    auto sempty_bar = [&](int q) { return bars + 8u * (2 * STAGES + 4 + TQ + q); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4 + 2 * TQ));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *tile_ring = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -212,6 +220,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+        for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }   // MMA thread + 4 epilogue warps
+        if (blockIdx.x == 0) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -235,7 +245,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int q = 0;
+            uint32_t qphase = 0;
+            for (bool first = true; ok; first = false) {
+                // next tile: the CTA's own first, then whatever the grid has not started yet
+                int t = first ? (int)blockIdx.x : (int)(gridDim.x + atomicAdd(p.tile_counter, 1u));
+                if (t >= num_tiles) t = -1;
+                if (!mbar_wait(sempty_bar(q), qphase ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
+                tile_ring[q] = t;
+                mbar_arrive(sfull_bar(q));            // release: the MMA and epilogue warps read the slot after this
+                if (++q == TQ) { q = 0; qphase ^= 1u; }
+                if (t < 0) break;
                 int tm, tn;
                 tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
                 const int m0 = tm * BM, n0 = tn * BN;
@@ -278,8 +298,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t a_lt = (TF32 && p.a_mn) ? 1u : 2u, b_lt = (TF32 && p.b_mn) ? 1u : 2u;
             const uint32_t a_kstep = p.a_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
             const uint32_t b_kstep = p.b_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
-            int it = 0;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            int it = 0, q = 0;
+            uint32_t qphase = 0;
+            for (; ok; ++it) {
+                if (!mbar_wait(sfull_bar(q), qphase, abort_flag, p.status, 6)) { ok = false; break; }
+                const int t = tile_ring[q];
+                mbar_arrive(sempty_bar(q));
+                if (++q == TQ) { q = 0; qphase ^= 1u; }
+                if (t < 0) break;
                 const int buf = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
@@ -305,9 +331,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ================= epilogue: warps 2..5, TMEM lanes 32*(warp%4).. =================
         const int q = warp & 3;
         const bool t_bf16 = !TF32;
-        int it = 0;
+        int it = 0, sq = 0;
+        uint32_t sqphase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        for (; ok; ++it) {
+            if (!mbar_wait(sfull_bar(sq), sqphase, abort_flag, p.status, 7)) { ok = false; break; }
+            const int t = tile_ring[sq];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sempty_bar(sq));
+            if (++sq == TQ) { sq = 0; sqphase ^= 1u; }
+            if (t < 0) break;
             int tm, tn;
             tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
             const int buf = it & 1;
@@ -504,6 +537,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           SMEM_BYTES));
         ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        // Ask for the full 228 KB shared-memory split rather than the smallest one that fits this kernel:
+        // the ~30 KB left over let the small reduction and update kernels of the other lanes share the SM.
+        cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
         attr_set_mask |= dev_bit;
     }
 
@@ -534,6 +574,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.out_f32 = e.out_f32; p.ld_out_f32 = e.ld_out_f32; p.out_t = e.out_t; p.ld_out_t = e.ld_out_t;
     p.accumulate = e.accumulate;
     p.status = ctx->status_dev;
+    if (!ctx->tile_counters) {
+        ZN_CUDA(ctx, cudaMalloc((void **)&ctx->tile_counters, 2 * sizeof(unsigned int)));
+        ZN_CUDA(ctx, cudaMemsetAsync(ctx->tile_counters, 0, 2 * sizeof(unsigned int), ctx->stream));
+    }
+    p.tile_counter = ctx->tile_counters + (ctx->tile_counter_turn & 1);
+    p.next_counter = ctx->tile_counters + ((ctx->tile_counter_turn + 1) & 1);
+    ctx->tile_counter_turn += 1;
 
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);

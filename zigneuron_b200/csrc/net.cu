@@ -37,7 +37,9 @@ struct Layer {
     int opt = 0;                          // 0 sgd, 1 adam
     float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, wd = 0.f;
     size_t t = 0;
-    cudaEvent_t grads_ready = nullptr, reduced = nullptr;
+    // ordering between the lanes of a step (see step_dev)
+    cudaEvent_t g_ready = nullptr, bias_done = nullptr, grads_ready = nullptr, reduced = nullptr, updated = nullptr;
+    bool update_pending = false;          // `updated` has been recorded and not yet waited for by the host
 };
 
 struct Slot {                             // one in-flight pipelined step
@@ -64,6 +66,7 @@ struct zn_net {
     void *gwork[2] = {nullptr, nullptr};
     int64_t g_ld_max = 0;
     float *scalars = nullptr;             // device: [0] norm, [1] clip factor
+    double *sumsq = nullptr;              // device: per-layer sum of squared gradients (64 slots)
     Slot slots[2];
     int head = 0, inflight = 0;
     size_t global_rows = 0;               // > 0: data parallel
@@ -93,7 +96,7 @@ int64_t pitch_of(const zn_net *n, size_t width) { return n->tc ? round_up((int64
 zn_status ensure_rows(zn_net *n, size_t rows) {
     zn_ctx *ctx = n->ctx;
     if (rows <= n->cap_rows && n->acts.size() == n->layers.size() + 1) return ZN_OK;
-    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ZN_TRY(zn_sync_all_lanes(ctx));
     const size_t keep = rows > n->cap_rows ? rows : n->cap_rows;
     free_acts(n);
     const size_t L = n->layers.size();
@@ -164,6 +167,8 @@ zn_status forward_dev(zn_net *n, const float *x_dev, size_t rows) {
         }
         const void *w = l.w_op ? l.w_op : (const void *)l.params;
         const int64_t ldw = l.w_op ? l.ld_w : (int64_t)l.out;
+        // the previous step's update of this layer may still be running on the optimizer lane
+        if (l.update_pending) ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, l.updated, 0));
         ZN_TRY(net_gemm(n, 0, cur, n->lds[i], w, ldw, (int64_t)rows, (int64_t)l.out, (int64_t)l.in, ep));
         cur = n->acts[i + 1];
     }
@@ -174,11 +179,25 @@ float *final_output(zn_net *n) { return n->tc ? n->out_f32 : (float *)n->acts[n-
 
 // Everything of one training step after the inputs are on the device.  x_dev / t_dev fp32.
 // The loss SUM lands in the tail slot of the last layer's gradient block.
-zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t rows, float lr, int loss) {
+//
+// Lanes (streams) of one step, so that only the GEMMs and the loss sit on the critical path:
+//   main  forward GEMMs, loss, and per layer (last to first) gW GEMM and dX GEMM
+//   aux   per layer the column reduction G -> gb, as soon as G exists
+//   comm  per layer, once gW and gb exist: all-reduce over ranks (data parallel), then that layer's sum of
+//         squared gradients
+//   opt   once every layer is reduced: norm and clip factor, loss/norm read-back into loss_dst, then the
+//         update of every layer; `done` is recorded after the read-back, BEFORE the updates
+// The updates of step k therefore run under the forward GEMMs of step k+1: the forward GEMM of layer l
+// waits (on the device) for the update of layer l only.
+zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t rows, float lr, int loss, float *loss_dst,
+                   cudaEvent_t done) {
     zn_ctx *ctx = n->ctx;
     const size_t L = n->layers.size();
     const bool exact = n->prec == ZN_FP32_EXACT;
     const bool dp = n->global_rows > 0 && zn_dp_active(ctx);
+    cudaStream_t s_main = ctx->lanes[ZN_LANE_MAIN].stream, s_comm = ctx->lanes[ZN_LANE_COMM].stream;
+    cudaStream_t s_opt = ctx->lanes[ZN_LANE_OPT].stream, s_aux = ctx->lanes[ZN_LANE_AUX].stream;
+    s_main = ctx->stream;   // lane 0 is active here; its slot in lanes[] is only refreshed on a switch
     ZN_TRY(forward_dev(n, x_dev, rows));
 
     Layer &last = n->layers[L - 1];
@@ -197,8 +216,14 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         const void *g = n->gwork[cur];
         const int64_t ld_g = n->lds[idx + 1];
         const void *x_in = (idx == 0 && !n->tc) ? (const void *)x_dev : (const void *)n->acts[idx];
-        // gb = column sums of G   (accumulateBias into a cleared gb, src/layer.zig:459)
-        ZN_TRY(zn_k_bias_reduce(ctx, g, n->bf16, ld_g, (int64_t)rows, (int64_t)l.out, l.grads + l.b_off, false, exact));
+        // gb = column sums of G   (accumulateBias into a cleared gb, src/layer.zig:459), on the aux lane
+        ZN_CUDA(ctx, cudaEventRecord(l.g_ready, s_main));
+        ZN_CUDA(ctx, cudaStreamWaitEvent(s_aux, l.g_ready, 0));
+        {
+            zn_lane_guard lane(ctx, ZN_LANE_AUX);
+            ZN_TRY(zn_k_bias_reduce(ctx, g, n->bf16, ld_g, (int64_t)rows, (int64_t)l.out, l.grads + l.b_off, false, exact));
+        }
+        ZN_CUDA(ctx, cudaEventRecord(l.bias_done, s_aux));
         // gW = X^T . G           (matMulTransposeA, src/layer.zig:466)
         {
             zn_epilogue ep;
@@ -206,13 +231,19 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
             ep.ld_out_f32 = (int64_t)l.out;
             ZN_TRY(net_gemm(n, 1, x_in, n->lds[idx], g, ld_g, (int64_t)l.in, (int64_t)l.out, (int64_t)rows, ep));
         }
-        if (dp) {
-            // this layer's gradients are final: start summing them over ranks while earlier layers run
-            ZN_CUDA(ctx, cudaEventRecord(l.grads_ready, ctx->stream));
-            ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, l.grads_ready, 0));
-            ZN_TRY(zn_dp_allreduce(ctx, l.grads, l.blk + (idx + 1 == L ? 1 : 0), ctx->comm_stream));
-            ZN_CUDA(ctx, cudaEventRecord(l.reduced, ctx->comm_stream));
+        // this layer's gradients are final: sum them over ranks and square-sum them while earlier layers run
+        ZN_CUDA(ctx, cudaEventRecord(l.grads_ready, s_main));
+        ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.grads_ready, 0));
+        ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.bias_done, 0));
+        if (dp) ZN_TRY(zn_dp_allreduce(ctx, l.grads, l.blk + (idx + 1 == L ? 1 : 0), s_comm));
+        if (!exact) {
+            zn_lane_guard lane(ctx, ZN_LANE_COMM);
+            const zn_seg segs[2] = {{l.grads, l.in * l.out}, {l.grads + l.b_off, l.out}};
+            ZN_TRY(zn_k_sumsq(ctx, segs, 2, n->sumsq + idx));
         }
+        ZN_CUDA(ctx, cudaEventRecord(l.reduced, s_comm));
+        // G of the layer above lives in the block the next dX overwrites: its column sums must be done
+        if (idx + 1 < L) ZN_CUDA(ctx, cudaStreamWaitEvent(s_main, n->layers[idx + 1].bias_done, 0));
         // dX = G . W^T, masked by the previous layer's activation derivative (src/layer.zig:440-448)
         {
             zn_epilogue ep;
@@ -232,16 +263,27 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     n->last_input_grad = n->gwork[cur];
     n->last_rows = rows;
 
-    if (dp)
-        for (size_t i = 0; i < L; ++i) ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, n->layers[i].reduced, 0));
+    // ---- optimizer lane: everything below waits for all layers' reductions, not for the main stream
+    for (size_t i = 0; i < L; ++i) ZN_CUDA(ctx, cudaStreamWaitEvent(s_opt, n->layers[i].reduced, 0));
+    zn_lane_guard opt_lane(ctx, ZN_LANE_OPT);
 
     // global norm over every gradient tensor, weights then bias, layer by layer (src/network.zig:513-521)
-    std::vector<zn_seg> segs;
-    for (size_t i = 0; i < L; ++i) {
-        segs.push_back({n->layers[i].grads, n->layers[i].in * n->layers[i].out});
-        segs.push_back({n->layers[i].grads + n->layers[i].b_off, n->layers[i].out});
+    if (exact) {
+        std::vector<zn_seg> segs;
+        for (size_t i = 0; i < L; ++i) {
+            segs.push_back({n->layers[i].grads, n->layers[i].in * n->layers[i].out});
+            segs.push_back({n->layers[i].grads + n->layers[i].b_off, n->layers[i].out});
+        }
+        ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars, true));
+    } else {
+        ZN_TRY(zn_k_norm_combine(ctx, n->sumsq, (int)L, n->scalars));
     }
-    ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars, exact));
+    if (loss_dst) {
+        ZN_CUDA(ctx, cudaMemcpyAsync(loss_dst, loss_slot, sizeof(float), cudaMemcpyDefault, s_opt));
+        if (!zn_is_device_ptr(loss_dst))
+            ZN_CUDA(ctx, cudaMemcpyAsync(loss_dst + 1, n->scalars, 2 * sizeof(float), cudaMemcpyDeviceToHost, s_opt));
+    }
+    if (done) ZN_CUDA(ctx, cudaEventRecord(done, s_opt));
 
     // optimizer per layer (src/network.zig:541-549)
     for (size_t i = 0; i < L; ++i) {
@@ -263,6 +305,8 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         a.w = l.params + l.b_off; a.g = l.grads + l.b_off; a.count = l.out; a.shadow = nullptr;
         if (l.opt == 1) { a.m = l.m + l.b_off; a.v = l.v + l.b_off; a.w_clamp = 100.0f; ZN_TRY(zn_k_adam(ctx, a)); }
         else { a.w_clamp = 50.0f; ZN_TRY(zn_k_sgd(ctx, a, true)); }
+        ZN_CUDA(ctx, cudaEventRecord(l.updated, s_opt));
+        l.update_pending = true;
     }
     return ZN_OK;
 }
@@ -274,10 +318,20 @@ float loss_from_sum(const zn_net *n, float sum, size_t rows, int loss) {
     return total_rows > 1 ? sum / (float)total_rows : sum;
 }
 
-zn_status check_net(zn_net *n, bool need_layers) {
+// Entry checks.  Unless `keep_running`, the host also waits for everything the last step left running on the
+// side lanes (parameter updates), so that whatever the caller reads or replaces next is final.
+zn_status check_net(zn_net *n, bool need_layers, bool keep_running = false) {
     if (!n || !n->ctx) return ZN_ERR_NOT_INITIALIZED;
     if (need_layers && n->layers.empty()) return zn_fail(n->ctx, ZN_ERR_NOT_AVAILABLE, "network has no layers");
     cudaSetDevice(n->ctx->device);
+    if (!keep_running) {
+        bool pending = false;
+        for (Layer &l : n->layers) pending = pending || l.update_pending;
+        if (pending) {
+            ZN_TRY(zn_sync_all_lanes(n->ctx));
+            for (Layer &l : n->layers) l.update_pending = false;
+        }
+    }
     return ZN_OK;
 }
 
@@ -289,13 +343,13 @@ zn_status ensure_slot(zn_net *n, Slot &s, size_t x_floats, size_t t_floats) {
         ZN_CUDA(ctx, cudaHostAlloc((void **)&s.loss_host, 4 * sizeof(float), cudaHostAllocDefault));
     }
     if (s.x_cap < x_floats) {
-        ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        ZN_TRY(zn_sync_all_lanes(ctx));
         cudaFree(s.x); s.x = nullptr; s.x_cap = 0;
         ZN_CUDA(ctx, cudaMalloc((void **)&s.x, x_floats * sizeof(float)));
         s.x_cap = x_floats;
     }
     if (s.t_cap < t_floats) {
-        ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        ZN_TRY(zn_sync_all_lanes(ctx));
         cudaFree(s.t); s.t = nullptr; s.t_cap = 0;
         ZN_CUDA(ctx, cudaMalloc((void **)&s.t, t_floats * sizeof(float)));
         s.t_cap = t_floats;
@@ -323,8 +377,10 @@ extern "C" zn_status zn_net_create(zn_ctx *ctx, zn_precision precision, zn_net *
     n->tc = precision == ZN_TF32_TC || precision == ZN_BF16_TC;
     n->bf16 = precision == ZN_BF16_TC;
     cudaError_t e = cudaMalloc((void **)&n->scalars, 16 * sizeof(float));
-    if (e != cudaSuccess) { delete n; return zn_cuda_status(ctx, e, "cudaMalloc"); }
+    if (e == cudaSuccess) e = cudaMalloc((void **)&n->sumsq, 64 * sizeof(double));
+    if (e != cudaSuccess) { cudaFree(n->scalars); delete n; return zn_cuda_status(ctx, e, "cudaMalloc"); }
     cudaMemsetAsync(n->scalars, 0, 16 * sizeof(float), ctx->stream);
+    cudaMemsetAsync(n->sumsq, 0, 64 * sizeof(double), ctx->stream);
     *out = n;
     return ZN_OK;
 }
@@ -333,16 +389,16 @@ extern "C" void zn_net_destroy(zn_net *n) {
     if (!n) return;
     if (n->ctx) {
         cudaSetDevice(n->ctx->device);
-        cudaStreamSynchronize(n->ctx->stream);
+        zn_sync_all_lanes(n->ctx);
         cudaStreamSynchronize(n->ctx->copy_stream);
-        cudaStreamSynchronize(n->ctx->comm_stream);
     }
     free_acts(n);
     for (Layer &l : n->layers) {
         cudaFree(l.params); cudaFree(l.grads); cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
-        if (l.grads_ready) cudaEventDestroy(l.grads_ready);
-        if (l.reduced) cudaEventDestroy(l.reduced);
+        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated})
+            if (ev) cudaEventDestroy(ev);
     }
+    cudaFree(n->sumsq);
     for (Slot &s : n->slots) {
         cudaFree(s.x); cudaFree(s.t);
         if (s.copied) cudaEventDestroy(s.copied);
@@ -364,6 +420,7 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     if (!n->layers.empty() && n->layers.back().out != input_size)
         return zn_fail(ctx, ZN_ERR_SHAPE, "layer input %zu does not match previous output %zu", input_size, n->layers.back().out);
     if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "steps in flight");
+    if (n->layers.size() >= 16) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "at most 16 Dense layers per network");
     Layer l;
     l.in = input_size; l.out = output_size; l.act = act;
     l.b_off = (size_t)round_up((int64_t)(input_size * output_size), 4);
@@ -374,8 +431,8 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     ZN_CUDA(ctx, cudaMalloc((void **)&l.grads, alloc));
     ZN_CUDA(ctx, cudaMemsetAsync(l.params, 0, alloc, ctx->stream));
     ZN_CUDA(ctx, cudaMemsetAsync(l.grads, 0, alloc, ctx->stream));
-    ZN_CUDA(ctx, cudaEventCreateWithFlags(&l.grads_ready, cudaEventDisableTiming));
-    ZN_CUDA(ctx, cudaEventCreateWithFlags(&l.reduced, cudaEventDisableTiming));
+    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated})
+        ZN_CUDA(ctx, cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
     if (n->tc) {
         const bool direct = !n->bf16 && output_size % 4 == 0;   // tf32 can read W itself when its pitch is TMA-legal
         if (!direct) {
@@ -523,7 +580,7 @@ extern "C" zn_status zn_net_forward(zn_net *n, const float *input, size_t rows, 
 
 extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const float *target, size_t rows, float lr,
                                        zn_loss loss, float *loss_out) {
-    ZN_TRY(check_net(n, true));
+    ZN_TRY(check_net(n, true, true));
     zn_ctx *ctx = n->ctx;
     if (!input || !target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "train_step: null operand");
     if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "train_step: zero rows");
@@ -542,11 +599,10 @@ extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const floa
         ZN_CUDA(ctx, cudaMemcpyAsync(s.t, target, rows * out * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
         t_dev = s.t;
     }
-    ZN_TRY(step_dev(n, x_dev, t_dev, rows, lr, (int)loss));
-    Layer &last = n->layers.back();
-    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host, last.grads + last.blk, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host + 1, n->scalars, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ZN_TRY(step_dev(n, x_dev, t_dev, rows, lr, (int)loss, s.loss_host, s.done));
+    // The loss and the norm are final once every layer is reduced; the parameter updates keep running on
+    // the optimizer lane and the next step (or any getter) orders itself after them.
+    ZN_CUDA(ctx, cudaEventSynchronize(s.done));
     n->last_norm = s.loss_host[1];
     n->last_factor = s.loss_host[2];
     if (loss_out) *loss_out = loss_from_sum(n, s.loss_host[0], rows, (int)loss);
@@ -555,7 +611,7 @@ extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const floa
 
 extern "C" zn_status zn_net_submit_step(zn_net *n, const float *host_input, const float *host_target, size_t rows,
                                         float lr, zn_loss loss) {
-    ZN_TRY(check_net(n, true));
+    ZN_TRY(check_net(n, true, true));
     zn_ctx *ctx = n->ctx;
     if (!host_input || !host_target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "submit_step: null operand");
     if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "submit_step: zero rows");
@@ -573,18 +629,14 @@ extern "C" zn_status zn_net_submit_step(zn_net *n, const float *host_input, cons
     ZN_CUDA(ctx, cudaMemcpyAsync(s.t, host_target, rows * out * sizeof(float), cudaMemcpyHostToDevice, ctx->copy_stream));
     ZN_CUDA(ctx, cudaEventRecord(s.copied, ctx->copy_stream));
     ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, s.copied, 0));
-    ZN_TRY(step_dev(n, s.x, s.t, rows, lr, (int)loss));
-    Layer &last = n->layers.back();
-    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host, last.grads + last.blk, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-    ZN_CUDA(ctx, cudaMemcpyAsync(s.loss_host + 1, n->scalars, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-    ZN_CUDA(ctx, cudaEventRecord(s.done, ctx->stream));
+    ZN_TRY(step_dev(n, s.x, s.t, rows, lr, (int)loss, s.loss_host, s.done));
     s.rows = rows; s.loss = (int)loss; s.busy = true;
     n->inflight += 1;
     return ZN_OK;
 }
 
 extern "C" zn_status zn_net_wait_step(zn_net *n, float *loss_out) {
-    ZN_TRY(check_net(n, true));
+    ZN_TRY(check_net(n, true, true));
     zn_ctx *ctx = n->ctx;
     if (n->inflight == 0) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "no step in flight");
     Slot &s = n->slots[n->head];
@@ -615,24 +667,21 @@ extern "C" zn_status zn_net_train(zn_net *n, const float *inputs, const float *t
     float *losses_dev = nullptr;
     ZN_CUDA(ctx, cudaMalloc((void **)&losses_dev, samples * sizeof(float)));
     std::vector<float> losses(samples);
-    Layer &last = n->layers.back();
     zn_status st = ZN_OK;
     for (size_t e = 0; e < epochs && st == ZN_OK; ++e) {
         // one trainStep per sample, in order (src/network.zig:613-614)
         for (size_t i = 0; i < samples && st == ZN_OK; ++i) {
-            st = step_dev(n, s.x + i * in, s.t + i * out, 1, lr, (int)loss);
-            if (st == ZN_OK &&
-                cudaMemcpyAsync(losses_dev + i, last.grads + last.blk, sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
-                st = zn_fail(ctx, ZN_ERR_CUDA, "loss copy failed");
+            st = step_dev(n, s.x + i * in, s.t + i * out, 1, lr, (int)loss, losses_dev + i, nullptr);
         }
         if (st != ZN_OK) break;
-        if (cudaMemcpyAsync(losses.data(), losses_dev, samples * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+        if (zn_sync_all_lanes(ctx) != ZN_OK ||
+            cudaMemcpyAsync(losses.data(), losses_dev, samples * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
             cudaStreamSynchronize(ctx->stream) != cudaSuccess) { st = zn_fail(ctx, ZN_ERR_CUDA, "loss read-back failed"); break; }
         float total = 0.f;
         for (size_t i = 0; i < samples; ++i) total += loss_from_sum(n, losses[i], 1, (int)loss);
         if (epoch_loss) epoch_loss[e] = total / (float)samples;   // src/network.zig:615
     }
-    cudaStreamSynchronize(ctx->stream);
+    zn_sync_all_lanes(ctx);
     cudaFree(losses_dev);
     if (st != ZN_OK) return st;
     return zn_check_device_status(ctx);

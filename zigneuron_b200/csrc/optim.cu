@@ -41,7 +41,7 @@ __global__ void sq_partial_kernel(const __grid_constant__ SegTable tab, float *_
     if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
         for (unsigned long long i = base + threadIdx.x * 4ull; i < end; i += TPB * 4ull) {
             if (i + 4 <= end) {
-                const float4 v = *reinterpret_cast<const float4 *>(p + i);
+                const float4 v = __ldcs(reinterpret_cast<const float4 *>(p + i));   // read once: keep it out of L2's way
                 s += v.x * v.x; s += v.y * v.y; s += v.z * v.z; s += v.w * v.w;
             } else {
                 for (unsigned long long j = i; j < end; ++j) s += p[j] * p[j];
@@ -141,6 +141,53 @@ __global__ void sgd_kernel(zn_opt_args a, int is_bias) {
 }
 
 // cpuAdamUpdate, src/backend.zig:2760-2772, with Adam.step's L2 term (src/optimizer.zig:221-228) folded in.
+__device__ __forceinline__ void adam_one(const zn_opt_args &a, float f, float omb1, float omb2, float &g, float &w,
+                                         float &m, float &v) {
+    if (f != 1.0f) g = __fmul_rn(g, f);
+    if (a.wd > 0.0f) g = __fadd_rn(g, __fmul_rn(a.wd, w));
+    const float gc = clamp_grad(g);
+    m = __fadd_rn(__fmul_rn(a.beta1, m), __fmul_rn(omb1, gc));
+    v = __fadd_rn(__fmul_rn(a.beta2, v), __fmul_rn(__fmul_rn(omb2, gc), gc));
+    const float m_hat = __fdiv_rn(m, a.bc1);
+    const float v_hat = __fdiv_rn(v, a.bc2);
+    w = __fsub_rn(w, __fdiv_rn(__fmul_rn(a.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), a.eps)));
+    w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+}
+
+// Four parameters per thread with 16-byte accesses; the host picks this variant when every pointer is
+// 16-byte aligned, the count is a multiple of 4 and the operand copy (if any) has the weights' own pitch.
+template <typename ST>
+__global__ void adam_vec4_kernel(zn_opt_args a) {
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const bool write_g = (f != 1.0f) || (a.wd > 0.0f);
+    const float omb1 = 1.0f - a.beta1, omb2 = 1.0f - a.beta2;
+    const size_t n4 = a.count / 4;
+    float4 *W = reinterpret_cast<float4 *>(a.w), *G = reinterpret_cast<float4 *>(a.g);
+    float4 *M = reinterpret_cast<float4 *>(a.m), *V = reinterpret_cast<float4 *>(a.v);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        // streaming accesses: this pass touches every parameter once while GEMMs of the next step run on the
+        // same GPU; it should not push their operand tiles out of L2
+        float4 g = __ldcs(&G[i]), w = __ldcs(&W[i]), m = __ldcs(&M[i]), v = __ldcs(&V[i]);
+        adam_one(a, f, omb1, omb2, g.x, w.x, m.x, v.x);
+        adam_one(a, f, omb1, omb2, g.y, w.y, m.y, v.y);
+        adam_one(a, f, omb1, omb2, g.z, w.z, m.z, v.z);
+        adam_one(a, f, omb1, omb2, g.w, w.w, m.w, v.w);
+        if (write_g) __stcs(&G[i], g);
+        __stcs(&M[i], m);
+        __stcs(&V[i], v);
+        __stcs(&W[i], w);
+        if (a.shadow) {
+            if (sizeof(ST) == 2) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+                reinterpret_cast<uint2 *>(a.shadow)[i] =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+            } else {
+                reinterpret_cast<float4 *>(a.shadow)[i] = w;
+            }
+        }
+    }
+}
+
 template <typename ST>
 __global__ void adam_kernel(zn_opt_args a) {
     const float f = a.factor_dev ? *a.factor_dev : 1.0f;
@@ -166,7 +213,31 @@ __global__ void adam_kernel(zn_opt_args a) {
     }
 }
 
+// The training step runs these kernels on side lanes underneath the persistent GEMM, whose CTAs need the
+// SM configured for maximum shared memory.  A kernel that lets the driver pick another shared-memory /
+// L1 split cannot share an SM with them and would only run between GEMM launches; ask for the same split.
+void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
+    static uint64_t done_mask = 0;
+    const uint64_t bit = 1ull << (ctx->device & 63);
+    if (done_mask & bit) return;
+    done_mask |= bit;
+    const int c = cudaSharedmemCarveoutMaxShared;
+    const cudaFuncAttribute at = cudaFuncAttributePreferredSharedMemoryCarveout;
+    cudaFuncSetAttribute(sq_partial_kernel, at, c);
+    cudaFuncSetAttribute(norm_final_kernel, at, c);
+    cudaFuncSetAttribute(norm_exact_kernel, at, c);
+    cudaFuncSetAttribute(scale_kernel, at, c);
+    cudaFuncSetAttribute(sgd_kernel<float>, at, c);
+    cudaFuncSetAttribute(sgd_kernel<__nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(adam_kernel<float>, at, c);
+    cudaFuncSetAttribute(adam_kernel<__nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(adam_vec4_kernel<float>, at, c);
+    cudaFuncSetAttribute(adam_vec4_kernel<__nv_bfloat16>, at, c);
+    cudaGetLastError();
+}
+
 int grid_for(zn_ctx *ctx, size_t n) {
+    prefer_gemm_compatible_carveout(ctx);
     size_t blocks = (n + TPB - 1) / TPB;
     const size_t cap = (size_t)ctx->sm_count * 8;
     if (blocks > cap) blocks = cap;
@@ -205,6 +276,72 @@ zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_
     return ZN_OK;
 }
 
+namespace {
+
+__global__ void sumsq_final_kernel(const float *__restrict__ partial, int n, double *__restrict__ out) {
+    __shared__ double sm[TPB];
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partial[i];
+    sm[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = TPB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *out = sm[0];
+}
+
+__global__ void norm_combine_kernel(const double *__restrict__ sums, int count, float *__restrict__ out) {
+    double s = 0.0;
+    for (int i = 0; i < count; ++i) s += sums[i];
+    const float total = sqrtf((float)s);
+    out[0] = total;
+    out[1] = total > 1.0f ? __fdiv_rn(1.0f, __fadd_rn(total, 1e-6f)) : 1.0f;
+}
+
+}   // namespace
+
+zn_status zn_k_sumsq(zn_ctx *ctx, const zn_seg *segs, int nseg, double *sumsq_dev) {
+    if (nseg <= 0 || nseg > MAX_SEGS) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "sum of squares: 1..%d tensors supported", MAX_SEGS);
+    SegTable tab;
+    int blocks = 0;
+    double bytes = 0;
+    for (int i = 0; i < nseg; ++i) {
+        tab.ptr[i] = segs[i].ptr;
+        tab.count[i] = segs[i].count;
+        tab.first_block[i] = blocks;
+        blocks += (int)((segs[i].count + ELEMS_PER_BLOCK - 1) / ELEMS_PER_BLOCK);
+        bytes += 4.0 * segs[i].count;
+    }
+    tab.first_block[nseg] = blocks;
+    tab.nseg = nseg;
+    if (blocks == 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "sum of squares: empty tensors");
+    prefer_gemm_compatible_carveout(ctx);
+    {
+        static uint64_t done_mask = 0;
+        const uint64_t bit = 1ull << (ctx->device & 63);
+        if (!(done_mask & bit)) {
+            done_mask |= bit;
+            cudaFuncSetAttribute(sumsq_final_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(norm_combine_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaGetLastError();
+        }
+    }
+    ZN_TRY(zn_scratch_reserve(ctx, (size_t)blocks));
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 2);
+    sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch);
+    sumsq_final_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, blocks, sumsq_dev);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_norm_combine(zn_ctx *ctx, const double *sumsq_dev, int count, float *norm_factor_dev) {
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, 8.0 * count, 1);
+    norm_combine_kernel<<<1, 1, 0, ctx->stream>>>(sumsq_dev, count, norm_factor_dev);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
 zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev) {
     zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, 8.0 * n);
     scale_kernel<<<grid_for(ctx, n), TPB, 0, ctx->stream>>>(p, n, factor_dev);
@@ -222,6 +359,16 @@ zn_status zn_k_sgd(zn_ctx *ctx, const zn_opt_args &a, bool is_bias) {
 
 zn_status zn_k_adam(zn_ctx *ctx, const zn_opt_args &a) {
     zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, (28.0 + (a.shadow ? (a.shadow_bf16 ? 2 : 4) : 0)) * a.count);
+    auto aligned = [](const void *p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; };
+    const bool vec4 = a.count % 4 == 0 && a.count >= 4096 && aligned(a.w, 16) && aligned(a.g, 16) && aligned(a.m, 16) &&
+                      aligned(a.v, 16) && (!a.shadow || (a.ld_shadow == a.cols && aligned(a.shadow, a.shadow_bf16 ? 8 : 16)));
+    if (vec4) {
+        const int grid = grid_for(ctx, a.count / 4);
+        if (a.shadow && a.shadow_bf16) adam_vec4_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(a);
+        else adam_vec4_kernel<float><<<grid, TPB, 0, ctx->stream>>>(a);
+        ZN_CUDA(ctx, cudaGetLastError());
+        return ZN_OK;
+    }
     if (a.shadow && a.shadow_bf16) adam_kernel<__nv_bfloat16><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a);
     else adam_kernel<float><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a);
     ZN_CUDA(ctx, cudaGetLastError());

@@ -318,6 +318,24 @@ __global__ void sum_partials_kernel(const float *__restrict__ partial, int n, fl
     if (threadIdx.x == 0) *out = (float)sm[0];
 }
 
+// The column reduction runs on a side lane underneath the persistent GEMM, whose CTAs need the SM set up
+// for maximum shared memory; a kernel left to another shared-memory / L1 split cannot share an SM with
+// them.  Ask for the same split (see the same note in optim.cu).
+void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
+    static uint64_t done_mask = 0;
+    const uint64_t bit = 1ull << (ctx->device & 63);
+    if (done_mask & bit) return;
+    done_mask |= bit;
+    const int c = cudaSharedmemCarveoutMaxShared;
+    const cudaFuncAttribute at = cudaFuncAttributePreferredSharedMemoryCarveout;
+    cudaFuncSetAttribute(bias_reduce_partial_kernel<float, 4>, at, c);
+    cudaFuncSetAttribute(bias_reduce_partial_kernel<__nv_bfloat16, 8>, at, c);
+    cudaFuncSetAttribute(bias_reduce_final_kernel, at, c);
+    cudaFuncSetAttribute(bias_reduce_exact_kernel<float>, at, c);
+    cudaFuncSetAttribute(bias_reduce_exact_kernel<__nv_bfloat16>, at, c);
+    cudaGetLastError();
+}
+
 int grid_for(zn_ctx *ctx, int64_t work_items, int per_sm = 8) {
     int64_t blocks = (work_items + TPB - 1) / TPB;
     const int64_t cap = (int64_t)ctx->sm_count * per_sm;
@@ -377,6 +395,7 @@ zn_status zn_k_act_backward_t(zn_ctx *ctx, int act, const void *y, int64_t ld_y,
 zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, int64_t rows, int64_t cols, float *gb,
                            bool accumulate, bool exact) {
     const double bytes = (double)rows * cols * (g_bf16 ? 2 : 4) + 4.0 * cols;
+    prefer_gemm_compatible_carveout(ctx);
     if (exact) {
         zn_launch_scope scope(ctx, ZN_PROF_BIAS_REDUCE, 0, bytes);
         const int grid = (int)((cols + 127) / 128);

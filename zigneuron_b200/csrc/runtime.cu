@@ -71,6 +71,13 @@ extern "C" zn_status zn_ctx_create(int32_t device, zn_ctx **out) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->opt_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking);
+    for (int i = 0; i < 4 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&ctx->lane_join[i], cudaEventDisableTiming);
+    ctx->lanes[ZN_LANE_MAIN].stream = ctx->stream;
+    ctx->lanes[ZN_LANE_COMM].stream = ctx->comm_stream;
+    ctx->lanes[ZN_LANE_OPT].stream = ctx->opt_stream;
+    ctx->lanes[ZN_LANE_AUX].stream = ctx->aux_stream;
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaHostAlloc((void **)&ctx->status_host, sizeof(int), cudaHostAllocMapped);
     if (e == cudaSuccess) {
@@ -92,11 +99,19 @@ extern "C" zn_status zn_dp_destroy(zn_ctx *ctx);
 extern "C" void zn_ctx_destroy(zn_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
-    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    zn_lane_switch(ctx, ZN_LANE_MAIN);
+    for (int i = 0; i < 4; ++i)
+        if (ctx->lanes[i].stream) cudaStreamSynchronize(ctx->lanes[i].stream);
     if (ctx->dp) zn_dp_destroy(ctx);
     for (auto &kv : ctx->tensors) cudaFree(kv.first);
     for (int i = 0; i < 6; ++i) cudaFree(ctx->stage[i]);
     cudaFree(ctx->scratch);
+    cudaFree(ctx->tile_counters);
+    for (int i = 1; i < 4; ++i) cudaFree(ctx->lanes[i].scratch);
+    for (int i = 0; i < 4; ++i)
+        if (ctx->lane_join[i]) cudaEventDestroy(ctx->lane_join[i]);
+    if (ctx->opt_stream) cudaStreamDestroy(ctx->opt_stream);
+    if (ctx->aux_stream) cudaStreamDestroy(ctx->aux_stream);
     for (auto &slot : ctx->prof)
         for (auto &p : slot.pending) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
     for (auto ev : ctx->event_pool) cudaEventDestroy(ev);
@@ -126,6 +141,37 @@ zn_status zn_check_device_status(zn_ctx *ctx) {
     return ZN_OK;
 }
 
+void zn_lane_switch(zn_ctx *ctx, int lane) {
+    if (lane == ctx->lane) return;
+    zn_ctx::lane_state &cur = ctx->lanes[ctx->lane];
+    cur.stream = ctx->stream;
+    cur.scratch = ctx->scratch;
+    cur.scratch_floats = ctx->scratch_floats;
+    const zn_ctx::lane_state &next = ctx->lanes[lane];
+    ctx->stream = next.stream;
+    ctx->scratch = next.scratch;
+    ctx->scratch_floats = next.scratch_floats;
+    ctx->lane = lane;
+}
+
+zn_status zn_sync_all_lanes(zn_ctx *ctx) {
+    zn_lane_switch(ctx, ZN_LANE_MAIN);
+    for (int i = 0; i < 4; ++i) {
+        cudaStream_t s = i == ZN_LANE_MAIN ? ctx->stream : ctx->lanes[i].stream;
+        if (s) ZN_CUDA(ctx, cudaStreamSynchronize(s));
+    }
+    return ZN_OK;
+}
+
+zn_status zn_join_lanes_into_main(zn_ctx *ctx) {
+    zn_lane_switch(ctx, ZN_LANE_MAIN);
+    for (int i = 1; i < 4; ++i) {
+        ZN_CUDA(ctx, cudaEventRecord(ctx->lane_join[i], ctx->lanes[i].stream));
+        ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->lane_join[i], 0));
+    }
+    return ZN_OK;
+}
+
 extern "C" zn_status zn_begin_command_batch(zn_ctx *ctx) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
     ctx->batch_depth += 1;
@@ -135,7 +181,7 @@ extern "C" zn_status zn_begin_command_batch(zn_ctx *ctx) {
 extern "C" zn_status zn_end_command_batch(zn_ctx *ctx) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
     if (ctx->batch_depth > 0) ctx->batch_depth -= 1;
-    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ZN_TRY(zn_sync_all_lanes(ctx));
     return zn_check_device_status(ctx);
 }
 
@@ -259,7 +305,7 @@ zn_launch_scope::~zn_launch_scope() {
 }
 
 static void drain_profile(zn_ctx *ctx) {
-    cudaStreamSynchronize(ctx->stream);
+    zn_sync_all_lanes(ctx);
     for (auto &slot : ctx->prof) {
         for (auto &p : slot.pending) {
             float ms = 0;
@@ -311,6 +357,7 @@ extern "C" zn_status zn_timer_start(zn_ctx *ctx) {
 extern "C" zn_status zn_timer_stop(zn_ctx *ctx, float *ms_out) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
     if (!ctx->timer0 || !ms_out) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "timer not started or null output");
+    ZN_TRY(zn_join_lanes_into_main(ctx));   // work still running on the other lanes belongs to the timed region
     ZN_CUDA(ctx, cudaEventRecord(ctx->timer1, ctx->stream));
     ZN_CUDA(ctx, cudaEventSynchronize(ctx->timer1));
     ZN_CUDA(ctx, cudaEventElapsedTime(ms_out, ctx->timer0, ctx->timer1));

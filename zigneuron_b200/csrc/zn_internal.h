@@ -39,6 +39,15 @@ struct zn_ctx {
     // Scratch for two-stage reductions (block partials); grown on demand.
     float *scratch = nullptr;
     size_t scratch_floats = 0;
+    // Lanes.  `stream` / `scratch` above are those of the ACTIVE lane; every launcher uses them.  The
+    // training step runs its column reductions, its all-reduces and its parameter updates on lanes of
+    // their own so that they overlap the GEMMs; each lane has its own scratch so concurrent reductions
+    // never share partial-sum storage.  0 = main, 1 = communication, 2 = optimizer, 3 = auxiliary.
+    struct lane_state { cudaStream_t stream = nullptr; float *scratch = nullptr; size_t scratch_floats = 0; };
+    lane_state lanes[4];
+    int lane = 0;
+    cudaStream_t opt_stream = nullptr, aux_stream = nullptr;
+    cudaEvent_t lane_join[4] = {nullptr, nullptr, nullptr, nullptr};
     // Staging for ops called with host pointers; grown on demand.
     float *stage[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     size_t stage_floats[6] = {0, 0, 0, 0, 0, 0};
@@ -52,6 +61,10 @@ struct zn_ctx {
     zn_prof_slot prof[ZN_PROF_FAMILY_COUNT];
     std::vector<cudaEvent_t> event_pool;
     cudaEvent_t timer0 = nullptr, timer1 = nullptr;
+    // Two work counters for the persistent GEMM's dynamic tile scheduler, used in turn by successive launches
+    // on the main stream (each launch clears the one the next launch will use).
+    unsigned int *tile_counters = nullptr;
+    unsigned int tile_counter_turn = 0;
 
     zn_dp_state *dp = nullptr;
 };
@@ -77,6 +90,17 @@ struct zn_launch_scope {
     zn_launch_scope(zn_ctx *c, int fam, double flops, double bytes, int n_launches = 1);
     ~zn_launch_scope();
 };
+
+enum { ZN_LANE_MAIN = 0, ZN_LANE_COMM = 1, ZN_LANE_OPT = 2, ZN_LANE_AUX = 3 };
+void zn_lane_switch(zn_ctx *ctx, int lane);       // makes `lane` the active one (stream + scratch)
+struct zn_lane_guard {                            // active lane for the lifetime of the guard
+    zn_ctx *ctx;
+    int prev;
+    zn_lane_guard(zn_ctx *c, int lane) : ctx(c), prev(c->lane) { zn_lane_switch(c, lane); }
+    ~zn_lane_guard() { zn_lane_switch(ctx, prev); }
+};
+zn_status zn_sync_all_lanes(zn_ctx *ctx);         // host waits for every lane
+zn_status zn_join_lanes_into_main(zn_ctx *ctx);   // the main stream waits (on the device) for the other lanes
 
 zn_status zn_scratch_reserve(zn_ctx *ctx, size_t floats);
 zn_status zn_check_device_status(zn_ctx *ctx);   // reads the pinned status word after a sync
@@ -133,6 +157,11 @@ struct zn_seg { const float *ptr; size_t count; };
 // norm_factor_dev[0] = sqrt(sum g^2), [1] = clip factor (1 when norm <= 1); extra_sq_dev optional.
 zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_factor_dev, bool exact = false);
 zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev);
+// The same norm in two steps, so that each layer's share can be summed as soon as its gradients are final:
+// sumsq_dev[0] = sum of squares over the segments (double); combine adds `count` such sums in order and
+// writes norm / clip factor as zn_k_grad_norm does.
+zn_status zn_k_sumsq(zn_ctx *ctx, const zn_seg *segs, int nseg, double *sumsq_dev);
+zn_status zn_k_norm_combine(zn_ctx *ctx, const double *sumsq_dev, int count, float *norm_factor_dev);
 
 struct zn_opt_args {
     float *w; float *g; float *m; float *v; size_t count;
