@@ -38,7 +38,8 @@ constexpr int B_STAGE = BN * ROW_BYTES;           // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int BIAS_SMEM = 4 * BN * 4;                 // one tile's bias values, a private copy per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + BIAS_SMEM;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
 struct TcParams {
@@ -61,6 +62,7 @@ struct TcParams {
     // Dynamic tile scheduling: a CTA takes tile blockIdx.x first, then gridDim.x + atomicAdd(tile_counter).
     // Each launch also clears the counter the NEXT launch on the stream will use.
     unsigned int *tile_counter, *next_counter;
+    int dynamic_tiles;       // 0: plain round-robin over the grid (diagnostic)
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -185,6 +187,121 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int &tm
     tn = r / rows;
 }
 
+// Fused epilogue for 32 consecutive columns of one output row held by this thread:
+// bias, activation, activation-derivative mask, accumulate, stores (fp32 and/or operand type).
+template <bool TF32>
+__device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row, int col0, const uint32_t (&r)[32],
+                                               const float *bias_s /* 32 staged bias values of these columns, or null */) {
+    constexpr bool t_bf16 = !TF32;
+    const int valid = min(32, p.N - col0);
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (bias_s) {   // every lane reads the same shared-memory word: a broadcast, no bank conflict
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += bias_s[j];
+    }
+    // one branch on the (uniform) activation outside the element loop: a switch per element makes the
+    // compiler issue every activation's code, predicated off, for each of the 32 values
+    if (p.act == ZN_ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+    } else if (p.act == ZN_ACT_SIGMOID) {
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) v[j] = act_apply(ZN_ACT_SIGMOID, v[j]);
+    } else if (p.act == ZN_ACT_TANH) {
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) v[j] = act_apply(ZN_ACT_TANH, v[j]);
+    }
+    if (p.mask) {
+        if (t_bf16) {
+            const __nv_bfloat16 *mrow = static_cast<const __nv_bfloat16 *>(p.mask) + row * p.ld_mask + col0;
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(mrow) & 15) == 0)) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const uint4 u = *reinterpret_cast<const uint4 *>(mrow + g * 8);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        // bf16 > 0  <=>  sign bit clear and magnitude bits non-zero
+                        const uint32_t lo = w[h] & 0xFFFFu, hi = w[h] >> 16;
+                        if (!(lo != 0u && lo < 0x8000u)) v[g * 8 + h * 2] = 0.f;
+                        if (!(hi != 0u && hi < 0x8000u)) v[g * 8 + h * 2 + 1] = 0.f;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < valid && !(__bfloat162float(mrow[j]) > 0.f)) v[j] = 0.f;
+            }
+        } else {
+            const float *mrow = static_cast<const float *>(p.mask) + row * p.ld_mask + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid && !(mrow[j] > 0.f)) v[j] = 0.f;
+        }
+    }
+    if (p.out_f32) {
+        float *orow = p.out_f32 + row * p.ld_out_f32 + col0;
+        const bool vec = valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
+        if (p.accumulate) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid) v[j] += orow[j];
+        }
+        if (vec) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+                *reinterpret_cast<float4 *>(orow + g * 4) =
+                    make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid) orow[j] = v[j];
+        }
+    }
+    if (p.out_t) {
+        if (t_bf16) {
+            __nv_bfloat16 *orow = static_cast<__nv_bfloat16 *>(p.out_t) + row * p.ld_out_t + col0;
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0)) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const __nv_bfloat162 b2 =
+                            __floats2bfloat162_rn(v[g * 8 + h * 2], v[g * 8 + h * 2 + 1]);
+                        w[h] = *reinterpret_cast<const uint32_t *>(&b2);
+                    }
+                    *reinterpret_cast<uint4 *>(orow + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < valid) orow[j] = __float2bfloat16_rn(v[j]);
+            }
+        } else {
+            float *orow = static_cast<float *>(p.out_t) + row * p.ld_out_t + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid) orow[j] = v[j];
+        }
+    }
+}
+
+// Each epilogue warp copies the tile's BN bias values into its own strip of shared memory once, instead of
+// every thread fetching all of them from global memory through an L1 that the shared-memory split leaves
+// tiny.  A private strip per warp needs no barrier between warps, only __syncwarp around the reuse.
+__device__ __forceinline__ const float *stage_bias(const TcParams &p, float *bias_smem, int n0) {
+    if (!p.bias) return nullptr;
+    const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & 3;
+    float *dst = bias_smem + w * BN;
+    __syncwarp();                                   // the previous tile's reads of the strip are done
+    for (int j = lane; j < BN; j += 32) dst[j] = (n0 + j < p.N) ? __ldg(p.bias + n0 + j) : 0.f;
+    __syncwarp();
+    return dst;
+}
+
 // ET: operand element type (__nv_bfloat16 or float-as-tf32).
 template <typename ET>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -212,6 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4 + 2 * TQ));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *tile_ring = reinterpret_cast<volatile int *>(tmem_slot + 2);
+    float *bias_smem = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -247,9 +365,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             int q = 0;
             uint32_t qphase = 0;
+            int prev_t = 0;
             for (bool first = true; ok; first = false) {
                 // next tile: the CTA's own first, then whatever the grid has not started yet
-                int t = first ? (int)blockIdx.x : (int)(gridDim.x + atomicAdd(p.tile_counter, 1u));
+                int t = first ? (int)blockIdx.x
+                              : (p.dynamic_tiles ? (int)(gridDim.x + atomicAdd(p.tile_counter, 1u)) : prev_t + (int)gridDim.x);
+                prev_t = t;
                 if (t >= num_tiles) t = -1;
                 if (!mbar_wait(sempty_bar(q), qphase ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
                 tile_ring[q] = t;
@@ -330,7 +451,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else {
         // ================= epilogue: warps 2..5, TMEM lanes 32*(warp%4).. =================
         const int q = warp & 3;
-        const bool t_bf16 = !TF32;
         int it = 0, sq = 0;
         uint32_t sqphase = 0;
         bool ok = true;
@@ -349,6 +469,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_after();
             const long long row = (long long)tm * BM + q * 32 + lane;
             const int n0 = tn * BN;
+            const float *bias_s = stage_bias(p, bias_smem, n0);
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
             for (int c = 0; c < nchunks; ++c) {
@@ -362,94 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
                 if (row >= p.M) continue;
-                const int col0 = n0 + c * 32;
-                const int valid = min(32, p.N - col0);
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                if (p.bias) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (j < valid) v[j] += __ldg(p.bias + col0 + j);
-                }
-                if (p.act != ZN_ACT_LINEAR) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = act_apply(p.act, v[j]);
-                }
-                if (p.mask) {
-                    if (t_bf16) {
-                        const __nv_bfloat16 *mrow = static_cast<const __nv_bfloat16 *>(p.mask) + row * p.ld_mask + col0;
-                        if (valid == 32 && ((reinterpret_cast<uintptr_t>(mrow) & 15) == 0)) {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                const uint4 u = *reinterpret_cast<const uint4 *>(mrow + g * 8);
-                                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                                for (int h = 0; h < 4; ++h) {
-                                    // bf16 > 0  <=>  sign bit clear and magnitude bits non-zero
-                                    const uint32_t lo = w[h] & 0xFFFFu, hi = w[h] >> 16;
-                                    if (!(lo != 0u && lo < 0x8000u)) v[g * 8 + h * 2] = 0.f;
-                                    if (!(hi != 0u && hi < 0x8000u)) v[g * 8 + h * 2 + 1] = 0.f;
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < valid && !(__bfloat162float(mrow[j]) > 0.f)) v[j] = 0.f;
-                        }
-                    } else {
-                        const float *mrow = static_cast<const float *>(p.mask) + row * p.ld_mask + col0;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid && !(mrow[j] > 0.f)) v[j] = 0.f;
-                    }
-                }
-                if (p.out_f32) {
-                    float *orow = p.out_f32 + row * p.ld_out_f32 + col0;
-                    const bool vec = valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
-                    if (p.accumulate) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) v[j] += orow[j];
-                    }
-                    if (vec) {
-#pragma unroll
-                        for (int g = 0; g < 8; ++g)
-                            *reinterpret_cast<float4 *>(orow + g * 4) =
-                                make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) orow[j] = v[j];
-                    }
-                }
-                if (p.out_t) {
-                    if (t_bf16) {
-                        __nv_bfloat16 *orow = static_cast<__nv_bfloat16 *>(p.out_t) + row * p.ld_out_t + col0;
-                        if (valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0)) {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int h = 0; h < 4; ++h) {
-                                    const __nv_bfloat162 b2 =
-                                        __floats2bfloat162_rn(v[g * 8 + h * 2], v[g * 8 + h * 2 + 1]);
-                                    w[h] = *reinterpret_cast<const uint32_t *>(&b2);
-                                }
-                                *reinterpret_cast<uint4 *>(orow + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < valid) orow[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    } else {
-                        float *orow = static_cast<float *>(p.out_t) + row * p.ld_out_t + col0;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) orow[j] = v[j];
-                    }
-                }
+                epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
             }
         }
     }
@@ -464,6 +498,236 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// =====================================================================================================
+// Two-CTA variant.  A cluster of two CTAs on a pair of SMs computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own half (128 of the 256
+// columns) of B, the leader CTA's single thread issues the MMAs, and each CTA ends up with its 128 rows of
+// the accumulator in its own tensor memory.  Per SM that is 32 KB of operands per k-block instead of the
+// 48 KB of the one-CTA kernel, which is what the L2 -> shared-memory path can sustain at full tensor rate.
+// Barriers: the leader's `full` barrier counts the bytes of BOTH CTAs' TMA loads (each CTA's loads name
+// the leader's barrier); `empty` and `tmem_full` are signalled in both CTAs by one multicast
+// tcgen05.commit; the epilogue warps of both CTAs arrive on the leader's `tmem_empty`.
+
+constexpr int STAGES2 = 6;
+constexpr int HALF = 128;                         // rows of A, and columns of B, staged per CTA
+constexpr int A2_STAGE = HALF * ROW_BYTES;        // 16 KiB
+constexpr int B2_STAGE = HALF * ROW_BYTES;        // 16 KiB
+constexpr int STAGE2_BYTES = A2_STAGE + B2_STAGE;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256 + BIAS_SMEM;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes go to a barrier that may live in the peer CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar)
+        : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both)
+                 : "memory");
+}
+template <bool TF32>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    if (TF32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    }
+}
+
+template <typename ET>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+    constexpr bool TF32 = sizeof(ET) == 4;
+    constexpr int ES = sizeof(ET);
+    constexpr int BK = ROW_BYTES / ES;
+    constexpr int CH = ROW_BYTES / ES;
+    constexpr int UMMA_K_BYTES = 32;
+    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - raw);
+    const uint32_t bars = base + STAGES2 * STAGE2_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
+    auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + b); };
+    auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + 2 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES2 * STAGE2_BYTES + 8 * (2 * STAGES2 + 4));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *bias_smem = reinterpret_cast<float *>(gen + STAGES2 * STAGE2_BYTES + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        for (int s = 0; s < STAGES2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps x 2 CTAs
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // both CTAs' barriers exist before anything remote touches them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m_pairs = (p.M + 2 * HALF - 1) / (2 * HALF);
+    const int num_tiles = num_m_pairs * p.num_n_tiles;
+    const int nkb = p.num_k_blocks;
+    const int cluster_id = (int)(blockIdx.x >> 1), num_clusters = (int)(gridDim.x >> 1);
+
+    if (warp == 0) {
+        // ================= TMA producer (both CTAs) =================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                int tm, tn;
+                tile_coords(t, num_m_pairs, p.num_n_tiles, tm, tn);
+                const int m0 = tm * 2 * HALF + (int)rank * HALF;       // this CTA's rows of A
+                const int n0 = tn * BN + (int)rank * HALF;             // this CTA's columns of B
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                    const uint32_t sa = base + s * STAGE2_BYTES, sb = sa + A2_STAGE;
+                    const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE2_BYTES);
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d_pair(sa, &tmA, k0, m0, lead_full);                       // box {BK, 128}
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < HALF / CH; ++c)
+                            tma_load_2d_pair(sa + c * (BK * ROW_BYTES), &tmA, m0 + c * CH, k0, lead_full);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d_pair(sb, &tmB, k0, n0, lead_full);                       // box {BK, 128}
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < HALF / CH; ++c)
+                            tma_load_2d_pair(sb + c * (BK * ROW_BYTES), &tmB, n0 + c * CH, k0, lead_full);
+                    }
+                    if (++s == STAGES2) { s = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer (leader CTA only) =================
+        if (lane == 0 && rank == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const uint32_t a_lbo = p.a_mn ? p.mn_lbo : 16, b_lbo = p.b_mn ? p.mn_lbo : 16;
+            const uint32_t a_sbo = p.a_mn ? p.mn_sbo : 1024, b_sbo = p.b_mn ? p.mn_sbo : 1024;
+            const uint32_t a_lt = (TF32 && p.a_mn) ? 1u : 2u, b_lt = (TF32 && p.b_mn) ? 1u : 2u;
+            const uint32_t a_kstep = p.a_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
+            const uint32_t b_kstep = p.b_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
+            int it = 0;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 13)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * STAGE2_BYTES, sb = sa + A2_STAGE;
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ++ks) {
+                        const uint64_t ad = make_desc(sa + ks * a_kstep, a_lbo, a_sbo, a_lt);
+                        const uint64_t bd = make_desc(sb + ks * b_kstep, b_lbo, b_sbo, b_lt);
+                        tc_mma_pair<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty_bar(s));         // frees the stage in both CTAs
+                    if (++s == STAGES2) { s = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit_pair(tfull_bar(buf));   // accumulator complete, in both CTAs
+            }
+        }
+    } else {
+        // ================= epilogue (both CTAs): warps 2..5, this CTA's 128 rows =================
+        const int q = warp & 3;
+        int it = 0;
+        bool ok = true;
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+            int tm, tn;
+            tile_coords(t, num_m_pairs, p.num_n_tiles, tm, tn);
+            const int buf = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
+            tc_fence_after();
+            const long long row = (long long)tm * 2 * HALF + (long long)rank * HALF + q * 32 + lane;
+            const int n0 = tn * BN;
+            const float *bias_s = stage_bias(p, bias_smem, n0);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
+            for (int c = 0; c < nchunks; ++c) {
+                uint32_t r[32];
+                tc_ld32(taddr + (uint32_t)(c * 32), r);
+                tc_wait_ld();
+                if (c == nchunks - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));   // to the leader's MMA thread
+                }
+                if (row >= p.M) continue;
+                epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+            }
+        }
+    }
+
+    // ---- common exit: neither CTA may leave while its partner can still reach its shared or tensor memory
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -581,11 +845,46 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.tile_counter = ctx->tile_counters + (ctx->tile_counter_turn & 1);
     p.next_counter = ctx->tile_counters + ((ctx->tile_counter_turn + 1) & 1);
     ctx->tile_counter_turn += 1;
+    static const int dyn = getenv("ZN_TC_STATIC_TILES") ? 0 : 1;
+    p.dynamic_tiles = dyn;
 
-    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
-    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
     zn_launch_scope scope(ctx, ZN_PROF_GEMM_TC, 2.0 * m * n * k,
                           (double)es * (m * k + k * n) + (e.out_f32 ? 4.0 : (double)es) * m * n);
+    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;   // ZN_TC_PAIR=0: one-CTA kernel only (diagnostic)
+    if (pair_mode && m > BM) {
+        // two-CTA kernel: 256 x 256 tiles, B staged in halves of 128 columns per CTA
+        if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, HALF, false));
+        p.idesc = (p.idesc & ~(0x1Fu << 24)) | ((uint32_t)((2 * HALF) >> 4) << 24);   // M = 256 across the pair
+        const long long pair_tiles = (long long)((m + 2 * HALF - 1) / (2 * HALF)) * p.num_n_tiles;
+        const int max_clusters = ctx->sm_count / 2;
+        const int clusters = (int)(pair_tiles < max_clusters ? pair_tiles : max_clusters);
+        static uint64_t pair_attr_mask = 0;
+        if (!(pair_attr_mask & dev_bit)) {
+            ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_pair_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES));
+            ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES));
+            cudaFuncSetAttribute(gemm_tc_pair_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(gemm_tc_pair_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaGetLastError();
+            pair_attr_mask |= dev_bit;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * clusters));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = SMEM2_BYTES;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (elem_type == 0) ZN_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<__nv_bfloat16>, tmA, tmB, p));
+        else ZN_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<float>, tmA, tmB, p));
+        return ZN_OK;
+    }
+    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
     if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
     else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
     ZN_CUDA(ctx, cudaGetLastError());

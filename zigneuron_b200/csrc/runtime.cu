@@ -2,6 +2,7 @@
 // Replaces CudaBackend.init / CudaContext.init / the dlopen'd driver table of the
 // reference (src/cuda.zig:163, src/cuda_context.zig:382-497, src/cuda_driver.zig:710).
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 
 #include "zn_internal.h"
@@ -78,6 +79,10 @@ extern "C" zn_status zn_ctx_create(int32_t device, zn_ctx **out) {
     ctx->lanes[ZN_LANE_COMM].stream = ctx->comm_stream;
     ctx->lanes[ZN_LANE_OPT].stream = ctx->opt_stream;
     ctx->lanes[ZN_LANE_AUX].stream = ctx->aux_stream;
+    if (getenv("ZN_SERIAL_LANES")) {   // diagnostic: reductions and updates back on the main stream, in program order
+        ctx->lanes[ZN_LANE_OPT].stream = ctx->stream;
+        ctx->lanes[ZN_LANE_AUX].stream = ctx->stream;
+    }
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaHostAlloc((void **)&ctx->status_host, sizeof(int), cudaHostAllocMapped);
     if (e == cudaSuccess) {
