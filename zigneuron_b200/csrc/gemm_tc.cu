@@ -89,6 +89,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {   // acquire at cluster scope
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when the CTA has been aborted or the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
                                           int code) {
@@ -96,6 +107,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                __threadfence_system();
+                return false;
+            }
+        }
+    }
+}
+
+// Same, for a barrier that a thread of the partner CTA arrives on after writing this CTA's shared memory.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                                  int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
@@ -585,8 +615,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
     auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + b); };
     auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + 2 + b); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES2 * STAGE2_BYTES + 8 * (2 * STAGES2 + 4));
+    auto sfull_bar = [&](int q) { return bars + 8u * (2 * STAGES2 + 4 + q); };
+    auto sempty_bar = [&](int q) { return bars + 8u * (2 * STAGES2 + 4 + TQ + q); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES2 * STAGE2_BYTES + 8 * (2 * STAGES2 + 4 + 2 * TQ));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *tile_ring = reinterpret_cast<volatile int *>(tmem_slot + 2);
     float *bias_smem = reinterpret_cast<float *>(gen + STAGES2 * STAGE2_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -597,6 +630,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
         for (int s = 0; s < STAGES2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps x 2 CTAs
+        // tile-index ring: the leader's producer publishes into both CTAs; its `empty` side counts every reader
+        // of the pair: leader MMA thread + 4 leader epilogue warps + peer producer + 4 peer epilogue warps
+        for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 10); }
+        if (blockIdx.x == 0) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -623,7 +660,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+            int q = 0, prev_t = 0;
+            uint32_t qphase = 0;
+            for (bool first = true; ok; first = false) {
+                int t;
+                if (rank == 0) {
+                    // the leader picks the pair's next tile and publishes it into both CTAs' rings
+                    t = first ? cluster_id
+                              : (p.dynamic_tiles ? (int)(num_clusters + atomicAdd(p.tile_counter, 1u)) : prev_t + num_clusters);
+                    prev_t = t;
+                    if (t >= num_tiles) t = -1;
+                    if (!mbar_wait_cluster(sempty_bar(q), qphase ^ 1u, abort_flag, p.status, 15)) { ok = false; break; }
+                    tile_ring[q] = t;
+                    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(smem_u32((const void *)&tile_ring[q]), 1)), "r"(t)
+                                 : "memory");
+                    mbar_arrive(sfull_bar(q));
+                    mbar_arrive_cluster(map_to_cta(sfull_bar(q), 1));
+                } else {
+                    if (!mbar_wait_cluster(sfull_bar(q), qphase, abort_flag, p.status, 16)) { ok = false; break; }
+                    t = tile_ring[q];
+                    mbar_arrive_cluster(map_to_cta(sempty_bar(q), 0));
+                }
+                if (++q == TQ) { q = 0; qphase ^= 1u; }
+                if (t < 0) break;
                 int tm, tn;
                 tile_coords(t, num_m_pairs, p.num_n_tiles, tm, tn);
                 const int m0 = tm * 2 * HALF + (int)rank * HALF;       // this CTA's rows of A
@@ -663,8 +722,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t a_lt = (TF32 && p.a_mn) ? 1u : 2u, b_lt = (TF32 && p.b_mn) ? 1u : 2u;
             const uint32_t a_kstep = p.a_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
             const uint32_t b_kstep = p.b_mn ? (UMMA_K_BYTES / ES) * ROW_BYTES : UMMA_K_BYTES;
-            int it = 0;
-            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+            int it = 0, q = 0;
+            uint32_t qphase = 0;
+            for (; ok; ++it) {
+                if (!mbar_wait(sfull_bar(q), qphase, abort_flag, p.status, 17)) { ok = false; break; }
+                const int t = tile_ring[q];
+                mbar_arrive(sempty_bar(q));
+                if (++q == TQ) { q = 0; qphase ^= 1u; }
+                if (t < 0) break;
                 const int buf = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
@@ -689,9 +754,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else {
         // ================= epilogue (both CTAs): warps 2..5, this CTA's 128 rows =================
         const int q = warp & 3;
-        int it = 0;
+        int it = 0, sq = 0;
+        uint32_t sqphase = 0;
         bool ok = true;
-        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+        for (; ok; ++it) {
+            if (!mbar_wait_cluster(sfull_bar(sq), sqphase, abort_flag, p.status, 18)) { ok = false; break; }
+            const int t = tile_ring[sq];
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(sempty_bar(sq), 0));
+            if (++sq == TQ) { sq = 0; sqphase ^= 1u; }
+            if (t < 0) break;
             int tm, tn;
             tile_coords(t, num_m_pairs, p.num_n_tiles, tm, tn);
             const int buf = it & 1;
