@@ -36,6 +36,7 @@ BLOCK_ROWS = 1024                     # data is generated in blocks of rows keye
 SUM_IO = sum(a * b for a, b in DIMS)  # 201,326,592
 PARAMS = SUM_IO + sum(b for _, b in DIMS)
 FLOP_PER_SAMPLE = 6.0 * SUM_IO        # forward + dX + dW GEMMs, the reference's dX of layer 0 included
+NCU_DRAM_BYTES_PER_FLOP = 465.4e6 / (2.0 * 8192 * 8192 * 4096)   # dram read+write of one captured GEMM launch / its flops
 
 
 def layer_weights(layer):
@@ -313,11 +314,18 @@ def run_ours(args):
                                    "of_measured_sustained": FLOP_PER_SAMPLE * value / 1e12 / world / peaks["bf16_sustained"],
                                    "of_measured_burst": FLOP_PER_SAMPLE * value / 1e12 / world / peaks["bf16_burst"],
                                    "of_datasheet_2250": FLOP_PER_SAMPLE * value / 1e12 / world / 2250.0},
-        "roofline": {"kernel": "gemm_tc_kernel<bf16> (tcgen05, 12 launches per step: NN, TN, NT per layer)",
+        "roofline": {"kernel": "gemm_tc_pair_kernel<bf16> (tcgen05 cta_group::2, 12 launches per step: NN, TN, NT per layer)",
                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak if peak else None, "peak_source": f"{peaks['source']}, sustained bf16",
-                     "launches": g["launches"], "avg_launch_ms": g["ms"] / max(1, g["launches"]), "traffic": None},
+                     "launches": g["launches"], "avg_launch_ms": g["ms"] / max(1, g["launches"]),
+                     # DRAM bytes of one launch: ncu capture of the 8192x8192x4096 case (465 MB for 0.55 TFLOP,
+                     # profiles/gemm_tc_pair_bf16_8192x8192x4096_full.md) scaled by the flops of an average launch here
+                     "traffic": NCU_DRAM_BYTES_PER_FLOP * g["flops"] / max(1, g["launches"]),
+                     "traffic_unit": "bytes per launch (scaled from a smaller ncu capture)"},
         "kernel_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
+        "kernel_ms_note": "gemm, loss and convert run on the main stream and add up to the step; optimizer, bias_reduce and "
+                          "grad_norm run on side streams underneath the GEMMs, so their durations (and GB/s) are stretched "
+                          "by sharing the GPU and do not add to the step",
         "hbm_kernels": {k: {"achieved_gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] > 0 else None,
                             "frac_of_measured_hbm": (v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm"]) if v["ms"] > 0 else None}
                         for k, v in prof.items() if k != "gemm"},
@@ -375,9 +383,53 @@ def run_gemm_sweep(args):
     be.deinit()
 
 
+def run_other_config(args):
+    """BASELINE configs[1] (784-512-256-10, batch 1024, Adam, CE with logits, seed 1) and configs[2] (the wide MLP at
+    batch 8192 with SGD, seed 2), inputs resident on the device.  Extra lines for the results table."""
+    import zigneuron_b200 as zn
+    if args.workload == "mlp784":
+        dims, acts, B, seed, loss, lr = [(784, 512), (512, 256), (256, 10)], ["relu", "relu", "linear"], 1024, 1, zn.Loss.cross_entropy_logits, 1e-3
+        precisions = [("fp32_simt", zn.Precision.FP32_SIMT), ("tf32", zn.Precision.TF32_TC), ("bf16", zn.Precision.BF16_TC)]
+    else:
+        dims, acts, B, seed, loss, lr = DIMS, ACTS, 8192, 2, zn.Loss.mse, 1e-3
+        precisions = [("bf16", zn.Precision.BF16_TC), ("tf32", zn.Precision.TF32_TC)]
+    rng = np.random.default_rng(seed)
+    if args.workload == "mlp784":
+        x = rng.random((B, 784), dtype=np.float32)
+        t = np.eye(10, dtype=np.float32)[rng.integers(0, 10, B)]
+    else:
+        x = rng.standard_normal((B, dims[0][0]), dtype=np.float32)
+        t = rng.standard_normal((B, dims[-1][1]), dtype=np.float32)
+    be = zn.Backend(0)
+    flop = 6.0 * B * sum(a * b for a, b in dims)
+    for pname, prec in precisions:
+        net = zn.Network(be, prec)
+        wr = np.random.default_rng([seed, 7])
+        for i, ((a, b), act) in enumerate(zip(dims, acts)):
+            net.addDense(a, b, act)
+            scale = np.sqrt((2.0 if act == "relu" else 1.0) / a) if args.workload != "mlp784" else np.sqrt(2.0 / (a + b))
+            net.setWeights(i, ((wr.random((a, b), dtype=np.float32) * 2 - 1) * np.float32(scale)).astype(np.float32), np.zeros(b, np.float32))
+        if args.workload == "mlp784":
+            net.setOptimizer(zn.Adam())
+        dx, dt = be.tensor(x), be.tensor(t)
+        losses = [net.trainStep(dx, dt, lr, loss, rows=B) for _ in range(args.warmup)]
+        be.endCommandBatch()
+        be.timer_start()
+        for _ in range(args.steps):
+            losses.append(net.trainStep(dx, dt, lr, loss, rows=B))
+        ms = be.timer_stop() / args.steps
+        print(json.dumps({"workload": args.workload, "precision": pname, "batch": B, "ms_per_step": ms,
+                          "samples_per_s": B / (ms / 1e3), "tflops": flop / (ms / 1e3) / 1e12,
+                          "loss_first": losses[0], "loss_last": losses[-1]}), flush=True)
+        net.deinit()
+        dx.free()
+        dt.free()
+    be.deinit()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="wide_mlp_dp", choices=["wide_mlp_dp", "gemm_sweep"])
+    ap.add_argument("--workload", default="wide_mlp_dp", choices=["wide_mlp_dp", "gemm_sweep", "mlp784", "wide_mlp_sgd"])
     ap.add_argument("--sizes", default="1024x1024x1024,4096x4096x4096,8192x8192x8192,65536x512x512")
     ap.add_argument("--precisions", default="bf16,tf32,fp32")
     ap.add_argument("--gpus", type=int, default=1)
@@ -390,6 +442,8 @@ def main():
         args.warmup = 3
     if args.workload == "gemm_sweep":
         run_gemm_sweep(args)
+    elif args.workload in ("mlp784", "wide_mlp_sgd"):
+        run_other_config(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -140,6 +140,41 @@ __global__ void sgd_kernel(zn_opt_args a, int is_bias) {
     }
 }
 
+__device__ __forceinline__ void sgd_one(const zn_opt_args &a, float f, int is_bias, float &g, float &w) {
+    if (f != 1.0f) g = __fmul_rn(g, f);
+    const float gc = clamp_grad(g);
+    if (is_bias) w = __fsub_rn(w, __fmul_rn(a.lr, gc));
+    else w = __fsub_rn(w, __fmul_rn(a.lr, __fadd_rn(gc, __fmul_rn(a.wd, w))));
+    w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+}
+
+// Four parameters per thread, 16-byte streaming accesses (same conditions as adam_vec4_kernel).
+template <typename ST>
+__global__ void sgd_vec4_kernel(zn_opt_args a, int is_bias) {
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const bool write_g = f != 1.0f;
+    const size_t n4 = a.count / 4;
+    float4 *W = reinterpret_cast<float4 *>(a.w), *G = reinterpret_cast<float4 *>(a.g);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 g = __ldcs(&G[i]), w = __ldcs(&W[i]);
+        sgd_one(a, f, is_bias, g.x, w.x);
+        sgd_one(a, f, is_bias, g.y, w.y);
+        sgd_one(a, f, is_bias, g.z, w.z);
+        sgd_one(a, f, is_bias, g.w, w.w);
+        if (write_g) __stcs(&G[i], g);
+        __stcs(&W[i], w);
+        if (a.shadow) {
+            if (sizeof(ST) == 2) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+                reinterpret_cast<uint2 *>(a.shadow)[i] =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+            } else {
+                reinterpret_cast<float4 *>(a.shadow)[i] = w;
+            }
+        }
+    }
+}
+
 // cpuAdamUpdate, src/backend.zig:2760-2772, with Adam.step's L2 term (src/optimizer.zig:221-228) folded in.
 __device__ __forceinline__ void adam_one(const zn_opt_args &a, float f, float omb1, float omb2, float &g, float &w,
                                          float &m, float &v) {
@@ -229,6 +264,8 @@ void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
     cudaFuncSetAttribute(scale_kernel, at, c);
     cudaFuncSetAttribute(sgd_kernel<float>, at, c);
     cudaFuncSetAttribute(sgd_kernel<__nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(sgd_vec4_kernel<float>, at, c);
+    cudaFuncSetAttribute(sgd_vec4_kernel<__nv_bfloat16>, at, c);
     cudaFuncSetAttribute(adam_kernel<float>, at, c);
     cudaFuncSetAttribute(adam_kernel<__nv_bfloat16>, at, c);
     cudaFuncSetAttribute(adam_vec4_kernel<float>, at, c);
@@ -351,6 +388,16 @@ zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev) {
 
 zn_status zn_k_sgd(zn_ctx *ctx, const zn_opt_args &a, bool is_bias) {
     zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, (12.0 + (a.shadow ? (a.shadow_bf16 ? 2 : 4) : 0)) * a.count);
+    auto aligned = [](const void *p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; };
+    const bool vec4 = a.count % 4 == 0 && a.count >= 4096 && aligned(a.w, 16) && aligned(a.g, 16) &&
+                      (!a.shadow || (a.ld_shadow == a.cols && aligned(a.shadow, a.shadow_bf16 ? 8 : 16)));
+    if (vec4) {
+        const int grid = grid_for(ctx, a.count / 4);
+        if (a.shadow && a.shadow_bf16) sgd_vec4_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(a, is_bias ? 1 : 0);
+        else sgd_vec4_kernel<float><<<grid, TPB, 0, ctx->stream>>>(a, is_bias ? 1 : 0);
+        ZN_CUDA(ctx, cudaGetLastError());
+        return ZN_OK;
+    }
     if (a.shadow && a.shadow_bf16) sgd_kernel<__nv_bfloat16><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a, is_bias ? 1 : 0);
     else sgd_kernel<float><<<grid_for(ctx, a.count), TPB, 0, ctx->stream>>>(a, is_bias ? 1 : 0);
     ZN_CUDA(ctx, cudaGetLastError());
