@@ -217,6 +217,18 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int &tm
     tn = r / rows;
 }
 
+// 256-bit global accesses (sm_100): one full 32-byte sector per thread and instruction.
+__device__ __forceinline__ void st_global_v8(void *p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+__device__ __forceinline__ void ld_global_v8(const void *p, uint32_t (&w)[8]) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+}
+
 // Fused epilogue for 32 consecutive columns of one output row held by this thread:
 // bias, activation, activation-derivative mask, accumulate, stores (fp32 and/or operand type).
 template <bool TF32>
@@ -246,7 +258,19 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
     if (p.mask) {
         if (t_bf16) {
             const __nv_bfloat16 *mrow = static_cast<const __nv_bfloat16 *>(p.mask) + row * p.ld_mask + col0;
-            if (valid == 32 && ((reinterpret_cast<uintptr_t>(mrow) & 15) == 0)) {
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(mrow) & 31) == 0)) {
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t w[8];
+                    ld_global_v8(mrow + g * 16, w);
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) {
+                        const uint32_t lo = w[h] & 0xFFFFu, hi = w[h] >> 16;
+                        if (!(lo != 0u && lo < 0x8000u)) v[g * 16 + h * 2] = 0.f;
+                        if (!(hi != 0u && hi < 0x8000u)) v[g * 16 + h * 2 + 1] = 0.f;
+                    }
+                }
+            } else if (valid == 32 && ((reinterpret_cast<uintptr_t>(mrow) & 15) == 0)) {
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     const uint4 u = *reinterpret_cast<const uint4 *>(mrow + g * 8);
@@ -279,7 +303,15 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
             for (int j = 0; j < 32; ++j)
                 if (j < valid) v[j] += orow[j];
         }
-        if (vec) {
+        if (vec && ((reinterpret_cast<uintptr_t>(orow) & 31) == 0)) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t w[8];
+#pragma unroll
+                for (int h = 0; h < 8; ++h) w[h] = __float_as_uint(v[g * 8 + h]);
+                st_global_v8(orow + g * 8, w);
+            }
+        } else if (vec) {
 #pragma unroll
             for (int g = 0; g < 8; ++g)
                 *reinterpret_cast<float4 *>(orow + g * 4) =
@@ -293,7 +325,19 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
     if (p.out_t) {
         if (t_bf16) {
             __nv_bfloat16 *orow = static_cast<__nv_bfloat16 *>(p.out_t) + row * p.ld_out_t + col0;
-            if (valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0)) {
+            if (valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 31) == 0)) {
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) {
+                        const __nv_bfloat162 b2 =
+                            __floats2bfloat162_rn(v[g * 16 + h * 2], v[g * 16 + h * 2 + 1]);
+                        w[h] = *reinterpret_cast<const uint32_t *>(&b2);
+                    }
+                    st_global_v8(orow + g * 16, w);
+                }
+            } else if (valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0)) {
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     uint32_t w[4];
