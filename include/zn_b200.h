@@ -214,6 +214,12 @@ ZN_API zn_status zn_net_train(zn_net *net, const float *inputs, const float *tar
                               size_t epochs, float learning_rate, zn_loss loss, float *epoch_loss);
 /* Norm and clip factor of the last step (host floats, may be NULL). */
 ZN_API zn_status zn_net_last_clip(zn_net *net, float *norm_out, float *factor_out);
+/* Network.save / Network.load, src/network.zig:692-745 -> saveModel / loadModel, src/serialization.zig:78-147:
+ * the reference's .znn file ("ZNN\0", version 1, layer count, then per Dense layer type 1, input size, output
+ * size, activation tag, weights, bias; little-endian; no optimizer state).  Files written by either side load
+ * in the other as long as every layer is Dense. */
+ZN_API zn_status zn_net_save(zn_net *net, const char *path);
+ZN_API zn_status zn_net_load(zn_ctx *ctx, zn_precision precision, const char *path, zn_net **out);
 /* Pinned host memory for the pipelined step's inputs. */
 ZN_API zn_status zn_host_alloc(zn_ctx *ctx, size_t count, float **out_host);
 ZN_API zn_status zn_host_free(zn_ctx *ctx, float *host);

@@ -240,3 +240,34 @@ def test_shape_errors(be):
     net.addDense(8, 2, "linear")
     with pytest.raises(zn.ZnError):
         net.trainStep(np.zeros((2, 4), np.float32), np.zeros((2, 2), np.float32), 0.1, zn.Loss.kl_divergence)
+
+
+def test_znn_save_and_load(be, tmp_path):
+    """The reference's .znn layout (src/serialization.zig:1-22, :165-183): "ZNN\\0", u32 version 1, u32 layer count,
+    then per Dense layer u32 type 1, u32 in, u32 out, u32 activation tag, f32 weights, f32 bias, little-endian."""
+    import struct
+    rng = np.random.default_rng(6)
+    dims, acts = [(5, 7), (7, 3)], ["relu", "linear"]
+    gnet, onet = build_pair(be, P.FP32_SIMT, dims, acts, seed=6, bias_scale=0.3)
+    path = str(tmp_path / "model.znn")
+    gnet.save(path)
+    want = b"ZNN\x00" + struct.pack("<II", 1, 2)
+    for i, ((a, b), act) in enumerate(zip(dims, acts)):
+        W, bias = onet.get_params(i)
+        want += struct.pack("<IIII", 1, a, b, int(zn.Activation[act])) + W.astype("<f4").tobytes() + bias.astype("<f4").tobytes()
+    assert open(path, "rb").read() == want
+    for prec in (P.FP32_SIMT, P.BF16_TC):
+        back = zn.Network.load(be, path, prec)
+        assert back.shapes == dims
+        for i in range(2):
+            assert np.array_equal(back.getWeights(i)[0], gnet.getWeights(i)[0])
+            assert np.array_equal(back.getWeights(i)[1], gnet.getWeights(i)[1])
+        x = rng.standard_normal((4, 5)).astype(np.float32)
+        assert_close(back.forward(x), onet.forward(x, 4), 1e-5 if prec == P.FP32_SIMT else 2e-2, "loaded forward")
+    bad = tmp_path / "bad.znn"
+    bad.write_bytes(b"NOPE" + want[4:])
+    with pytest.raises(zn.ZnError):
+        zn.Network.load(be, str(bad))
+    bad.write_bytes(want[:-5])
+    with pytest.raises(zn.ZnError):
+        zn.Network.load(be, str(bad))

@@ -198,6 +198,115 @@ void launch(zn_ctx *ctx, const float *a, int64_t lda, const float *b, int64_t ld
     else gemm_simt_kernel<A_KC, B_NC, false><<<grid, THREADS, 0, ctx->stream>>>(a, lda, b, ldb, m, n, k, ep);
 }
 
+// ---- small-tile variant ------------------------------------------------------------------------------
+// 64 x 64 tiles, 4 x 4 outputs per thread.  Same arithmetic and the same k order per element as the kernel
+// above; used when the 128 x 128 grid would leave most SMs idle (the layers of small networks).
+constexpr int SM_T = 64;
+
+template <bool KC /* source contiguous along k */>
+__device__ __forceinline__ void load4(const float *__restrict__ src, int64_t ld, int64_t mn0, int64_t k0, int64_t MN,
+                                      int64_t K, int t, bool vec_ok, float (&r)[4]) {
+    // KC:  the tile is [64 mn][16 k], thread -> (mn = t & 63, k = (t >> 6) * 4 .. +3), element (mn, k) at src[mn * ld + k]
+    // !KC: the tile is [16 k][64 mn], thread -> (k = t >> 4, mn = (t & 15) * 4 .. +3), element (mn, k) at src[k * ld + mn]
+    if (KC) {
+        const int64_t gmn = mn0 + (t & 63), gk = k0 + (t >> 6) * 4;
+        const float *p = src + gmn * ld + gk;
+        if (gmn < MN && gk + 4 <= K && vec_ok) {
+            const float4 v = *reinterpret_cast<const float4 *>(p);
+            r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[i] = (gmn < MN && gk + i < K) ? p[i] : 0.f;
+        }
+    } else {
+        const int64_t gk = k0 + (t >> 4), gmn = mn0 + (t & 15) * 4;
+        const float *p = src + gk * ld + gmn;
+        if (gk < K && gmn + 4 <= MN && vec_ok) {
+            const float4 v = *reinterpret_cast<const float4 *>(p);
+            r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[i] = (gk < K && gmn + i < MN) ? p[i] : 0.f;
+        }
+    }
+}
+
+template <bool A_KC, bool B_NC, bool EXACT>
+__global__ void __launch_bounds__(THREADS)
+gemm_simt_small_kernel(const float *__restrict__ a, int64_t lda, const float *__restrict__ b, int64_t ldb,
+                       int64_t M, int64_t N, int64_t K, Epi ep) {
+    __shared__ __align__(16) float As[BK][SM_T];
+    __shared__ __align__(16) float Bs[BK][SM_T];
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const int64_t m0 = (int64_t)blockIdx.y * SM_T, n0 = (int64_t)blockIdx.x * SM_T;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t r = m0 + ty * 4 + i, c = n0 + tx * 4 + j;
+            acc[i][j] = (ep.acc_init && r < M && c < N) ? ep.out[r * ep.ld_out + c] : 0.f;
+        }
+    const bool a_vec = ((reinterpret_cast<uintptr_t>(a) & 15) == 0) && (lda % 4 == 0);
+    const bool b_vec = ((reinterpret_cast<uintptr_t>(b) & 15) == 0) && (ldb % 4 == 0);
+
+    for (int64_t k0 = 0; k0 < K; k0 += BK) {
+        float ra[4], rb[4];
+        load4<A_KC>(a, lda, m0, k0, M, K, t, a_vec, ra);
+        load4<!B_NC>(b, ldb, n0, k0, N, K, t, b_vec, rb);     // B is contiguous along k exactly when it is not along n
+        __syncthreads();
+        if (A_KC) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) As[(t >> 6) * 4 + i][t & 63] = ra[i];
+        } else {
+            *reinterpret_cast<float4 *>(&As[t >> 4][(t & 15) * 4]) = make_float4(ra[0], ra[1], ra[2], ra[3]);
+        }
+        if (!B_NC) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Bs[(t >> 6) * 4 + i][t & 63] = rb[i];
+        } else {
+            *reinterpret_cast<float4 *>(&Bs[t >> 4][(t & 15) * 4]) = make_float4(rb[0], rb[1], rb[2], rb[3]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 a4 = *reinterpret_cast<const float4 *>(&As[kk][ty * 4]);
+            const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = mac<EXACT>(acc[i][j], av[i], bv[j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t r = m0 + ty * 4 + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t c = n0 + tx * 4 + j;
+            if (c >= N) continue;
+            float v = acc[i][j];
+            if (ep.bias) v = __fadd_rn(v, ep.bias[c]);
+            v = apply_act(ep.act, v);
+            if (ep.mask) v = ep.mask[r * ep.ld_mask + c] > 0.f ? v : 0.f;
+            float *dst = ep.out + r * ep.ld_out + c;
+            if (ep.accumulate) v = __fadd_rn(*dst, v);
+            *dst = v;
+        }
+    }
+}
+
+template <bool A_KC, bool B_NC>
+void launch_small(zn_ctx *ctx, const float *a, int64_t lda, const float *b, int64_t ldb, int64_t m, int64_t n, int64_t k,
+                  const Epi &ep, bool exact) {
+    dim3 grid((unsigned)((n + SM_T - 1) / SM_T), (unsigned)((m + SM_T - 1) / SM_T));
+    if (exact) gemm_simt_small_kernel<A_KC, B_NC, true><<<grid, THREADS, 0, ctx->stream>>>(a, lda, b, ldb, m, n, k, ep);
+    else gemm_simt_small_kernel<A_KC, B_NC, false><<<grid, THREADS, 0, ctx->stream>>>(a, lda, b, ldb, m, n, k, ep);
+}
+
 }   // namespace
 
 zn_status zn_gemm_simt(zn_ctx *ctx, const float *a, int64_t a_rs, int64_t a_cs, const float *b, int64_t b_rs,
@@ -212,6 +321,16 @@ zn_status zn_gemm_simt(zn_ctx *ctx, const float *a, int64_t a_rs, int64_t a_cs, 
     if (e.accumulate && a_kc && b_nc && !e.bias && e.act == ZN_ACT_LINEAR && !e.mask) { ep.acc_init = 1; ep.accumulate = 0; }
     const int64_t lda = a_kc ? a_rs : a_cs, ldb = b_nc ? b_rs : b_cs;
     zn_launch_scope scope(ctx, ZN_PROF_GEMM_SIMT, 2.0 * m * n * k, 4.0 * (m * k + k * n + m * n));
+    // few large tiles would leave most of the machine idle: use 64 x 64 tiles then
+    const int64_t big_tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    if (big_tiles < 2 * (int64_t)ctx->sm_count && (m + SM_T - 1) / SM_T <= 65535) {
+        if (a_kc && b_nc) launch_small<true, true>(ctx, a, lda, b, ldb, m, n, k, ep, exact);
+        else if (a_kc && !b_nc) launch_small<true, false>(ctx, a, lda, b, ldb, m, n, k, ep, exact);
+        else if (!a_kc && b_nc) launch_small<false, true>(ctx, a, lda, b, ldb, m, n, k, ep, exact);
+        else launch_small<false, false>(ctx, a, lda, b, ldb, m, n, k, ep, exact);
+        ZN_CUDA(ctx, cudaGetLastError());
+        return ZN_OK;
+    }
     if (a_kc && b_nc) launch<true, true>(ctx, a, lda, b, ldb, m, n, k, ep, exact);
     else if (a_kc && !b_nc) launch<true, false>(ctx, a, lda, b, ldb, m, n, k, ep, exact);
     else if (!a_kc && b_nc) launch<false, true>(ctx, a, lda, b, ldb, m, n, k, ep, exact);

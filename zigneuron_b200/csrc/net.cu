@@ -694,6 +694,71 @@ extern "C" zn_status zn_net_last_clip(zn_net *n, float *norm_out, float *factor_
     return ZN_OK;
 }
 
+// ---- .znn files: Network.save / Network.load (src/network.zig:692-745) -> saveModel / loadModel
+// (src/serialization.zig:78-147).  Little-endian: "ZNN\0", u32 version = 1, u32 layer count; per Dense layer
+// u32 type = 1, u32 input size, u32 output size, u32 activation tag, f32 weights[in*out], f32 bias[out]
+// (writeLayer, :165-183).  As in the reference, optimizer state is not part of the file.
+namespace {
+constexpr uint32_t ZNN_VERSION = 1, ZNN_LAYER_DENSE = 1;
+bool put_u32(FILE *f, uint32_t v) { return fwrite(&v, 4, 1, f) == 1; }
+bool get_u32(FILE *f, uint32_t *v) { return fread(v, 4, 1, f) == 1; }
+}   // namespace
+
+extern "C" zn_status zn_net_save(zn_net *n, const char *path) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!path) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "save: null path");
+    FILE *f = fopen(path, "wb");
+    if (!f) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "save: cannot create %s", path);
+    bool ok = fwrite("ZNN\0", 1, 4, f) == 4 && put_u32(f, ZNN_VERSION) && put_u32(f, (uint32_t)n->layers.size());
+    std::vector<float> host;
+    for (size_t i = 0; i < n->layers.size() && ok; ++i) {
+        Layer &l = n->layers[i];
+        if (l.in > UINT32_MAX || l.out > UINT32_MAX) { ok = false; break; }
+        host.resize(l.len);
+        if (cudaMemcpyAsync(host.data(), l.params, l.len * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+            cudaStreamSynchronize(ctx->stream) != cudaSuccess) { ok = false; break; }
+        ok = put_u32(f, ZNN_LAYER_DENSE) && put_u32(f, (uint32_t)l.in) && put_u32(f, (uint32_t)l.out) && put_u32(f, (uint32_t)l.act) &&
+             fwrite(host.data(), sizeof(float), l.in * l.out, f) == l.in * l.out &&
+             fwrite(host.data() + l.b_off, sizeof(float), l.out, f) == l.out;
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) return zn_fail(ctx, ZN_ERR_CUDA, "save: writing %s failed", path);
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_load(zn_ctx *ctx, zn_precision precision, const char *path, zn_net **out) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!path || !out) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load: null argument");
+    *out = nullptr;
+    FILE *f = fopen(path, "rb");
+    if (!f) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "load: cannot open %s", path);
+    char magic[4];
+    uint32_t version = 0, count = 0;
+    zn_status st = ZN_OK;
+    zn_net *n = nullptr;
+    if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "ZNN\0", 4) != 0) st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "InvalidMagic: %s is not a .znn file", path);
+    else if (!get_u32(f, &version) || version != ZNN_VERSION) st = zn_fail(ctx, ZN_ERR_UNSUPPORTED, "UnsupportedVersion %u", version);
+    else if (!get_u32(f, &count) || count == 0 || count > 16) st = zn_fail(ctx, ZN_ERR_UNSUPPORTED, "layer count %u outside 1..16", count);
+    if (st == ZN_OK) st = zn_net_create(ctx, precision, &n);
+    std::vector<float> w, b;
+    for (uint32_t i = 0; i < count && st == ZN_OK; ++i) {
+        uint32_t type = 0, in = 0, o = 0, act = 0;
+        if (!get_u32(f, &type) || !get_u32(f, &in) || !get_u32(f, &o) || !get_u32(f, &act)) { st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load: truncated layer header"); break; }
+        if (type != ZNN_LAYER_DENSE) { st = zn_fail(ctx, ZN_ERR_UNSUPPORTED, "layer type %u is not Dense", type); break; }
+        if (in == 0 || o == 0 || (uint64_t)in * o > (1ull << 32)) { st = zn_fail(ctx, ZN_ERR_SHAPE, "load: layer %u has size %u x %u", i, in, o); break; }
+        w.resize((size_t)in * o);
+        b.resize(o);
+        if (fread(w.data(), sizeof(float), w.size(), f) != w.size() || fread(b.data(), sizeof(float), o, f) != o) { st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load: truncated layer data"); break; }
+        st = zn_net_add_dense(n, in, o, (zn_activation)act, nullptr);
+        if (st == ZN_OK) st = zn_net_set_weights(n, i, w.data(), b.data());
+    }
+    fclose(f);
+    if (st != ZN_OK) { zn_net_destroy(n); return st; }
+    *out = n;
+    return ZN_OK;
+}
+
 extern "C" zn_status zn_net_set_data_parallel(zn_net *n, size_t global_rows) {
     ZN_TRY(check_net(n, true));
     if (global_rows > 0 && !zn_dp_active(n->ctx))

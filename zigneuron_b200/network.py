@@ -2,6 +2,7 @@
 layers, resident on the GPU.  Names follow the reference: addDense, forward,
 trainStep, train; per-layer optimizers as in `Network.optimizers`."""
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -123,6 +124,28 @@ class Network:
         losses = np.zeros(epochs, np.float32)
         self._ck(lib.zn_net_train(self.handle, ptr(x), ptr(t), samples, epochs, learning_rate, int(loss_fn), ptr(losses)))
         return losses
+
+    # Network.save / Network.load, src/network.zig:692-745 (the reference's .znn format)
+    def save(self, path):
+        self._ck(lib.zn_net_save(self.handle, os.fsencode(path)))
+
+    @classmethod
+    def load(cls, backend, path, precision=None):
+        net = cls.__new__(cls)
+        net.backend = backend
+        net.precision = Precision(precision if precision is not None else backend.precision)
+        h = C.c_void_p()
+        check(lib.zn_net_load(backend.handle, int(net.precision), os.fsencode(path), C.byref(h)), backend.handle)
+        net.handle = h.value
+        net.shapes = []
+        with open(path, "rb") as f:
+            f.seek(8)
+            count = int.from_bytes(f.read(4), "little")
+            for _ in range(count):
+                _type, n_in, n_out, _act = (int.from_bytes(f.read(4), "little") for _ in range(4))
+                net.shapes.append((n_in, n_out))
+                f.seek(4 * (n_in * n_out + n_out), 1)
+        return net
 
     def lastClip(self):
         a, b = C.c_float(), C.c_float()
