@@ -163,6 +163,9 @@ ZN_API zn_status zn_sgd_update_bias(zn_ctx *ctx, float *bias, const float *grads
  * bias corrections are the caller's, as in Adam.step (src/optimizer.zig:210-213). */
 ZN_API zn_status zn_adam_update(zn_ctx *ctx, float *weights, const float *grads, float *m, float *v, size_t count,
                                 float lr, float beta1, float beta2, float eps, float bias_corr1, float bias_corr2);
+/* Backend.rmspropUpdate, src/backend.zig:446-456 -> cpuRmspropUpdate :2774-2783. */
+ZN_API zn_status zn_rmsprop_update(zn_ctx *ctx, float *weights, const float *grads, float *g_avg, size_t count,
+                                   float lr, float rho, float eps);
 /* The global gradient-norm clip of Network.trainStep, src/network.zig:513-535,
  * over `tensor_count` gradient tensors in the order given (device or host
  * pointers, all of one kind).  norm_out / factor_out are host floats (may be NULL). */
@@ -191,6 +194,15 @@ ZN_API zn_status zn_net_get_input_grad(zn_net *net, float *grad_input, size_t co
  * layer = -1 sets every layer.  Sgd.step :160-164, Adam.step :209-233. */
 ZN_API zn_status zn_net_set_sgd(zn_net *net, int32_t layer, float weight_decay);
 ZN_API zn_status zn_net_set_adam(zn_net *net, int32_t layer, float beta1, float beta2, float eps, float weight_decay);
+/* Sgd{ .momentum > 0 }, src/optimizer.zig:96-104 (velocity tensors) and Sgd.step :114-159:
+ * v = momentum*v - lr*g; w = w + v, without the clamps of the plain SGD path. */
+ZN_API zn_status zn_net_set_sgd_momentum(zn_net *net, int32_t layer, float momentum);
+/* AdamW, src/optimizer.zig:236-297: Adam.step's update without the L2 term, then the
+ * decoupled decay w *= 1 - lr*weight_decay on weights and bias. */
+ZN_API zn_status zn_net_set_adamw(zn_net *net, int32_t layer, float beta1, float beta2, float eps, float weight_decay);
+/* Rmsprop, src/optimizer.zig:300-359: optional L2 term added to the gradients, then
+ * Backend.rmspropUpdate on weights and bias. */
+ZN_API zn_status zn_net_set_rmsprop(zn_net *net, int32_t layer, float rho, float eps, float weight_decay);
 /* Network.forward, src/network.zig:309-386, on a block of `rows` samples. */
 ZN_API zn_status zn_net_forward(zn_net *net, const float *input, size_t rows, float *output);
 /* Network.trainStep, src/network.zig:481-579, on a block of `rows` samples:

@@ -37,7 +37,7 @@ enum { ZO_RELU = 0, ZO_SIGMOID = 1, ZO_TANH = 2, ZO_SOFTMAX = 3, ZO_LINEAR = 4,
        ZO_GELU = 5, ZO_LEAKY_RELU = 6, ZO_ELU = 7 };
 /* Loss tags: order of `Loss` in src/loss.zig:12-22. */
 enum { ZO_MSE = 0, ZO_CE = 1, ZO_CE_LOGITS = 2, ZO_BCE = 3, ZO_KL = 4 };
-enum { ZO_OPT_SGD = 0, ZO_OPT_ADAM = 1 };
+enum { ZO_OPT_SGD = 0, ZO_OPT_ADAM = 1, ZO_OPT_MOMENTUM = 2, ZO_OPT_ADAMW = 3, ZO_OPT_RMSPROP = 4 };
 
 /* ------------------------------------------------------------------ GEMMs */
 
@@ -269,6 +269,33 @@ ZO_API void zo_adam_bias_corrections(float beta1, float beta2, size_t t, float *
     *bc2 = 1.0f - powf(beta2, tf);
 }
 
+/* src/backend.zig:2774-2783 (cpuRmspropUpdate). */
+ZO_API void zo_rmsprop_update(float *w, const float *g_raw, float *g_avg, size_t n, float lr, float rho, float eps) {
+    for (size_t i = 0; i < n; ++i) {
+        const float g = clamp_grad(g_raw[i]);
+        g_avg[i] = rho * g_avg[i] + (1.0f - rho) * g * g;
+        w[i] -= lr * g / (sqrtf(g_avg[i]) + eps);
+        w[i] = fminf(100.0f, fmaxf(-100.0f, w[i]));
+    }
+}
+
+/* Sgd.step with momentum > 0, src/optimizer.zig:114-159: v = momentum*v - lr*g; w = w + v, built from
+ * Backend.scale and Backend.elementWise, so without the gradient or weight clamps of the plain path. */
+ZO_API void zo_sgd_momentum_update(float *w, const float *g, float *vel, size_t n, float lr, float momentum) {
+    for (size_t i = 0; i < n; ++i) {
+        const float scaled_v = vel[i] * momentum;
+        const float scaled_g = g[i] * lr;
+        vel[i] = scaled_v - scaled_g;
+        w[i] = w[i] + vel[i];
+    }
+}
+
+/* The decoupled decay AdamW.step applies after adamUpdate, src/optimizer.zig:288-296. */
+ZO_API void zo_decoupled_decay(float *w, size_t n, float lr, float weight_decay) {
+    const float wdlr = lr * weight_decay;
+    for (size_t i = 0; i < n; ++i) w[i] = w[i] * (1.0f - wdlr);
+}
+
 /* Global gradient-norm clip of Network.trainStep, src/network.zig:513-535:
  * one running f32 sum over every tensor in the order given, sqrt, and when
  * the norm exceeds 1.0 every gradient is multiplied by 1/(norm + 1e-6).
@@ -308,7 +335,7 @@ typedef struct {
     float *x_cache, *y_cache;          /* LayerCache, src/network.zig:33-36 */
     size_t cache_rows;
     int opt;                           /* Network.optimizers[i], src/network.zig:44 */
-    float beta1, beta2, eps, wd;
+    float beta1, beta2, eps, wd, momentum, rho;
     size_t t;
     float *mW, *vW, *mb, *vb;          /* Adam state, src/optimizer.zig:169-184 */
 } zo_layer;
@@ -387,6 +414,35 @@ ZO_API void zo_net_set_adam(zo_net *net, size_t layer, float beta1, float beta2,
     l->vW = (float *)calloc(l->in * l->out, sizeof(float));
     l->mb = (float *)calloc(l->out, sizeof(float));
     l->vb = (float *)calloc(l->out, sizeof(float));
+}
+
+static void alloc_state(zo_layer *l, int two) {
+    free(l->mW); free(l->vW); free(l->mb); free(l->vb);
+    l->mW = (float *)calloc(l->in * l->out, sizeof(float));
+    l->mb = (float *)calloc(l->out, sizeof(float));
+    l->vW = two ? (float *)calloc(l->in * l->out, sizeof(float)) : NULL;
+    l->vb = two ? (float *)calloc(l->out, sizeof(float)) : NULL;
+}
+
+/* Sgd{ .momentum = m } with its velocity tensors, src/optimizer.zig:96-104. */
+ZO_API void zo_net_set_sgd_momentum(zo_net *net, size_t layer, float momentum) {
+    zo_layer *l = &net->layers[layer];
+    l->opt = ZO_OPT_MOMENTUM; l->momentum = momentum;
+    alloc_state(l, 0);
+}
+
+/* AdamW, src/optimizer.zig:236-297. */
+ZO_API void zo_net_set_adamw(zo_net *net, size_t layer, float beta1, float beta2, float eps, float weight_decay) {
+    zo_layer *l = &net->layers[layer];
+    l->opt = ZO_OPT_ADAMW; l->beta1 = beta1; l->beta2 = beta2; l->eps = eps; l->wd = weight_decay; l->t = 0;
+    alloc_state(l, 1);
+}
+
+/* Rmsprop, src/optimizer.zig:300-345. */
+ZO_API void zo_net_set_rmsprop(zo_net *net, size_t layer, float rho, float eps, float weight_decay) {
+    zo_layer *l = &net->layers[layer];
+    l->opt = ZO_OPT_RMSPROP; l->rho = rho; l->eps = eps; l->wd = weight_decay;
+    alloc_state(l, 0);
 }
 
 static void ensure_cache(zo_layer *l, size_t rows) {
@@ -511,6 +567,24 @@ static void net_apply_optimizers(zo_net *net, float lr) {
             }
             zo_adam_update(l->W, l->gW, l->mW, l->vW, nw, lr, l->beta1, l->beta2, l->eps, bc1, bc2);
             zo_adam_update(l->b, l->gb, l->mb, l->vb, l->out, lr, l->beta1, l->beta2, l->eps, bc1, bc2);
+        } else if (l->opt == ZO_OPT_ADAMW) {
+            l->t += 1;
+            float bc1, bc2;
+            zo_adam_bias_corrections(l->beta1, l->beta2, l->t, &bc1, &bc2);
+            zo_adam_update(l->W, l->gW, l->mW, l->vW, nw, lr, l->beta1, l->beta2, l->eps, bc1, bc2);
+            zo_adam_update(l->b, l->gb, l->mb, l->vb, l->out, lr, l->beta1, l->beta2, l->eps, bc1, bc2);
+            zo_decoupled_decay(l->W, nw, lr, l->wd);
+            zo_decoupled_decay(l->b, l->out, lr, l->wd);
+        } else if (l->opt == ZO_OPT_RMSPROP) {
+            if (l->wd > 0.0f) {
+                for (size_t j = 0; j < nw; ++j) l->gW[j] += l->wd * l->W[j];
+                for (size_t j = 0; j < l->out; ++j) l->gb[j] += l->wd * l->b[j];
+            }
+            zo_rmsprop_update(l->W, l->gW, l->mW, nw, lr, l->rho, l->eps);
+            zo_rmsprop_update(l->b, l->gb, l->mb, l->out, lr, l->rho, l->eps);
+        } else if (l->opt == ZO_OPT_MOMENTUM) {
+            zo_sgd_momentum_update(l->W, l->gW, l->mW, nw, lr, l->momentum);
+            zo_sgd_momentum_update(l->b, l->gb, l->mb, l->out, lr, l->momentum);
         } else {
             zo_sgd_update(l->W, l->gW, nw, lr, l->wd);
             zo_sgd_update_bias(l->b, l->gb, l->out, lr);

@@ -69,6 +69,11 @@ def load():
         "zo_net_set_grads": (None, [vp, sz, _f32p, _f32p]),
         "zo_net_set_sgd": (None, [vp, sz, f]),
         "zo_net_set_adam": (None, [vp, sz, f, f, f, f]),
+        "zo_net_set_adamw": (None, [vp, sz, f, f, f, f]),
+        "zo_net_set_sgd_momentum": (None, [vp, sz, f]),
+        "zo_net_set_rmsprop": (None, [vp, sz, f, f, f]),
+        "zo_rmsprop_update": (None, [_f32p, _f32p, _f32p, sz, f, f, f]),
+        "zo_sgd_momentum_update": (None, [_f32p, _f32p, _f32p, sz, f, f]),
         "zo_net_forward": (None, [vp, _f32p, sz, _f32p]),
         "zo_net_train_step": (f, [vp, _f32p, _f32p, sz, f, i]),
         "zo_net_shard_gradients": (f, [vp, _f32p, _f32p, sz, sz, i]),
@@ -166,6 +171,18 @@ def adam_update(w, g, m, v, lr, beta1, beta2, eps, bc1, bc2):
     return w, m, v
 
 
+def rmsprop_update(w, g, g_avg, lr, rho, eps):
+    w, ga = _c(w).copy(), _c(g_avg).copy()
+    load().zo_rmsprop_update(w.reshape(-1), _c(g).reshape(-1), ga.reshape(-1), w.size, lr, rho, eps)
+    return w, ga
+
+
+def sgd_momentum_update(w, g, vel, lr, momentum):
+    w, v = _c(w).copy(), _c(vel).copy()
+    load().zo_sgd_momentum_update(w.reshape(-1), _c(g).reshape(-1), v.reshape(-1), w.size, lr, momentum)
+    return w, v
+
+
 def clip_grad_norm(grads):
     """grads: list of float32 arrays, scaled IN PLACE; returns (norm, factor)."""
     lib = load()
@@ -226,6 +243,15 @@ class Net:
 
     def set_adam(self, layer, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
         self._lib.zo_net_set_adam(self._h, layer, beta1, beta2, eps, weight_decay)
+
+    def set_adamw(self, layer, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01):
+        self._lib.zo_net_set_adamw(self._h, layer, beta1, beta2, eps, weight_decay)
+
+    def set_sgd_momentum(self, layer, momentum):
+        self._lib.zo_net_set_sgd_momentum(self._h, layer, momentum)
+
+    def set_rmsprop(self, layer, rho=0.9, eps=1e-8, weight_decay=0.0):
+        self._lib.zo_net_set_rmsprop(self._h, layer, rho, eps, weight_decay)
 
     def forward(self, x, rows):
         out = np.empty(rows * self.shapes[-1][1], np.float32)

@@ -115,6 +115,72 @@ def test_mlp_784_adam(be, prec, loss_tol, w_tol, steps):
         assert np.abs(b - ob).max() <= 2.2 * steps * 1e-3
 
 
+OTHER_OPTIMIZERS = {
+    "momentum": (zn.Sgd(momentum=0.9), lambda o, i: o.set_sgd_momentum(i, 0.9), 0.05),
+    "adamw": (zn.AdamW(weight_decay=0.05), lambda o, i: o.set_adamw(i, 0.9, 0.999, 1e-8, 0.05), 1e-3),
+    "rmsprop": (zn.Rmsprop(), lambda o, i: o.set_rmsprop(i, 0.9, 1e-8, 0.0), 1e-3),
+    "rmsprop_l2": (zn.Rmsprop(rho=0.8, weight_decay=0.01), lambda o, i: o.set_rmsprop(i, 0.8, 1e-8, 0.01), 1e-3),
+}
+
+
+@pytest.mark.parametrize("name", list(OTHER_OPTIMIZERS))
+@pytest.mark.parametrize("prec", [P.FP32_EXACT, P.FP32_SIMT, P.BF16_TC])
+def test_other_optimizers(be, name, prec):
+    """Momentum SGD, AdamW and RMSprop (src/optimizer.zig:114-159, :236-297, :300-359) through whole training
+    steps of a 64-96-48-8 network; FP32_EXACT follows the oracle to rounding, the others to their GEMM
+    precision plus the optimizer's own amplification (a sign-like update moves a weight by about lr)."""
+    gopt, oset, lr = OTHER_OPTIMIZERS[name]
+    rng = np.random.default_rng(5)
+    B, dims, acts = 128, [(64, 96), (96, 48), (48, 8)], ["relu", "tanh", "linear"]
+    x = rng.standard_normal((B, 64)).astype(np.float32)
+    t = rng.standard_normal((B, 8)).astype(np.float32)
+    gnet, onet = build_pair(be, prec, dims, acts, seed=5, bias_scale=0.1)
+    gnet.setOptimizer(gopt)
+    for i in range(3):
+        oset(onet, i)
+    steps = 4
+    for step in range(steps):
+        lg = gnet.trainStep(x, t, lr, zn.Loss.mse)
+        lo = onet.train_step(x, t, B, lr, zo.MSE)
+        ltol = 1e-5 if prec != P.BF16_TC else 2e-2
+        assert abs(lg - lo) <= ltol * max(1.0, abs(lo)), (name, step, lg, lo)
+    adaptive = name != "momentum"
+    for i in range(3):
+        W, b = gnet.getWeights(i)
+        oW, ob = onet.get_params(i)
+        if prec == P.FP32_EXACT:
+            # tanhf differs from the host libm in the last place; a sign-like update amplifies that
+            wtol = 1e-5 if adaptive else 1e-6
+            assert rel_l2(W, oW) <= wtol and rel_l2(b, ob) <= 1e-5, (name, i, rel_l2(W, oW), rel_l2(b, ob))
+        elif prec == P.FP32_SIMT:
+            assert rel_l2(W, oW) <= (2e-3 if adaptive else 1e-5), (name, i, rel_l2(W, oW))
+        else:
+            assert rel_l2(W, oW) <= 2e-2, (name, i, rel_l2(W, oW))
+        if adaptive:    # no weight can be further off than `steps` opposite moves of the largest step size
+            bound = 2.2 * steps * lr * (1.0 if name == "adamw" else 1.0 / np.sqrt(1.0 - 0.9))
+            assert np.abs(W - oW).max() <= bound and np.abs(b - ob).max() <= bound
+
+
+def test_optimizer_can_be_switched(be):
+    """Changing a layer's optimizer resets its state (src/network.zig:117 replaces the union value)."""
+    rng = np.random.default_rng(6)
+    B, dims, acts = 32, [(16, 24), (24, 4)], ["relu", "linear"]
+    x = rng.standard_normal((B, 16)).astype(np.float32)
+    t = rng.standard_normal((B, 4)).astype(np.float32)
+    gnet, onet = build_pair(be, P.FP32_EXACT, dims, acts, seed=6)
+    gnet.setOptimizer(zn.Rmsprop())
+    for i in range(2):
+        onet.set_rmsprop(i, 0.9, 1e-8, 0.0)
+    gnet.trainStep(x, t, 1e-3, zn.Loss.mse)
+    onet.train_step(x, t, B, 1e-3, zo.MSE)
+    gnet.setOptimizer(zn.Sgd(momentum=0.5), layer=1)
+    onet.set_sgd_momentum(1, 0.5)
+    for _ in range(2):
+        gnet.trainStep(x, t, 1e-2, zn.Loss.mse)
+        onet.train_step(x, t, B, 1e-2, zo.MSE)
+    compare_params(gnet, onet, 1e-5, "switched")
+
+
 def test_clip_factor_deviation_is_the_oracles_sum(be):
     """The reference adds 5e5 squared gradients into one f32 (src/network.zig:516-521); that sum is off by
     about 1e-4.  The GPU norm (block partials, combined in double) agrees with float64 to 1e-6 and so

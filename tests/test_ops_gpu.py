@@ -249,6 +249,27 @@ def test_optimizers(be):
     assert abs(w1[0] - 0.499) < 1e-6
 
 
+def test_rmsprop_update(be):
+    """Backend.rmspropUpdate (src/backend.zig:446-456, :2774-2783): bit-exact, NaN and clamp cases included,
+    on a length that takes the scalar kernel and one that takes the 16-byte kernel."""
+    rng = np.random.default_rng(19)
+    for n in (100003, 1 << 16):
+        w = rng.standard_normal(n).astype(np.float32) * 40
+        g = rng.standard_normal(n).astype(np.float32) * 4
+        g[::97] = np.nan
+        g[5::101] = 77.0
+        ga = np.abs(rng.standard_normal(n)).astype(np.float32) * 0.01
+        for lr, rho, eps in [(1e-3, 0.9, 1e-8), (0.5, 0.5, 1e-3)]:
+            ww, gg = zo.rmsprop_update(w, g, ga, lr, rho, eps)
+            gw, gga = w.copy(), ga.copy()
+            be.rmspropUpdate(gw, g, gga, lr, rho, eps)
+            assert np.array_equal(gga, gg) and np.array_equal(gw, ww)
+    # known answer from the formula: w 1, g 0.1, lr 1e-3 -> 1 - 1e-4/(sqrt(1e-3)+1e-8)
+    w1, s1 = np.array([1.0], np.float32), np.zeros(1, np.float32)
+    be.rmspropUpdate(w1, np.array([0.1], np.float32), s1, 1e-3, 0.9, 1e-8)
+    assert abs(w1[0] - 0.99683772) < 1e-6 and abs(s1[0] - 1e-3) < 1e-9
+
+
 def test_clip_grad_norm(be):
     rng = np.random.default_rng(10)
     grads = [rng.standard_normal(s).astype(np.float32) for s in (20 * 4, 20, 200 * 100 + 3, 1)]

@@ -88,6 +88,38 @@ def test_optimizer_golden():
                                  case["lr"], case["beta1"], case["beta2"], case["eps"], bc1, bc2)
         assert np.allclose(w, f32(case["expected"]), atol=case["tol"], rtol=0)
         assert w[0] < case["w"][0]
+    for case in KAT["sgd_momentum"]:
+        w, vel = f32(case["w"]), np.zeros(len(case["w"]), np.float32)
+        for step in case["steps"]:
+            w, vel = zo.sgd_momentum_update(w, f32(step["g"]), vel, case["lr"], case["momentum"])
+            assert np.allclose(w, f32(step["expected"]), atol=step["tol"], rtol=0), case["cite"]
+    for case in KAT["rmsprop"]:
+        w, ga = zo.rmsprop_update(f32(case["w"]), f32(case["g"]), np.zeros(1, np.float32),
+                                  case["lr"], case["rho"], case["eps"])
+        assert np.allclose(w, f32(case["expected"]), atol=case["tol"], rtol=0), case["cite"]
+        assert np.allclose(ga, f32(case["expected_g_avg"]), rtol=1e-6)
+
+
+def test_adamw_is_adam_then_decoupled_decay():
+    """AdamW.step (src/optimizer.zig:273-297): Adam's update without the L2 term, then w *= 1 - lr*wd on
+    weights and bias alike."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((8, 5)).astype(np.float32)
+    t = rng.standard_normal((8, 3)).astype(np.float32)
+    w0 = (rng.standard_normal((5, 3)) * 0.3).astype(np.float32)
+    b0 = (rng.standard_normal(3) * 0.1).astype(np.float32)
+    lr, wd = 0.01, 0.1
+    nets = []
+    for kind in ("adam", "adamw"):
+        net = zo.Net()
+        net.add_dense(5, 3, zo.TANH)
+        net.set_params(0, w0, b0)
+        (net.set_adam(0, 0.9, 0.999, 1e-8, 0.0) if kind == "adam" else net.set_adamw(0, 0.9, 0.999, 1e-8, wd))
+        net.train_step(x, t, 8, lr, zo.MSE)
+        nets.append(net.get_params(0))
+    (wa, ba), (ww, bw) = nets
+    mul = np.float32(1.0) - np.float32(lr) * np.float32(wd)
+    assert np.array_equal(ww, wa * mul) and np.array_equal(bw, ba * mul)
 
 
 def test_three_gemm_orientations_agree():

@@ -7,6 +7,6 @@ built; there is no CPU implementation behind these classes.
 """
 from ._lib import LIB_PATH, ZnError, lib  # noqa: F401  (import = load the .so, or fail)
 from .backend import Activation, Backend, DeviceTensor, Loss, Precision  # noqa: F401
-from .network import Adam, Network, Sgd  # noqa: F401
+from .network import Adam, AdamW, Network, Rmsprop, Sgd  # noqa: F401
 
-__all__ = ["Backend", "Network", "Activation", "Loss", "Precision", "DeviceTensor", "Sgd", "Adam", "ZnError"]
+__all__ = ["Backend", "Network", "Activation", "Loss", "Precision", "DeviceTensor", "Sgd", "Adam", "AdamW", "Rmsprop", "ZnError"]

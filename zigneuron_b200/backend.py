@@ -190,6 +190,10 @@ class Backend:
         self._ck(lib.zn_adam_update(self.handle, ptr(weights), ptr(gradients), ptr(m), ptr(v), self._len(weights),
                                     lr, beta1, beta2, eps, bias_corr1, bias_corr2))
 
+    def rmspropUpdate(self, weights, gradients, g_avg, lr, rho, eps):
+        self._ck(lib.zn_rmsprop_update(self.handle, ptr(weights), ptr(gradients), ptr(g_avg), self._len(weights),
+                                       lr, rho, eps))
+
     def clipGradNorm(self, grads):
         """The clip inside Network.trainStep (src/network.zig:513-535); scales in place, returns (norm, factor)."""
         n = len(grads)

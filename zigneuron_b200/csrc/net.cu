@@ -27,6 +27,8 @@ namespace {
 
 int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+enum { OPT_SGD = 0, OPT_ADAM = 1, OPT_MOMENTUM = 2, OPT_ADAMW = 3, OPT_RMSPROP = 4 };
+
 struct Layer {
     size_t in = 0, out = 0;
     int act = ZN_ACT_LINEAR;
@@ -34,7 +36,8 @@ struct Layer {
     float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
     void *w_op = nullptr;                 // operand copy of W (tensor-core modes), null when W itself is usable
     int64_t ld_w = 0;
-    int opt = 0;                          // 0 sgd, 1 adam
+    int opt = OPT_SGD;                    // OPT_* below
+    float momentum = 0.0f, rho = 0.9f;
     float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, wd = 0.f;
     size_t t = 0;
     // ordering between the lanes of a step (see step_dev)
@@ -290,21 +293,36 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         Layer &l = n->layers[i];
         zn_opt_args a{};
         a.lr = lr; a.wd = l.wd; a.factor_dev = n->scalars + 1;
-        a.beta1 = l.beta1; a.beta2 = l.beta2; a.eps = l.eps;
-        if (l.opt == 1) {
+        a.beta1 = l.beta1; a.beta2 = l.beta2; a.eps = l.eps; a.momentum = l.momentum; a.rho = l.rho;
+        const bool adam = l.opt == OPT_ADAM || l.opt == OPT_ADAMW;
+        if (adam) {
             l.t += 1;
             const float tf = (float)l.t;
             a.bc1 = 1.0f - powf(l.beta1, tf);
             a.bc2 = 1.0f - powf(l.beta2, tf);
         }
+        if (l.opt == OPT_ADAMW) {      // decay is decoupled: nothing joins the gradient
+            const float wdlr = lr * l.wd;
+            a.wd = 0.0f;
+            a.decay_mul = 1.0f - wdlr;
+        }
+        auto update = [&](bool is_bias) -> zn_status {
+            switch (l.opt) {
+            case OPT_ADAM: case OPT_ADAMW: a.w_clamp = 100.0f; return zn_k_adam(ctx, a);
+            case OPT_MOMENTUM: return zn_k_sgd_momentum(ctx, a);
+            case OPT_RMSPROP: a.w_clamp = 100.0f; return zn_k_rmsprop(ctx, a);
+            default: a.w_clamp = is_bias ? 50.0f : 100.0f; return zn_k_sgd(ctx, a, is_bias);
+            }
+        };
         // weights
-        a.w = l.params; a.g = l.grads; a.m = l.m; a.v = l.v; a.count = l.in * l.out; a.w_clamp = 100.0f;
+        a.w = l.params; a.g = l.grads; a.m = l.m; a.v = l.v; a.count = l.in * l.out;
         a.shadow = l.w_op; a.shadow_bf16 = n->bf16; a.cols = (int64_t)l.out; a.ld_shadow = l.ld_w;
-        if (l.opt == 1) ZN_TRY(zn_k_adam(ctx, a)); else ZN_TRY(zn_k_sgd(ctx, a, false));
+        ZN_TRY(update(false));
         // bias
         a.w = l.params + l.b_off; a.g = l.grads + l.b_off; a.count = l.out; a.shadow = nullptr;
-        if (l.opt == 1) { a.m = l.m + l.b_off; a.v = l.v + l.b_off; a.w_clamp = 100.0f; ZN_TRY(zn_k_adam(ctx, a)); }
-        else { a.w_clamp = 50.0f; ZN_TRY(zn_k_sgd(ctx, a, true)); }
+        if (l.m) a.m = l.m + l.b_off;
+        if (l.v) a.v = l.v + l.b_off;
+        ZN_TRY(update(true));
         ZN_CUDA(ctx, cudaEventRecord(l.updated, s_opt));
         l.update_pending = true;
     }
@@ -539,23 +557,63 @@ extern "C" zn_status zn_net_set_sgd(zn_net *n, int32_t layer, float weight_decay
     ZN_TRY(check_net(n, true));
     size_t lo, hi;
     ZN_TRY(for_layers(n, layer, &lo, &hi));
-    for (size_t i = lo; i < hi; ++i) { n->layers[i].opt = 0; n->layers[i].wd = weight_decay; }
+    for (size_t i = lo; i < hi; ++i) { n->layers[i].opt = OPT_SGD; n->layers[i].wd = weight_decay; }
     return ZN_OK;
 }
 
-extern "C" zn_status zn_net_set_adam(zn_net *n, int32_t layer, float beta1, float beta2, float eps, float weight_decay) {
-    ZN_TRY(check_net(n, true));
+// Optimizer state blocks have the shape of the parameter block; `two` asks for the second one (Adam's v).
+static zn_status reset_state(zn_net *n, Layer &l, bool two) {
     zn_ctx *ctx = n->ctx;
+    const size_t bytes = (l.blk + 4) * sizeof(float);
+    if (!l.m) ZN_CUDA(ctx, cudaMalloc((void **)&l.m, bytes));
+    ZN_CUDA(ctx, cudaMemsetAsync(l.m, 0, bytes, ctx->stream));
+    if (two) {
+        if (!l.v) ZN_CUDA(ctx, cudaMalloc((void **)&l.v, bytes));
+        ZN_CUDA(ctx, cudaMemsetAsync(l.v, 0, bytes, ctx->stream));
+    }
+    return ZN_OK;
+}
+
+static zn_status set_adam_kind(zn_net *n, int32_t layer, int kind, float beta1, float beta2, float eps, float weight_decay) {
+    ZN_TRY(check_net(n, true));
     size_t lo, hi;
     ZN_TRY(for_layers(n, layer, &lo, &hi));
     for (size_t i = lo; i < hi; ++i) {
         Layer &l = n->layers[i];
-        l.opt = 1; l.beta1 = beta1; l.beta2 = beta2; l.eps = eps; l.wd = weight_decay; l.t = 0;
-        const size_t bytes = (l.blk + 4) * sizeof(float);
-        if (!l.m) ZN_CUDA(ctx, cudaMalloc((void **)&l.m, bytes));
-        if (!l.v) ZN_CUDA(ctx, cudaMalloc((void **)&l.v, bytes));
-        ZN_CUDA(ctx, cudaMemsetAsync(l.m, 0, bytes, ctx->stream));
-        ZN_CUDA(ctx, cudaMemsetAsync(l.v, 0, bytes, ctx->stream));
+        l.opt = kind; l.beta1 = beta1; l.beta2 = beta2; l.eps = eps; l.wd = weight_decay; l.t = 0;
+        ZN_TRY(reset_state(n, l, true));
+    }
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_set_adam(zn_net *n, int32_t layer, float beta1, float beta2, float eps, float weight_decay) {
+    return set_adam_kind(n, layer, OPT_ADAM, beta1, beta2, eps, weight_decay);
+}
+
+extern "C" zn_status zn_net_set_adamw(zn_net *n, int32_t layer, float beta1, float beta2, float eps, float weight_decay) {
+    return set_adam_kind(n, layer, OPT_ADAMW, beta1, beta2, eps, weight_decay);
+}
+
+extern "C" zn_status zn_net_set_sgd_momentum(zn_net *n, int32_t layer, float momentum) {
+    ZN_TRY(check_net(n, true));
+    size_t lo, hi;
+    ZN_TRY(for_layers(n, layer, &lo, &hi));
+    for (size_t i = lo; i < hi; ++i) {
+        Layer &l = n->layers[i];
+        l.opt = OPT_MOMENTUM; l.momentum = momentum; l.wd = 0.0f;
+        ZN_TRY(reset_state(n, l, false));
+    }
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_set_rmsprop(zn_net *n, int32_t layer, float rho, float eps, float weight_decay) {
+    ZN_TRY(check_net(n, true));
+    size_t lo, hi;
+    ZN_TRY(for_layers(n, layer, &lo, &hi));
+    for (size_t i = lo; i < hi; ++i) {
+        Layer &l = n->layers[i];
+        l.opt = OPT_RMSPROP; l.rho = rho; l.eps = eps; l.wd = weight_decay;
+        ZN_TRY(reset_state(n, l, false));
     }
     return ZN_OK;
 }

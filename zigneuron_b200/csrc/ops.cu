@@ -281,6 +281,23 @@ extern "C" zn_status zn_adam_update(zn_ctx *ctx, float *weights, const float *gr
     return finish(ctx, &W, any_host);
 }
 
+extern "C" zn_status zn_rmsprop_update(zn_ctx *ctx, float *weights, const float *grads, float *g_avg, size_t count,
+                                       float lr, float rho, float eps) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!weights || !grads || !g_avg) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "rmsprop_update: null operand");
+    if (count == 0) return ZN_OK;
+    Operand W, G, S;
+    ZN_TRY(resolve(ctx, 0, weights, count, true, &W));
+    ZN_TRY(resolve(ctx, 1, grads, count, true, &G));
+    ZN_TRY(resolve(ctx, 2, g_avg, count, true, &S));
+    zn_opt_args a{};
+    a.w = W.dev; a.g = G.dev; a.m = S.dev; a.count = count;
+    a.lr = lr; a.rho = rho; a.eps = eps; a.w_clamp = 100.0f;
+    ZN_TRY(zn_k_rmsprop(ctx, a));
+    if (S.host) ZN_CUDA(ctx, cudaMemcpyAsync(S.host, S.dev, count * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    return finish(ctx, &W, W.host || G.host || S.host);
+}
+
 extern "C" zn_status zn_clip_grad_norm(zn_ctx *ctx, float *const *grads, const size_t *counts, size_t tensor_count,
                                        float *norm_out, float *factor_out) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;

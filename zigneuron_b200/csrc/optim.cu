@@ -187,6 +187,8 @@ __device__ __forceinline__ void adam_one(const zn_opt_args &a, float f, float om
     const float v_hat = __fdiv_rn(v, a.bc2);
     w = __fsub_rn(w, __fdiv_rn(__fmul_rn(a.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), a.eps)));
     w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+    // AdamW's decoupled decay, applied to the clamped weight (src/optimizer.zig:288-296)
+    if (a.decay_mul != 0.0f) w = __fmul_rn(w, a.decay_mul);
 }
 
 // Four parameters per thread with 16-byte accesses; the host picks this variant when every pointer is
@@ -243,8 +245,74 @@ __global__ void adam_kernel(zn_opt_args a) {
         const float v_hat = __fdiv_rn(v, a.bc2);
         w = __fsub_rn(w, __fdiv_rn(__fmul_rn(a.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), a.eps)));
         w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+        if (a.decay_mul != 0.0f) w = __fmul_rn(w, a.decay_mul);
         a.w[i] = w;
         if (a.shadow) store_shadow<ST>(static_cast<ST *>(a.shadow), i, a.cols, a.ld_shadow, w);
+    }
+}
+
+// Optimizers with one state tensor (held in a.m).
+//   MOMENTUM  Sgd.step with momentum > 0 (src/optimizer.zig:114-159): v = momentum*v - lr*g; w = w + v.  The
+//             reference builds this from Backend.scale and Backend.elementWise, so neither clamp applies.
+//   RMSPROP   Rmsprop.step's L2 term (src/optimizer.zig:346-355) and cpuRmspropUpdate (src/backend.zig:2774-2783).
+enum { STATE1_MOMENTUM = 0, STATE1_RMSPROP = 1 };
+
+template <int KIND>
+__device__ __forceinline__ void state1_one(const zn_opt_args &a, float f, float omr, float &g, float &w, float &s) {
+    if (f != 1.0f) g = __fmul_rn(g, f);
+    if (KIND == STATE1_MOMENTUM) {
+        s = __fsub_rn(__fmul_rn(s, a.momentum), __fmul_rn(g, a.lr));
+        w = __fadd_rn(w, s);
+    } else {
+        if (a.wd > 0.0f) g = __fadd_rn(g, __fmul_rn(a.wd, w));
+        const float gc = clamp_grad(g);
+        s = __fadd_rn(__fmul_rn(a.rho, s), __fmul_rn(__fmul_rn(omr, gc), gc));
+        w = __fsub_rn(w, __fdiv_rn(__fmul_rn(a.lr, gc), __fadd_rn(__fsqrt_rn(s), a.eps)));
+        w = fminf(a.w_clamp, fmaxf(-a.w_clamp, w));
+    }
+}
+
+template <int KIND, typename ST>
+__global__ void state1_kernel(zn_opt_args a) {
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const bool write_g = (f != 1.0f) || (KIND == STATE1_RMSPROP && a.wd > 0.0f);
+    const float omr = 1.0f - a.rho;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.count; i += (size_t)gridDim.x * blockDim.x) {
+        float g = a.g[i], w = a.w[i], s = a.m[i];
+        state1_one<KIND>(a, f, omr, g, w, s);
+        if (write_g) a.g[i] = g;
+        a.m[i] = s;
+        a.w[i] = w;
+        if (a.shadow) store_shadow<ST>(static_cast<ST *>(a.shadow), i, a.cols, a.ld_shadow, w);
+    }
+}
+
+// Four parameters per thread, 16-byte streaming accesses (same conditions as adam_vec4_kernel).
+template <int KIND, typename ST>
+__global__ void state1_vec4_kernel(zn_opt_args a) {
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const bool write_g = (f != 1.0f) || (KIND == STATE1_RMSPROP && a.wd > 0.0f);
+    const float omr = 1.0f - a.rho;
+    const size_t n4 = a.count / 4;
+    float4 *W = reinterpret_cast<float4 *>(a.w), *G = reinterpret_cast<float4 *>(a.g), *S = reinterpret_cast<float4 *>(a.m);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 g = __ldcs(&G[i]), w = __ldcs(&W[i]), s = __ldcs(&S[i]);
+        state1_one<KIND>(a, f, omr, g.x, w.x, s.x);
+        state1_one<KIND>(a, f, omr, g.y, w.y, s.y);
+        state1_one<KIND>(a, f, omr, g.z, w.z, s.z);
+        state1_one<KIND>(a, f, omr, g.w, w.w, s.w);
+        if (write_g) __stcs(&G[i], g);
+        __stcs(&S[i], s);
+        __stcs(&W[i], w);
+        if (a.shadow) {
+            if (sizeof(ST) == 2) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+                reinterpret_cast<uint2 *>(a.shadow)[i] =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+            } else {
+                reinterpret_cast<float4 *>(a.shadow)[i] = w;
+            }
+        }
     }
 }
 
@@ -270,6 +338,14 @@ void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
     cudaFuncSetAttribute(adam_kernel<__nv_bfloat16>, at, c);
     cudaFuncSetAttribute(adam_vec4_kernel<float>, at, c);
     cudaFuncSetAttribute(adam_vec4_kernel<__nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(state1_kernel<STATE1_MOMENTUM, float>, at, c);
+    cudaFuncSetAttribute(state1_kernel<STATE1_MOMENTUM, __nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(state1_kernel<STATE1_RMSPROP, float>, at, c);
+    cudaFuncSetAttribute(state1_kernel<STATE1_RMSPROP, __nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(state1_vec4_kernel<STATE1_MOMENTUM, float>, at, c);
+    cudaFuncSetAttribute(state1_vec4_kernel<STATE1_MOMENTUM, __nv_bfloat16>, at, c);
+    cudaFuncSetAttribute(state1_vec4_kernel<STATE1_RMSPROP, float>, at, c);
+    cudaFuncSetAttribute(state1_vec4_kernel<STATE1_RMSPROP, __nv_bfloat16>, at, c);
     cudaGetLastError();
 }
 
@@ -421,3 +497,30 @@ zn_status zn_k_adam(zn_ctx *ctx, const zn_opt_args &a) {
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }
+
+namespace {
+
+template <int KIND>
+zn_status launch_state1(zn_ctx *ctx, const zn_opt_args &a) {
+    zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, (20.0 + (a.shadow ? (a.shadow_bf16 ? 2 : 4) : 0)) * a.count);
+    auto aligned = [](const void *p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; };
+    const bool vec4 = a.count % 4 == 0 && a.count >= 4096 && aligned(a.w, 16) && aligned(a.g, 16) && aligned(a.m, 16) &&
+                      (!a.shadow || (a.ld_shadow == a.cols && aligned(a.shadow, a.shadow_bf16 ? 8 : 16)));
+    const bool bf16 = a.shadow && a.shadow_bf16;
+    if (vec4) {
+        const int grid = grid_for(ctx, a.count / 4);
+        if (bf16) state1_vec4_kernel<KIND, __nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(a);
+        else state1_vec4_kernel<KIND, float><<<grid, TPB, 0, ctx->stream>>>(a);
+    } else {
+        const int grid = grid_for(ctx, a.count);
+        if (bf16) state1_kernel<KIND, __nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(a);
+        else state1_kernel<KIND, float><<<grid, TPB, 0, ctx->stream>>>(a);
+    }
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+}   // namespace
+
+zn_status zn_k_sgd_momentum(zn_ctx *ctx, const zn_opt_args &a) { return launch_state1<STATE1_MOMENTUM>(ctx, a); }
+zn_status zn_k_rmsprop(zn_ctx *ctx, const zn_opt_args &a) { return launch_state1<STATE1_RMSPROP>(ctx, a); }

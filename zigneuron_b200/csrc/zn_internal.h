@@ -166,6 +166,8 @@ zn_status zn_k_norm_combine(zn_ctx *ctx, const double *sumsq_dev, int count, flo
 struct zn_opt_args {
     float *w; float *g; float *m; float *v; size_t count;
     float lr, wd, beta1, beta2, eps, bc1, bc2;
+    float momentum, rho;            // momentum-SGD and RMSprop (their one state tensor is m)
+    float decay_mul;                // AdamW: w *= decay_mul after the Adam update; 0 = no decoupled decay
     float w_clamp;                  // 100 for weights, 50 for SGD bias
     const float *factor_dev;        // clip factor on the device, or null
     void *shadow;                   // operand-type copy of w for the tensor-core GEMMs, or null
@@ -174,3 +176,5 @@ struct zn_opt_args {
 };
 zn_status zn_k_sgd(zn_ctx *ctx, const zn_opt_args &a, bool is_bias);
 zn_status zn_k_adam(zn_ctx *ctx, const zn_opt_args &a);
+zn_status zn_k_sgd_momentum(zn_ctx *ctx, const zn_opt_args &a);
+zn_status zn_k_rmsprop(zn_ctx *ctx, const zn_opt_args &a);

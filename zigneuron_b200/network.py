@@ -12,7 +12,7 @@ from .backend import Activation, Backend, Loss, Precision
 
 
 @dataclass
-class Sgd:                      # src/optimizer.zig:81-85 (momentum 0 only on this path)
+class Sgd:                      # src/optimizer.zig:81-85; momentum > 0 ignores weight_decay, as Sgd.step does
     momentum: float = 0.0
     weight_decay: float = 0.0
 
@@ -21,6 +21,21 @@ class Sgd:                      # src/optimizer.zig:81-85 (momentum 0 only on th
 class Adam:                     # src/optimizer.zig:169-184
     beta1: float = 0.9
     beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+
+
+@dataclass
+class AdamW:                    # src/optimizer.zig:236-250
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+
+
+@dataclass
+class Rmsprop:                  # src/optimizer.zig:311-320
+    rho: float = 0.9
     eps: float = 1e-8
     weight_decay: float = 0.0
 
@@ -59,10 +74,15 @@ class Network:
     def setOptimizer(self, opt, layer=-1):
         if isinstance(opt, Adam):
             self._ck(lib.zn_net_set_adam(self.handle, layer, opt.beta1, opt.beta2, opt.eps, opt.weight_decay))
+        elif isinstance(opt, AdamW):
+            self._ck(lib.zn_net_set_adamw(self.handle, layer, opt.beta1, opt.beta2, opt.eps, opt.weight_decay))
+        elif isinstance(opt, Rmsprop):
+            self._ck(lib.zn_net_set_rmsprop(self.handle, layer, opt.rho, opt.eps, opt.weight_decay))
         elif isinstance(opt, Sgd):
-            if opt.momentum != 0.0:
-                raise NotImplementedError("momentum SGD is outside the Dense hot path")
-            self._ck(lib.zn_net_set_sgd(self.handle, layer, opt.weight_decay))
+            if opt.momentum > 0.0:
+                self._ck(lib.zn_net_set_sgd_momentum(self.handle, layer, opt.momentum))
+            else:
+                self._ck(lib.zn_net_set_sgd(self.handle, layer, opt.weight_decay))
         else:
             raise TypeError(opt)
 
