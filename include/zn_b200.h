@@ -117,7 +117,9 @@ ZN_API zn_status zn_matmul_transpose_b(zn_ctx *ctx, const float *a, const float 
                                        size_t m, size_t n, size_t k, int32_t accumulate);
 /* Backend.matMulBias / matMulBiasRelu / matMulBiasSigmoid / matMulBiasTanh,
  * src/backend.zig:200-295: C[batch x n] = act(A[batch x k] . B[k x n] + bias[n]),
- * one kernel (act = ZN_ACT_LINEAR for plain matMulBias). */
+ * one kernel (act = ZN_ACT_LINEAR for plain matMulBias).  The other activations are taken too:
+ * gelu / leaky_relu / elu in the same kernel, softmax by a second kernel over the rows of C
+ * (the way Dense.forward applies it sample by sample, src/layer.zig:398-406). */
 ZN_API zn_status zn_matmul_bias_act(zn_ctx *ctx, const float *a, const float *b, const float *bias, float *c,
                                     size_t batch, size_t n, size_t k, zn_activation act);
 
@@ -138,7 +140,8 @@ ZN_API zn_status zn_accumulate_bias(zn_ctx *ctx, float *grad_bias, size_t bias_l
  * calls on a GPU share the block: calls that overlap in time on one GPU race and must be ordered by the
  * caller; nothing in the block needs clearing between calls. */
 ZN_API zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g, size_t g_len);
-/* Backend.activationForward, src/backend.zig:367-386 (in == out allowed). */
+/* Backend.activationForward, src/backend.zig:367-386 (in == out allowed).  With softmax the
+ * whole slice is one vector, as in the reference (:377-379); likewise in the backward. */
 ZN_API zn_status zn_activation_forward(zn_ctx *ctx, zn_activation act, const float *in, float *out, size_t count);
 /* Backend.activationBackward, src/backend.zig:390-399 -> :2649-2669; `y` is the ACTIVATED output. */
 ZN_API zn_status zn_activation_backward(zn_ctx *ctx, zn_activation act, const float *y, const float *grad_out,

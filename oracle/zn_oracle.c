@@ -124,6 +124,12 @@ static float act_forward(int act, float x) {
         if (x >= 0) return 1 / (1 + expf(-x));
         else { const float e = expf(x); return e / (1 + e); }
     case ZO_TANH: return tanhf(x);
+    case ZO_GELU: {                                  /* src/activation.zig:128-134 */
+        const float c = 0.7978845608f, k = 0.044715f;
+        const float x3 = x * x * x;
+        const float inner = c * (x + k * x3);
+        return 0.5f * x * (1.0f + tanhf(inner));
+    }
     case ZO_LEAKY_RELU: return x > 0 ? x : 0.01f * x;
     case ZO_ELU: return x > 0 ? x : 1.0f * (expf(x) - 1.0f);
     default: return x;
@@ -138,14 +144,42 @@ static float act_backward(int act, float y, float g) {
     case ZO_RELU: return y > 0 ? g : 0;
     case ZO_SIGMOID: return g * y * (1 - y);          /* optimization.zig sigmoidBackwardVectorized scalar tail */
     case ZO_TANH: return g * (1 - y * y);
+    case ZO_GELU: {                                  /* src/activation.zig:139-150: derivative taken at x = y */
+        const float c = 0.7978845608f, k = 0.044715f;
+        const float x = y;
+        const float x3 = x * x * x;
+        const float inner = c * (x + k * x3);
+        const float t = tanhf(inner);
+        const float sech2 = 1.0f - t * t;
+        return (0.5f * (1.0f + t) + 0.5f * x * sech2 * c * (1.0f + 3.0f * k * x * x)) * g;
+    }
     case ZO_LEAKY_RELU: return (y > 0 ? 1.0f : 0.01f) * g;
     case ZO_ELU: return (y > 0 ? 1.0f : y + 1.0f) * g;
     default: return g;
     }
 }
 
-/* src/backend.zig:367-386 (cpu arm): element-wise, in == out allowed. */
+/* Activation.softmaxForward, src/activation.zig:51-78: one vector, in == out allowed. */
+ZO_API void zo_softmax_forward(const float *in, float *out, size_t n) {
+    float max_val = -INFINITY;
+    for (size_t i = 0; i < n; ++i) if (in[i] > max_val) max_val = in[i];
+    float sum = 0;
+    for (size_t i = 0; i < n; ++i) { out[i] = expf(in[i] - max_val); sum += out[i]; }
+    if (sum > 0) { for (size_t i = 0; i < n; ++i) out[i] /= sum; }
+    else { const float u = 1.0f / (float)n; for (size_t i = 0; i < n; ++i) out[i] = u; }
+}
+
+/* Activation.softmaxBackward, src/activation.zig:82-95. */
+ZO_API void zo_softmax_backward(const float *s, const float *grad_out, float *grad_in, size_t n) {
+    float dot = 0;
+    for (size_t i = 0; i < n; ++i) dot += grad_out[i] * s[i];
+    for (size_t i = 0; i < n; ++i) grad_in[i] = s[i] * (grad_out[i] - dot);
+}
+
+/* src/backend.zig:367-386 (cpu arm): element-wise, in == out allowed; softmax takes the whole
+ * slice as one vector. */
 ZO_API void zo_activation_forward(int act, const float *in, float *out, size_t n) {
+    if (act == ZO_SOFTMAX) { zo_softmax_forward(in, out, n); return; }
     for (size_t i = 0; i < n; ++i) out[i] = act_forward(act, in[i]);
 }
 
@@ -153,6 +187,7 @@ ZO_API void zo_activation_forward(int act, const float *in, float *out, size_t n
 ZO_API void zo_activation_backward(int act, const float *y, const float *grad_out,
                                    float *grad_in, size_t n) {
     if (act == ZO_LINEAR) { memcpy(grad_in, grad_out, n * sizeof(float)); return; }
+    if (act == ZO_SOFTMAX) { zo_softmax_backward(y, grad_out, grad_in, n); return; }
     for (size_t i = 0; i < n; ++i) grad_in[i] = act_backward(act, y[i], grad_out[i]);
 }
 
@@ -457,7 +492,11 @@ static void ensure_cache(zo_layer *l, size_t rows) {
 static void dense_forward(zo_layer *l, const float *x, float *y, size_t rows) {
     zo_matmul(x, l->W, y, rows, l->out, l->in, 0);
     zo_add_bias(y, rows * l->out, l->b, l->out);
-    zo_activation_forward(l->act, y, y, rows * l->out);
+    if (l->act == ZO_SOFTMAX) {                      /* one sample at a time, src/layer.zig:398-406 */
+        for (size_t r = 0; r < rows; ++r) zo_softmax_forward(y + r * l->out, y + r * l->out, l->out);
+    } else {
+        zo_activation_forward(l->act, y, y, rows * l->out);
+    }
 }
 
 /* Network.forward, src/network.zig:309-386: every layer keeps a copy of its
@@ -481,7 +520,12 @@ ZO_API void zo_net_forward(zo_net *net, const float *x, size_t rows, float *out)
  * activated output, dX = G*W^T, gb += column sums of G, gW = X^T*G. */
 static void dense_backward(zo_layer *l, const float *x, const float *grad_out,
                            float *grad_in, const float *y, float *gaa, size_t rows) {
-    zo_activation_backward(l->act, y, grad_out, gaa, rows * l->out);
+    if (l->act == ZO_SOFTMAX) {                      /* src/layer.zig:429-438 */
+        for (size_t r = 0; r < rows; ++r)
+            zo_softmax_backward(y + r * l->out, grad_out + r * l->out, gaa + r * l->out, l->out);
+    } else {
+        zo_activation_backward(l->act, y, grad_out, gaa, rows * l->out);
+    }
     zo_matmul_transpose_b(gaa, l->W, grad_in, rows, l->in, l->out, 0);
     zo_accumulate_bias(l->gb, l->out, gaa, rows * l->out);
     zo_matmul_transpose_a(x, gaa, l->gW, l->in, l->out, rows, 0);

@@ -170,23 +170,90 @@ def test_activations(be):
     rng = np.random.default_rng(7)
     x = rng.standard_normal(10007).astype(np.float32) * 3
     g = rng.standard_normal(10007).astype(np.float32)
-    for name in ("relu", "linear", "sigmoid", "tanh"):
+    for name in ("relu", "linear", "sigmoid", "tanh", "gelu", "leaky_relu", "elu"):
         act, oact = zn.Activation[name], getattr(zo, name.upper())
         y = np.empty_like(x)
         be.activationForward(act, x, y)
         want = zo.activation_forward(oact, x)
-        if name in ("relu", "linear"):
+        if name in ("relu", "linear", "leaky_relu"):
             assert np.array_equal(y, want)
         else:
             assert_close(y, want, 1e-6, name)
         gi = np.empty_like(x)
         be.activationBackward(act, want, g, gi)
-        assert np.array_equal(gi, zo.activation_backward(oact, want, g)), name
+        if name == "gelu":       # its derivative calls tanhf, which differs from the host's in the last place
+            assert_close(gi, zo.activation_backward(oact, want, g), 1e-6, name)
+        else:
+            assert np.array_equal(gi, zo.activation_backward(oact, want, g)), name
     x2 = x.copy()
     be.activationForward(zn.Activation.relu, x2, x2)      # in place, as Dense.forward does
     assert np.array_equal(x2, np.maximum(x, 0))
-    with pytest.raises(zn.ZnError):
-        be.activationForward(zn.Activation.gelu, x, y)
+    # leaky_relu / elu / gelu known answers (src/activation.zig:128-185 by hand)
+    pts = np.array([-2.0, -1.0, 0.0, 1.0, 3.0], np.float32)
+    out = np.empty_like(pts)
+    be.activationForward(zn.Activation.leaky_relu, pts, out)
+    assert np.allclose(out, [-0.02, -0.01, 0.0, 1.0, 3.0], atol=1e-7)
+    be.activationForward(zn.Activation.elu, pts, out)
+    assert np.allclose(out, [np.expm1(-2.0), np.expm1(-1.0), 0.0, 1.0, 3.0], atol=1e-6)
+    be.activationForward(zn.Activation.gelu, pts, out)
+    assert abs(out[3] - 0.84119199) < 1e-6 and abs(out[1] + 0.15880801) < 1e-6 and out[2] == 0.0
+
+
+def test_softmax_activation(be):
+    """Backend.activationForward / activationBackward with softmax take the whole slice as ONE vector
+    (src/backend.zig:377-379, :2650-2652; src/activation.zig:51-95)."""
+    # reference test vectors: src/test/unit/activation.zig:55-76, :149-159
+    y = np.empty(3, np.float32)
+    be.activationForward(zn.Activation.softmax, np.array([1.0, 2.0, 3.0], np.float32), y)
+    assert abs(float(y.sum()) - 1.0) < 1e-3 and y[2] > y[1] > y[0]
+    assert np.allclose(y, [0.09003057, 0.24472847, 0.66524096], atol=1e-6)
+    gi = np.empty(2, np.float32)
+    be.activationBackward(zn.Activation.softmax, np.array([0.0, 1.0], np.float32), np.ones(2, np.float32), gi)
+    assert abs(float(gi.sum())) < 1e-4
+    rng = np.random.default_rng(17)
+    for n in (1, 7, 32, 33, 1000, 10007):
+        x = (rng.standard_normal(n) * 3).astype(np.float32)
+        g = rng.standard_normal(n).astype(np.float32)
+        y = np.empty_like(x)
+        be.activationForward(zn.Activation.softmax, x, y)
+        want = zo.activation_forward(zo.SOFTMAX, x)
+        # the oracle adds the exponentials into one running f32 sum; over 1e4 terms that sum is itself off by
+        # a few 1e-6 (FP32_EXACT, below, reproduces the order)
+        assert_close(y, want, 1e-5, f"softmax {n}")
+        gi = np.empty_like(x)
+        be.activationBackward(zn.Activation.softmax, want, g, gi)
+        wgi = zo.activation_backward(zo.SOFTMAX, want, g)
+        assert np.abs(gi - wgi).max() <= 1e-5 * max(np.abs(wgi).max(), 1e-6), n
+    x = (rng.standard_normal(50) * 2).astype(np.float32)
+    x2 = x.copy()
+    be.activationForward(zn.Activation.softmax, x2, x2)     # in place
+    assert_close(x2, zo.activation_forward(zo.SOFTMAX, x), 2e-6, "in place")
+    # all -inf: the sum of exponentials is not > 0, the reference answers with the uniform vector
+    y = np.empty(4, np.float32)
+    be.activationForward(zn.Activation.softmax, np.full(4, -np.inf, np.float32), y)
+    assert np.allclose(y, 0.25)
+    # reference order under FP32_EXACT: the only differences left are expf's last place
+    bx = zn.Backend(precision=zn.Precision.FP32_EXACT)
+    x = (rng.standard_normal(4099) * 3).astype(np.float32)
+    y = np.empty_like(x)
+    bx.activationForward(zn.Activation.softmax, x, y)
+    assert_close(y, zo.activation_forward(zo.SOFTMAX, x), 1e-6, "exact order")
+    bx.deinit()
+
+
+def test_matmul_bias_softmax_rows(be):
+    """The fused Dense forward with softmax normalises every row (src/layer.zig:398-406)."""
+    rng = np.random.default_rng(18)
+    m, n, k = 37, 10, 64
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = (rng.standard_normal((k, n)) / 8).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    c = np.empty((m, n), np.float32)
+    be.matMulBiasAct(a, b, bias, c, m, n, k, zn.Activation.softmax)
+    z = zo.add_bias(zo.matmul(a, b, m, n, k), bias).reshape(m, n)
+    want = np.stack([zo.activation_forward(zo.SOFTMAX, z[r]) for r in range(m)])
+    assert_close(c, want, 1e-5, "softmax rows")
+    assert np.allclose(c.sum(axis=1), 1.0, atol=1e-5)
 
 
 def test_losses(be):

@@ -122,6 +122,36 @@ def test_adamw_is_adam_then_decoupled_decay():
     assert np.array_equal(ww, wa * mul) and np.array_equal(bw, ba * mul)
 
 
+def test_remaining_activations_golden():
+    kat = KAT["activations_n2"]
+    for case in kat["softmax"]:
+        y = zo.activation_forward(zo.SOFTMAX, f32(case["x"]))
+        assert np.allclose(y, f32(case["expected"]), atol=case["tol"], rtol=0)
+        assert abs(float(y.sum()) - 1.0) < 1e-3 and y[2] > y[1] > y[0]
+    for case in kat["softmax_backward"]:
+        gi = zo.activation_backward(zo.SOFTMAX, f32(case["s"]), f32(case["g"]))
+        assert np.allclose(gi, f32(case["expected"]), atol=case["tol"], rtol=0) and abs(float(gi.sum())) < 1e-4
+    ids = {"leaky_relu": zo.LEAKY_RELU, "elu": zo.ELU, "gelu": zo.GELU}
+    for case in kat["pointwise"]:
+        y = zo.activation_forward(ids[case["act"]], f32(case["x"]))
+        assert np.allclose(y, f32(case["forward"]), atol=case["tol"], rtol=0), case["cite"]
+        if "backward_at_y_g1" in case:
+            gi = zo.activation_backward(ids[case["act"]], y, np.ones_like(y))
+            assert np.allclose(gi, f32(case["backward_at_y_g1"]), atol=case["tol"], rtol=0), case["cite"]
+    # gelu's derivative is the analytic one evaluated at y (src/activation.zig:139-150): check it against
+    # a float64 evaluation of the same formula
+    y = np.linspace(-3, 3, 41).astype(np.float32)
+    c, k = 0.7978845608, 0.044715
+    yd = y.astype(np.float64)
+    th = np.tanh(c * (yd + k * yd ** 3))
+    want = 0.5 * (1 + th) + 0.5 * yd * (1 - th * th) * c * (1 + 3 * k * yd * yd)
+    got = zo.activation_backward(zo.GELU, y, np.full_like(y, 2.0))
+    assert np.allclose(got, 2.0 * want, atol=2e-6, rtol=0)
+    # all inputs -inf: x - max is NaN, the sum is not > 0, the result is uniform (src/activation.zig:69-77)
+    y = zo.activation_forward(zo.SOFTMAX, np.full(4, -np.inf, np.float32))
+    assert np.allclose(y, 0.25)
+
+
 def test_three_gemm_orientations_agree():
     rng = np.random.default_rng(7)
     m, n, k = 13, 9, 21

@@ -32,7 +32,7 @@ def trunc_tf32(x):
 
 def reference_init(rng, n_in, n_out, act):
     """Weights in the reference's distribution: U(-1,1) * scale(act) (src/layer.zig:330-338)."""
-    if act == "relu":
+    if act in ("relu", "leaky_relu"):
         scale = np.sqrt(2.0 / n_in)
     elif act == "linear":
         scale = np.sqrt(1.0 / n_in)

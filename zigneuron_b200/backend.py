@@ -131,6 +131,10 @@ class Backend:
     def _mm_bias(self, a, b, bias, c, batch_size, n, k, act):
         self._ck(lib.zn_matmul_bias_act(self.handle, ptr(a), ptr(b), ptr(bias), ptr(c), batch_size, n, k, int(act)))
 
+    def matMulBiasAct(self, a, b, bias, c, batch_size, n, k, act):
+        """The fused Dense forward with any activation (softmax is applied row by row)."""
+        self._mm_bias(a, b, bias, c, batch_size, n, k, Activation(act))
+
     def matMulBias(self, a, b, bias, c, batch_size, n, k):
         self._mm_bias(a, b, bias, c, batch_size, n, k, Activation.linear)
 

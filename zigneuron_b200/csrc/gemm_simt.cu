@@ -8,6 +8,7 @@
 // the add are separate roundings as well (the reference has no FMA), which makes
 // the product bit-identical to the reference's.
 #include "zn_internal.h"
+#include "zn_act.cuh"
 
 namespace {
 
@@ -20,6 +21,9 @@ __device__ __forceinline__ float apply_act(int act, float v) {
         if (v >= 0.f) return 1.f / (1.f + expf(-v));
         else { const float e = expf(v); return e / (1.f + e); }
     case ZN_ACT_TANH: return tanhf(v);
+    case ZN_ACT_GELU: return zn_gelu_fwd(v);
+    case ZN_ACT_LEAKY_RELU: return zn_leaky_fwd(v);
+    case ZN_ACT_ELU: return zn_elu_fwd(v);
     default: return v;
     }
 }

@@ -26,6 +26,7 @@
 #include <cstring>
 
 #include "zn_internal.h"
+#include "zn_act.cuh"
 
 namespace {
 
@@ -254,6 +255,15 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
     } else if (p.act == ZN_ACT_TANH) {
 #pragma unroll 4
         for (int j = 0; j < 32; ++j) v[j] = act_apply(ZN_ACT_TANH, v[j]);
+    } else if (p.act == ZN_ACT_GELU) {
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) v[j] = zn_gelu_fwd(v[j]);
+    } else if (p.act == ZN_ACT_LEAKY_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = zn_leaky_fwd(v[j]);
+    } else if (p.act == ZN_ACT_ELU) {
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) v[j] = zn_elu_fwd(v[j]);
     }
     if (p.mask) {
         if (t_bf16) {

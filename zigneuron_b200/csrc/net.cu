@@ -159,20 +159,35 @@ zn_status forward_dev(zn_net *n, const float *x_dev, size_t rows) {
         Layer &l = n->layers[i];
         zn_epilogue ep;
         ep.bias = l.params + l.b_off;
-        ep.act = l.act;
+        // softmax needs whole rows: the GEMM writes the biased pre-activations, a row kernel follows
+        const bool softmax = l.act == ZN_ACT_SOFTMAX;
+        ep.act = softmax ? (int)ZN_ACT_LINEAR : l.act;
         const bool last = i + 1 == L;
         if (!n->tc) {
             ep.out_f32 = (float *)n->acts[i + 1];
             ep.ld_out_f32 = n->lds[i + 1];
         } else {
             if (last) { ep.out_f32 = n->out_f32; ep.ld_out_f32 = (int64_t)l.out; }
-            if (!last || l.act != ZN_ACT_LINEAR) { ep.out_t = n->acts[i + 1]; ep.ld_out_t = n->lds[i + 1]; }
+            if ((!last || l.act != ZN_ACT_LINEAR) && !(last && softmax)) { ep.out_t = n->acts[i + 1]; ep.ld_out_t = n->lds[i + 1]; }
         }
         const void *w = l.w_op ? l.w_op : (const void *)l.params;
         const int64_t ldw = l.w_op ? l.ld_w : (int64_t)l.out;
         // the previous step's update of this layer may still be running on the optimizer lane
         if (l.update_pending) ZN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, l.updated, 0));
         ZN_TRY(net_gemm(n, 0, cur, n->lds[i], w, ldw, (int64_t)rows, (int64_t)l.out, (int64_t)l.in, ep));
+        if (softmax) {     // Dense.forward, src/layer.zig:398-406
+            const bool exact = n->prec == ZN_FP32_EXACT;
+            const int64_t ld = n->lds[i + 1];
+            if (!n->tc)          // fp32 block, in place
+                ZN_TRY(zn_k_softmax_rows(ctx, n->acts[i + 1], false, ld, nullptr, false, 0, (float *)n->acts[i + 1], ld,
+                                         (int64_t)rows, (int64_t)l.out, exact));
+            else if (last)       // fp32 logits -> fp32 probabilities in place, plus the operand-typed copy the backward reads
+                ZN_TRY(zn_k_softmax_rows(ctx, n->out_f32, false, (int64_t)l.out, n->acts[i + 1], n->bf16, ld, n->out_f32,
+                                         (int64_t)l.out, (int64_t)rows, (int64_t)l.out, exact));
+            else                 // hidden layer: operand-typed block, in place
+                ZN_TRY(zn_k_softmax_rows(ctx, n->acts[i + 1], n->bf16, ld, n->acts[i + 1], n->bf16, ld, nullptr, 0,
+                                         (int64_t)rows, (int64_t)l.out, exact));
+        }
         cur = n->acts[i + 1];
     }
     return ZN_OK;
@@ -212,7 +227,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
                      (int64_t)rows, (int64_t)out_cols, (float)(total_rows * out_cols), loss_slot, exact));
     if (last.act != ZN_ACT_LINEAR)   // Dense.backward applies the derivative of every layer, the last included
         ZN_TRY(zn_k_act_backward_t(ctx, last.act, n->acts[L], n->lds[L], n->gwork[cur], n->lds[L], n->bf16,
-                                   (int64_t)rows, (int64_t)out_cols));
+                                   (int64_t)rows, (int64_t)out_cols, exact));
 
     for (size_t idx = L; idx-- > 0;) {
         Layer &l = n->layers[idx];
@@ -259,7 +274,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
             ZN_TRY(net_gemm(n, 2, g, ld_g, w, ldw, (int64_t)rows, (int64_t)l.in, (int64_t)l.out, ep));
             if (idx > 0 && prev_act != ZN_ACT_RELU && prev_act != ZN_ACT_LINEAR)
                 ZN_TRY(zn_k_act_backward_t(ctx, prev_act, n->acts[idx], n->lds[idx], n->gwork[cur ^ 1], n->lds[idx],
-                                           n->bf16, (int64_t)rows, (int64_t)l.in));
+                                           n->bf16, (int64_t)rows, (int64_t)l.in, exact));
         }
         cur ^= 1;
     }
@@ -433,8 +448,7 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     zn_ctx *ctx = n->ctx;
     if (input_size == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "InvalidInputSize: input_size is 0");     // src/layer.zig:307
     if (output_size == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "InvalidOutputSize: output_size is 0");  // src/layer.zig:308
-    if (act != ZN_ACT_RELU && act != ZN_ACT_LINEAR && act != ZN_ACT_SIGMOID && act != ZN_ACT_TANH)
-        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "activation %d is not on the Dense path", (int)act);
+    if (act < ZN_ACT_RELU || act > ZN_ACT_ELU) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "unknown activation %d", (int)act);
     if (!n->layers.empty() && n->layers.back().out != input_size)
         return zn_fail(ctx, ZN_ERR_SHAPE, "layer input %zu does not match previous output %zu", input_size, n->layers.back().out);
     if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "steps in flight");
@@ -463,7 +477,7 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     // Dense.init, src/layer.zig:326-339: U(-1,1) * scale(act), bias 0.  The generator is seeded by a
     // counter 1,2,3,... like the reference's, but is splitmix64, not Zig's PRNG.
     {
-        const float scale = (act == ZN_ACT_RELU) ? sqrtf(2.0f / (float)input_size)
+        const float scale = (act == ZN_ACT_RELU || act == ZN_ACT_LEAKY_RELU) ? sqrtf(2.0f / (float)input_size)
                             : (act == ZN_ACT_LINEAR) ? sqrtf(1.0f / (float)input_size)
                                                      : sqrtf(2.0f / (float)(input_size + output_size));
         uint64_t s = ++n->seed_counter;

@@ -104,8 +104,7 @@ zn_status matmul_common(zn_ctx *ctx, Orient o, const float *a, const float *b, c
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
     if (!a || !b || !c) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "matmul: null operand");
     if (m == 0 || n == 0 || k == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "matmul: zero dimension");
-    if (act != ZN_ACT_LINEAR && act != ZN_ACT_RELU && act != ZN_ACT_SIGMOID && act != ZN_ACT_TANH)
-        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "activation %d is not fused on the Dense path", act);
+    if (act < ZN_ACT_RELU || act > ZN_ACT_ELU) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "unknown activation %d", act);
     cudaSetDevice(ctx->device);
     Operand A, B, C, Bi;
     ZN_TRY(resolve(ctx, 0, a, m * k, true, &A));
@@ -114,11 +113,14 @@ zn_status matmul_common(zn_ctx *ctx, Orient o, const float *a, const float *b, c
     if (bias) ZN_TRY(resolve(ctx, 3, bias, n, true, &Bi));
     zn_epilogue ep;
     ep.bias = bias ? Bi.dev : nullptr;
-    ep.act = act;
+    ep.act = act == ZN_ACT_SOFTMAX ? (int)ZN_ACT_LINEAR : act;
     ep.out_f32 = C.dev;
     ep.ld_out_f32 = (int64_t)n;
     ep.accumulate = accumulate ? 1 : 0;
     ZN_TRY(gemm_dispatch(ctx, o, A.dev, B.dev, (int64_t)m, (int64_t)n, (int64_t)k, ep));
+    if (act == ZN_ACT_SOFTMAX)     // row by row, as Dense.forward applies it (src/layer.zig:398-406)
+        ZN_TRY(zn_k_softmax_rows(ctx, C.dev, false, (int64_t)n, nullptr, false, 0, C.dev, (int64_t)n, (int64_t)m, (int64_t)n,
+                                 ctx->precision == ZN_FP32_EXACT));
     return finish(ctx, &C, A.host || B.host || C.host || Bi.host);
 }
 
@@ -170,9 +172,7 @@ extern "C" zn_status zn_accumulate_bias(zn_ctx *ctx, float *grad_bias, size_t bi
     return finish(ctx, &GB, GB.host || G.host);
 }
 
-static bool act_supported(int act) {
-    return act == ZN_ACT_RELU || act == ZN_ACT_LINEAR || act == ZN_ACT_SIGMOID || act == ZN_ACT_TANH;
-}
+static bool act_supported(int act) { return act >= ZN_ACT_RELU && act <= ZN_ACT_ELU; }
 
 extern "C" zn_status zn_activation_forward(zn_ctx *ctx, zn_activation act, const float *in, float *out, size_t count) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
@@ -183,7 +183,11 @@ extern "C" zn_status zn_activation_forward(zn_ctx *ctx, zn_activation act, const
     ZN_TRY(resolve(ctx, 0, in, count, true, &I));
     if (in == out) O = I;
     else ZN_TRY(resolve(ctx, 1, out, count, false, &O));
-    ZN_TRY(zn_k_act_forward(ctx, act, I.dev, O.dev, (int64_t)count));
+    if (act == ZN_ACT_SOFTMAX)     // the whole slice is one vector (src/backend.zig:377-379)
+        ZN_TRY(zn_k_softmax_rows(ctx, I.dev, false, (int64_t)count, nullptr, false, 0, O.dev, (int64_t)count, 1, (int64_t)count,
+                                 ctx->precision == ZN_FP32_EXACT));
+    else
+        ZN_TRY(zn_k_act_forward(ctx, act, I.dev, O.dev, (int64_t)count));
     return finish(ctx, &O, I.host || O.host);
 }
 
@@ -197,7 +201,11 @@ extern "C" zn_status zn_activation_backward(zn_ctx *ctx, zn_activation act, cons
     ZN_TRY(resolve(ctx, 0, y, count, true, &Y));
     ZN_TRY(resolve(ctx, 1, grad_out, count, true, &GO));
     ZN_TRY(resolve(ctx, 2, grad_in, count, false, &GI));
-    ZN_TRY(zn_k_act_backward(ctx, act, Y.dev, GO.dev, GI.dev, (int64_t)count));
+    if (act == ZN_ACT_SOFTMAX)     // src/backend.zig:2650-2652
+        ZN_TRY(zn_k_softmax_backward_rows(ctx, Y.dev, (int64_t)count, GO.dev, (int64_t)count, GI.dev, (int64_t)count, false, 1,
+                                          (int64_t)count, ctx->precision == ZN_FP32_EXACT));
+    else
+        ZN_TRY(zn_k_act_backward(ctx, act, Y.dev, GO.dev, GI.dev, (int64_t)count));
     return finish(ctx, &GI, Y.host || GO.host || GI.host);
 }
 

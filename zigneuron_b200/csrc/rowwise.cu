@@ -5,6 +5,7 @@
 // (block partials in the context's scratch, then one block adds them in a fixed
 // order), so results do not depend on scheduling.
 #include "zn_internal.h"
+#include "zn_act.cuh"
 
 namespace {
 
@@ -42,6 +43,9 @@ __device__ __forceinline__ float act_fwd(int act, float x) {
         if (x >= 0.f) return 1.f / (1.f + expf(-x));
         else { const float e = expf(x); return e / (1.f + e); }
     case ZN_ACT_TANH: return tanhf(x);
+    case ZN_ACT_GELU: return zn_gelu_fwd(x);
+    case ZN_ACT_LEAKY_RELU: return zn_leaky_fwd(x);
+    case ZN_ACT_ELU: return zn_elu_fwd(x);
     default: return x;
     }
 }
@@ -50,6 +54,9 @@ __device__ __forceinline__ float act_bwd(int act, float y, float g) {
     case ZN_ACT_RELU: return y > 0.f ? g : 0.f;
     case ZN_ACT_SIGMOID: return __fmul_rn(__fmul_rn(g, y), (1.f - y));
     case ZN_ACT_TANH: return __fmul_rn(g, (1.f - __fmul_rn(y, y)));
+    case ZN_ACT_GELU: return zn_gelu_bwd(y, g);
+    case ZN_ACT_LEAKY_RELU: return zn_leaky_bwd(y, g);
+    case ZN_ACT_ELU: return zn_elu_bwd(y, g);
     default: return g;
     }
 }
@@ -122,6 +129,64 @@ __global__ void act_backward_t_kernel(int act, const T *__restrict__ y, int64_t 
         const float yv = to_f32(y[r * ld_y + c]);
         const float gv = to_f32(g[r * ld_g + c]);
         g[r * ld_g + c] = from_f32<T>(act_bwd(act, yv, gv));
+    }
+}
+
+// ---- row-wise softmax -------------------------------------------------------------------
+// Activation.softmaxForward (src/activation.zig:51-78) on every row of a block, the way Dense.forward
+// applies it sample by sample (src/layer.zig:398-406).  One warp per row.  `exact`: lane 0 takes the
+// maximum and the sum of exponentials in column order, as the reference does; otherwise lanes take
+// strided partial sums.  Either output may be null; in == out is allowed.
+template <typename TIN, typename TOUT>
+__global__ void softmax_rows_kernel(const TIN *in, int64_t ld_in, TOUT *out_t, int64_t ld_t, float *out_f32,
+                                    int64_t ld_f, int64_t rows, int64_t cols, int exact) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+        const TIN *x = in + r * ld_in;
+        float mx = -INFINITY, sum = 0.f;
+        if (exact) {
+            if (lane == 0) {
+                for (int64_t c = 0; c < cols; ++c) { const float v = to_f32(x[c]); if (v > mx) mx = v; }
+                for (int64_t c = 0; c < cols; ++c) sum = __fadd_rn(sum, expf(__fsub_rn(to_f32(x[c]), mx)));
+            }
+            mx = __shfl_sync(0xffffffffu, mx, 0);
+            sum = __shfl_sync(0xffffffffu, sum, 0);
+        } else {
+            for (int64_t c = lane; c < cols; c += 32) mx = fmaxf(mx, to_f32(x[c]));
+            mx = warp_max(mx);
+            for (int64_t c = lane; c < cols; c += 32) sum += expf(to_f32(x[c]) - mx);
+            sum = warp_sum(sum);
+        }
+        const bool ok = sum > 0.f;                       // false also for NaN: uniform, as the reference
+        const float uniform = __fdiv_rn(1.0f, (float)cols);
+        for (int64_t c = lane; c < cols; c += 32) {
+            const float v = ok ? __fdiv_rn(expf(__fsub_rn(to_f32(x[c]), mx)), sum) : uniform;
+            if (out_t) out_t[r * ld_t + c] = from_f32<TOUT>(v);
+            if (out_f32) out_f32[r * ld_f + c] = v;
+        }
+    }
+}
+
+// Activation.softmaxBackward (src/activation.zig:82-95) per row: gi = s * (go - sum(go * s)); gi == go allowed.
+template <typename T>
+__global__ void softmax_backward_rows_kernel(const T *s, int64_t ld_s, const T *go, int64_t ld_go, T *gi, int64_t ld_gi,
+                                             int64_t rows, int64_t cols, int exact) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+        const T *sr = s + r * ld_s, *gr = go + r * ld_go;
+        float dot = 0.f;
+        if (exact) {
+            if (lane == 0)
+                for (int64_t c = 0; c < cols; ++c) dot = __fadd_rn(dot, __fmul_rn(to_f32(gr[c]), to_f32(sr[c])));
+            dot = __shfl_sync(0xffffffffu, dot, 0);
+        } else {
+            for (int64_t c = lane; c < cols; c += 32) dot += to_f32(gr[c]) * to_f32(sr[c]);
+            dot = warp_sum(dot);
+        }
+        for (int64_t c = lane; c < cols; c += 32)
+            gi[r * ld_gi + c] = from_f32<T>(__fmul_rn(to_f32(sr[c]), __fsub_rn(to_f32(gr[c]), dot)));
     }
 }
 
@@ -380,8 +445,48 @@ zn_status zn_k_act_backward(zn_ctx *ctx, int act, const float *y, const float *g
     return ZN_OK;
 }
 
+static int row_grid(zn_ctx *ctx, int64_t rows) {
+    int64_t blocks = (rows + TPB / 32 - 1) / (TPB / 32);
+    const int64_t cap = (int64_t)ctx->sm_count * 8;
+    return (int)(blocks < 1 ? 1 : blocks > cap ? cap : blocks);
+}
+
+zn_status zn_k_softmax_rows(zn_ctx *ctx, const void *in, bool in_bf16, int64_t ld_in, void *out_t, bool out_bf16,
+                            int64_t ld_t, float *out_f32, int64_t ld_f, int64_t rows, int64_t cols, bool exact) {
+    zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, (double)rows * cols * 8);
+    const int grid = row_grid(ctx, rows);
+    if (in_bf16) {
+        if (out_t && !out_bf16) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "softmax: bf16 input needs a bf16 typed output");
+        softmax_rows_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(
+            (const __nv_bfloat16 *)in, ld_in, (__nv_bfloat16 *)out_t, ld_t, out_f32, ld_f, rows, cols, exact ? 1 : 0);
+    } else if (out_t && out_bf16) {
+        softmax_rows_kernel<float, __nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(
+            (const float *)in, ld_in, (__nv_bfloat16 *)out_t, ld_t, out_f32, ld_f, rows, cols, exact ? 1 : 0);
+    } else {
+        softmax_rows_kernel<float, float><<<grid, TPB, 0, ctx->stream>>>(
+            (const float *)in, ld_in, (float *)out_t, ld_t, out_f32, ld_f, rows, cols, exact ? 1 : 0);
+    }
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_softmax_backward_rows(zn_ctx *ctx, const void *s, int64_t ld_s, const void *go, int64_t ld_go, void *gi,
+                                     int64_t ld_gi, bool bf16, int64_t rows, int64_t cols, bool exact) {
+    zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, (double)rows * cols * (bf16 ? 8 : 16));
+    const int grid = row_grid(ctx, rows);
+    if (bf16)
+        softmax_backward_rows_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(
+            (const __nv_bfloat16 *)s, ld_s, (const __nv_bfloat16 *)go, ld_go, (__nv_bfloat16 *)gi, ld_gi, rows, cols, exact ? 1 : 0);
+    else
+        softmax_backward_rows_kernel<float><<<grid, TPB, 0, ctx->stream>>>(
+            (const float *)s, ld_s, (const float *)go, ld_go, (float *)gi, ld_gi, rows, cols, exact ? 1 : 0);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
 zn_status zn_k_act_backward_t(zn_ctx *ctx, int act, const void *y, int64_t ld_y, void *g, int64_t ld_g, bool bf16,
-                              int64_t rows, int64_t cols) {
+                              int64_t rows, int64_t cols, bool exact) {
+    if (act == ZN_ACT_SOFTMAX) return zn_k_softmax_backward_rows(ctx, y, ld_y, g, ld_g, g, ld_g, bf16, rows, cols, exact);
     zn_launch_scope scope(ctx, ZN_PROF_ELEMENTWISE, 0, (double)rows * cols * (bf16 ? 6 : 12));
     const int grid = grid_for(ctx, rows * cols);
     if (bf16)

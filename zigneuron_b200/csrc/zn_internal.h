@@ -141,8 +141,14 @@ zn_status zn_k_add_bias(zn_ctx *ctx, float *out, int64_t rows, int64_t cols, con
 zn_status zn_k_act_forward(zn_ctx *ctx, int act, const float *in, float *out, int64_t n);
 zn_status zn_k_act_backward(zn_ctx *ctx, int act, const float *y, const float *go, float *gi, int64_t n);
 // In place g = act'(y) (*) g on operand-typed blocks (activations whose derivative is not fused in a GEMM epilogue).
+// For softmax this is the row-wise backward (`exact`: the dot product in column order).
 zn_status zn_k_act_backward_t(zn_ctx *ctx, int act, const void *y, int64_t ld_y, void *g, int64_t ld_g, bool bf16,
-                              int64_t rows, int64_t cols);
+                              int64_t rows, int64_t cols, bool exact = false);
+// Softmax over each row of a block.  in: f32 or bf16; out_t (f32 or bf16) and out_f32 may each be null; in place allowed.
+zn_status zn_k_softmax_rows(zn_ctx *ctx, const void *in, bool in_bf16, int64_t ld_in, void *out_t, bool out_bf16,
+                            int64_t ld_t, float *out_f32, int64_t ld_f, int64_t rows, int64_t cols, bool exact);
+zn_status zn_k_softmax_backward_rows(zn_ctx *ctx, const void *s, int64_t ld_s, const void *go, int64_t ld_go, void *gi,
+                                     int64_t ld_gi, bool bf16, int64_t rows, int64_t cols, bool exact);
 // gb[c] (+)= sum_r g[r][c]; exact = one thread per column, rows ascending.
 zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, int64_t rows, int64_t cols,
                            float *gb, bool accumulate, bool exact);
