@@ -156,6 +156,15 @@ ZN_API zn_status zn_loss_forward(zn_ctx *ctx, zn_loss loss, const float *output,
 ZN_API zn_status zn_loss_backward(zn_ctx *ctx, zn_loss loss, const float *output, const float *target,
                                   float *grad_out, size_t rows, size_t cols);
 
+/* metrics.evaluateClassification, src/metrics.zig:239-264: per sample getPredictedClass
+ * (first maximum, :213-227) and getTrueClass (first target > 0.5, else 0, :230-235), then
+ * computeClassificationMetrics (:85-163).  outputs / targets: rows x cols, host or device.
+ * confusion (host, num_classes^2 counters, [true][predicted]) and metrics4 (host: accuracy,
+ * macro precision, macro recall, F1) may each be null.  rows = 0 fails with ZN_ERR_SHAPE
+ * (error.EmptyInput), a class index >= num_classes with ZN_ERR_INVALID_VALUE (error.InvalidClass). */
+ZN_API zn_status zn_evaluate_classification(zn_ctx *ctx, const float *outputs, const float *targets, size_t rows,
+                                            size_t cols, size_t num_classes, uint64_t *confusion, float *metrics4);
+
 /* ---- optimizers ------------------------------------------------------------------ */
 /* Backend.sgdUpdate, src/backend.zig:420-430 -> cpuSgdUpdate :2722-2739 (clamps included). */
 ZN_API zn_status zn_sgd_update(zn_ctx *ctx, float *weights, const float *grads, size_t count,
@@ -208,6 +217,10 @@ ZN_API zn_status zn_net_set_adamw(zn_net *net, int32_t layer, float beta1, float
 ZN_API zn_status zn_net_set_rmsprop(zn_net *net, int32_t layer, float rho, float eps, float weight_decay);
 /* Network.forward, src/network.zig:309-386, on a block of `rows` samples. */
 ZN_API zn_status zn_net_forward(zn_net *net, const float *input, size_t rows, float *output);
+/* Network.forward on the block, then metrics.evaluateClassification (below) on its output
+ * and `target` (rows x output size, one-hot), all on the device. */
+ZN_API zn_status zn_net_evaluate_classification(zn_net *net, const float *input, const float *target, size_t rows,
+                                                size_t num_classes, uint64_t *confusion, float *metrics4);
 /* Network.trainStep, src/network.zig:481-579, on a block of `rows` samples:
  * clear gradients, forward, loss gradient, backward, global norm clip,
  * optimizer, and the loss of the pre-update output in *loss_out (host).

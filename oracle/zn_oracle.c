@@ -697,3 +697,64 @@ ZO_API void zo_net_train(zo_net *net, const float *inputs, const float *targets,
         if (epoch_loss) epoch_loss[e] = total / (float)samples;
     }
 }
+
+/* ---------------------------------------------------------------- evaluation */
+
+/* getPredictedClass, src/metrics.zig:213-227: first index of the maximum (strict >). */
+ZO_API size_t zo_predicted_class(const float *output, size_t n) {
+    size_t idx = 0;
+    float best = output[0];
+    for (size_t i = 1; i < n; ++i)
+        if (output[i] > best) { best = output[i]; idx = i; }
+    return idx;
+}
+
+/* getTrueClass, src/metrics.zig:230-235: first entry above 0.5, else class 0. */
+ZO_API size_t zo_true_class(const float *target, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (target[i] > 0.5f) return i;
+    return 0;
+}
+
+/* computeClassificationMetrics, src/metrics.zig:85-163.  cm[target][pred], row-major classes x classes;
+ * out4 = accuracy, macro precision, macro recall, F1 of those two.  Returns 0, 1 = EmptyInput, 2 = InvalidClass. */
+ZO_API int zo_classification_metrics(const size_t *pred, const size_t *targ, size_t n, size_t classes,
+                                     unsigned long long *cm, float *out4) {
+    if (n == 0) return 1;
+    memset(cm, 0, classes * classes * sizeof(unsigned long long));
+    for (size_t i = 0; i < n; ++i) {
+        if (pred[i] >= classes || targ[i] >= classes) return 2;
+        cm[targ[i] * classes + pred[i]] += 1;
+    }
+    size_t correct = 0;
+    float total_precision = 0, total_recall = 0;
+    for (size_t c = 0; c < classes; ++c) {
+        const size_t tp = (size_t)cm[c * classes + c];
+        size_t fp = 0, fn = 0;
+        for (size_t i = 0; i < classes; ++i)
+            if (i != c) { fp += (size_t)cm[i * classes + c]; fn += (size_t)cm[c * classes + i]; }
+        correct += tp;
+        total_precision += (tp + fp > 0) ? (float)tp / (float)(tp + fp) : 0.0f;
+        total_recall += (tp + fn > 0) ? (float)tp / (float)(tp + fn) : 0.0f;
+    }
+    const float accuracy = (float)correct / (float)n;
+    const float precision = total_precision / (float)classes;
+    const float recall = total_recall / (float)classes;
+    out4[0] = accuracy; out4[1] = precision; out4[2] = recall;
+    out4[3] = (precision + recall > 0) ? 2.0f * precision * recall / (precision + recall) : 0.0f;
+    return 0;
+}
+
+/* evaluateClassification, src/metrics.zig:239-264, on row-major blocks of `rows` outputs and targets. */
+ZO_API int zo_evaluate_classification(const float *outputs, const float *targets, size_t rows, size_t cols,
+                                      size_t classes, unsigned long long *cm, float *out4) {
+    size_t *pred = (size_t *)malloc((rows ? rows : 1) * sizeof(size_t));
+    size_t *targ = (size_t *)malloc((rows ? rows : 1) * sizeof(size_t));
+    for (size_t r = 0; r < rows; ++r) {
+        pred[r] = zo_predicted_class(outputs + r * cols, cols);
+        targ[r] = zo_true_class(targets + r * cols, cols);
+    }
+    const int rc = zo_classification_metrics(pred, targ, rows, classes, cm, out4);
+    free(pred); free(targ);
+    return rc;
+}

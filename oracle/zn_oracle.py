@@ -59,6 +59,7 @@ def load():
         "zo_adam_bias_corrections": (None, [f, f, sz, C.POINTER(f), C.POINTER(f)]),
         "zo_clip_grad_norm": (f, [C.POINTER(vp), C.POINTER(sz), sz, C.POINTER(f)]),
         "zo_distribute_round_robin": (None, [sz, sz, sz, C.POINTER(sz), C.POINTER(sz)]),
+        "zo_evaluate_classification": (i, [_f32p, _f32p, sz, sz, sz, np.ctypeslib.ndpointer(dtype=np.uint64, flags="C_CONTIGUOUS"), _f32p]),
         "zo_net_create": (vp, []),
         "zo_net_destroy": (None, [vp]),
         "zo_net_add_dense": (i, [vp, sz, sz, i]),
@@ -181,6 +182,18 @@ def sgd_momentum_update(w, g, vel, lr, momentum):
     w, v = _c(w).copy(), _c(vel).copy()
     load().zo_sgd_momentum_update(w.reshape(-1), _c(g).reshape(-1), v.reshape(-1), w.size, lr, momentum)
     return w, v
+
+
+def evaluate_classification(outputs, targets, classes):
+    """metrics.evaluateClassification: returns (status, confusion[classes, classes], [accuracy, precision, recall, f1])."""
+    o, t = _c(outputs), _c(targets)
+    rows = o.shape[0] if o.ndim == 2 else 0
+    cols = o.shape[1] if o.ndim == 2 else 1
+    cm = np.zeros((classes, classes), np.uint64)
+    out = np.zeros(4, np.float32)
+    rc = load().zo_evaluate_classification(o.reshape(-1) if rows else np.zeros(1, np.float32),
+                                           t.reshape(-1) if rows else np.zeros(1, np.float32), rows, cols, classes, cm, out)
+    return rc, cm, out
 
 
 def clip_grad_norm(grads):

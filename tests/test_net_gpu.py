@@ -292,6 +292,23 @@ def test_remaining_activations_train(be, acts, prec, tol):
     compare_params(gnet, onet, tol, prec.name)
 
 
+@pytest.mark.parametrize("prec", [P.FP32_SIMT, P.BF16_TC])
+def test_network_evaluate_classification(be, prec):
+    """Train the 4-20-10-3 network on the Iris-shaped clusters, then evaluate on the device: the confusion matrix
+    equals the oracle's metrics of the SAME outputs, and training has made it mostly diagonal."""
+    x, t = iris_style(0)
+    gnet, _ = build_pair(be, prec, IRIS_DIMS, IRIS_ACTS, seed=0)
+    for _ in range(300):
+        gnet.trainStep(x, t, 0.005, zn.Loss.cross_entropy_logits)
+    cm, m = gnet.evaluateClassification(x, t, 3)
+    rc, wcm, wm = zo.evaluate_classification(gnet.forward(x), t, 3)
+    assert rc == 0 and np.array_equal(cm, wcm)
+    assert np.array_equal(np.array([m["accuracy"], m["precision"], m["recall"], m["f1_score"]], np.float32), wm)
+    assert int(cm.sum()) == 150 and m["accuracy"] > 0.9
+    with pytest.raises(zn.ZnError):
+        gnet.evaluateClassification(x, t, 2)                 # outputs have 3 classes: error.InvalidClass
+
+
 def test_pipelined_step_equals_blocking_step(be):
     rng = np.random.default_rng(4)
     B, dims, acts = 128, [(32, 64), (64, 16)], ["relu", "linear"]

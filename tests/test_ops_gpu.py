@@ -337,6 +337,43 @@ def test_rmsprop_update(be):
     assert abs(w1[0] - 0.99683772) < 1e-6 and abs(s1[0] - 1e-3) < 1e-9
 
 
+def test_evaluate_classification(be):
+    """metrics.evaluateClassification (src/metrics.zig:85-163, :213-264): the confusion matrix is integer work
+    and must be identical; the four ratios are f32 expressions of it, formed in the same order."""
+    o = np.array([[0.9, 0.05, 0.05], [0.1, 0.8, 0.1], [0.3, 0.3, 0.4], [0.6, 0.3, 0.1], [0.2, 0.2, 0.6], [0.5, 0.5, 0.0]], np.float32)
+    t = np.eye(3, dtype=np.float32)[[0, 1, 2, 1, 2, 1]]
+    cm, m = be.evaluateClassification(o, t, 3)
+    assert np.array_equal(cm, [[1, 0, 0], [2, 1, 0], [0, 0, 2]])
+    assert abs(m["accuracy"] - 2 / 3) < 1e-6 and abs(m["precision"] - 7 / 9) < 1e-6 and abs(m["f1_score"] - 7 / 9) < 1e-6
+    rng = np.random.default_rng(23)
+    for rows, cols, classes in [(1, 2, 2), (150, 3, 3), (4099, 10, 10), (2048, 100, 100), (5000, 40, 64), (777, 1000, 1000)]:
+        o = rng.standard_normal((rows, cols)).astype(np.float32)
+        o[rng.integers(0, rows, rows // 5), rng.integers(0, cols, rows // 5)] = 3.0     # ties between maxima
+        o[rng.integers(0, rows, rows // 7), rng.integers(0, cols, rows // 7)] = 3.0
+        o[rng.integers(0, rows, max(rows // 50, 1)), rng.integers(0, cols, max(rows // 50, 1))] = np.nan
+        o[rng.integers(0, rows, max(rows // 60, 1)), 0] = np.nan
+        t = np.eye(cols, dtype=np.float32)[rng.integers(0, cols, rows)]
+        t[rng.integers(0, rows, max(rows // 40, 1))] = 0.25                             # no entry above 0.5 -> class 0
+        rc, wcm, wm = zo.evaluate_classification(o, t, classes)
+        assert rc == 0
+        cm, m = be.evaluateClassification(o, t, classes)
+        assert np.array_equal(cm, wcm), (rows, cols)
+        got = np.array([m["accuracy"], m["precision"], m["recall"], m["f1_score"]], np.float32)
+        assert np.array_equal(got, wm), (rows, cols, got, wm)
+        assert int(cm.sum()) == rows
+    # device-resident operands
+    do, dt = be.tensor(o), be.tensor(t)
+    cm2, _ = be.evaluateClassification(do, dt, classes, rows=rows)
+    assert np.array_equal(cm2, wcm)
+    do.free(), dt.free()
+    with pytest.raises(zn.ZnError) as ei:                      # error.InvalidClass
+        be.evaluateClassification(np.array([[0.1, 0.2, 0.9]], np.float32), np.array([[1, 0, 0]], np.float32), 2)
+    assert ei.value.status == 1          # ZN_ERR_INVALID_VALUE
+    with pytest.raises(zn.ZnError) as ei:                      # error.EmptyInput
+        be.evaluateClassification(np.zeros((0, 3), np.float32), np.zeros((0, 3), np.float32), 3)
+    assert ei.value.status == 7
+
+
 def test_clip_grad_norm(be):
     rng = np.random.default_rng(10)
     grads = [rng.standard_normal(s).astype(np.float32) for s in (20 * 4, 20, 200 * 100 + 3, 1)]

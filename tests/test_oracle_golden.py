@@ -152,6 +152,24 @@ def test_remaining_activations_golden():
     assert np.allclose(y, 0.25)
 
 
+def test_classification_metrics_golden():
+    for case in KAT["classification_metrics"]:
+        o = f32(case["outputs"])
+        t = np.eye(case["classes"], dtype=np.float32)[case["true"]]
+        rc, cm, m = zo.evaluate_classification(o, t, case["classes"])
+        assert rc == 0 and np.array_equal(cm, np.array(case["confusion"], np.uint64))
+        want = [case[k] for k in ("accuracy", "precision", "recall", "f1_score")]
+        assert np.allclose(m, want, atol=case["tol"], rtol=0)
+    # error.EmptyInput and error.InvalidClass (src/metrics.zig:92, :105-110)
+    assert zo.evaluate_classification(np.zeros((0, 3), np.float32), np.zeros((0, 3), np.float32), 3)[0] == 1
+    o = np.array([[0.1, 0.2, 0.9]], np.float32)
+    assert zo.evaluate_classification(o, np.array([[1, 0, 0]], np.float32), 2)[0] == 2
+    # no target above 0.5 counts as class 0; a NaN in front pins the prediction to class 0
+    rc, cm, _ = zo.evaluate_classification(np.array([[np.nan, 5.0], [1.0, np.nan]], np.float32),
+                                           np.array([[0.2, 0.3], [0.0, 1.0]], np.float32), 2)
+    assert rc == 0 and np.array_equal(cm, [[1, 0], [1, 0]])
+
+
 def test_three_gemm_orientations_agree():
     rng = np.random.default_rng(7)
     m, n, k = 13, 9, 21

@@ -65,6 +65,7 @@ SIGNATURES = {
     "zn_sgd_update": (i32, [vp, vp, vp, sz, f32, f32]),
     "zn_sgd_update_bias": (i32, [vp, vp, vp, sz, f32]),
     "zn_adam_update": (i32, [vp, vp, vp, vp, vp, sz, f32, f32, f32, f32, f32, f32]),
+    "zn_evaluate_classification": (i32, [vp, vp, vp, sz, sz, sz, vp, vp]),
     "zn_rmsprop_update": (i32, [vp, vp, vp, vp, sz, f32, f32, f32]),
     "zn_clip_grad_norm": (i32, [vp, pvp, psz, sz, pf, pf]),
     "zn_net_create": (i32, [vp, i32, pvp]),
@@ -81,6 +82,7 @@ SIGNATURES = {
     "zn_net_set_adamw": (i32, [vp, i32, f32, f32, f32, f32]),
     "zn_net_set_rmsprop": (i32, [vp, i32, f32, f32, f32]),
     "zn_net_forward": (i32, [vp, vp, sz, vp]),
+    "zn_net_evaluate_classification": (i32, [vp, vp, vp, sz, sz, vp, vp]),
     "zn_net_train_step": (i32, [vp, vp, vp, sz, f32, i32, pf]),
     "zn_net_submit_step": (i32, [vp, vp, vp, sz, f32, i32]),
     "zn_net_wait_step": (i32, [vp, pf]),

@@ -183,6 +183,19 @@ class Backend:
         self._ck(lib.zn_loss_forward(self.handle, int(loss_fn), ptr(output), ptr(target), rows, n // rows, C.byref(out)))
         return out.value
 
+    # ---- metrics.evaluateClassification, src/metrics.zig:239-264
+    def evaluateClassification(self, outputs, targets, num_classes, rows=None):
+        """Returns (confusion[num_classes, num_classes] uint64 indexed [true][predicted],
+        dict(accuracy, precision, recall, f1_score))."""
+        if rows is None:
+            rows = outputs.shape[0] if isinstance(outputs, np.ndarray) and outputs.ndim == 2 else 0
+        cols = self._len(outputs) // rows if rows else 1
+        cm = np.zeros((num_classes, num_classes), np.uint64)
+        m = np.zeros(4, np.float32)
+        self._ck(lib.zn_evaluate_classification(self.handle, ptr(outputs), ptr(targets), rows, cols, num_classes,
+                                                cm.ctypes.data, m.ctypes.data))
+        return cm, dict(zip(("accuracy", "precision", "recall", "f1_score"), (float(v) for v in m)))
+
     # ---- optimizers, src/backend.zig:420-443, :640-646
     def sgdUpdate(self, weights, gradients, learning_rate, weight_decay):
         self._ck(lib.zn_sgd_update(self.handle, ptr(weights), ptr(gradients), self._len(weights), learning_rate, weight_decay))

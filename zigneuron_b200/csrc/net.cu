@@ -650,6 +650,30 @@ extern "C" zn_status zn_net_forward(zn_net *n, const float *input, size_t rows, 
     return zn_check_device_status(ctx);
 }
 
+extern "C" zn_status zn_net_evaluate_classification(zn_net *n, const float *input, const float *target, size_t rows,
+                                                    size_t num_classes, uint64_t *confusion, float *metrics4) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "EmptyInput: no samples to evaluate");
+    if (!input || !target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "evaluate_classification: null operand");
+    if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "pipelined steps in flight; wait for them first");
+    const size_t in = n->layers[0].in, out = n->layers.back().out;
+    Slot &s = n->slots[0];
+    ZN_TRY(ensure_slot(n, s, rows * in, rows * out));
+    const float *x_dev = input, *t_dev = target;
+    if (!zn_is_device_ptr(input)) {
+        ZN_CUDA(ctx, cudaMemcpyAsync(s.x, input, rows * in * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        x_dev = s.x;
+    }
+    if (!zn_is_device_ptr(target)) {
+        ZN_CUDA(ctx, cudaMemcpyAsync(s.t, target, rows * out * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        t_dev = s.t;
+    }
+    ZN_TRY(forward_dev(n, x_dev, rows));
+    const int64_t ld_o = n->tc ? (int64_t)out : n->lds[n->layers.size()];
+    return zn_k_classification_metrics(ctx, final_output(n), ld_o, t_dev, (int64_t)out, rows, out, num_classes, confusion, metrics4);
+}
+
 extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const float *target, size_t rows, float lr,
                                        zn_loss loss, float *loss_out) {
     ZN_TRY(check_net(n, true, true));

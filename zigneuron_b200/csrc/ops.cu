@@ -242,6 +242,19 @@ extern "C" zn_status zn_loss_backward(zn_ctx *ctx, zn_loss loss, const float *ou
     return finish(ctx, &G, O.host || T.host || G.host);
 }
 
+extern "C" zn_status zn_evaluate_classification(zn_ctx *ctx, const float *outputs, const float *targets, size_t rows,
+                                                size_t cols, size_t num_classes, uint64_t *confusion, float *metrics4) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "EmptyInput: no samples to evaluate");
+    if (!outputs || !targets) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "evaluate_classification: null operand");
+    if (cols == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "evaluate_classification: zero columns");
+    cudaSetDevice(ctx->device);
+    Operand O, T;
+    ZN_TRY(resolve(ctx, 0, outputs, rows * cols, true, &O));
+    ZN_TRY(resolve(ctx, 1, targets, rows * cols, true, &T));
+    return zn_k_classification_metrics(ctx, O.dev, (int64_t)cols, T.dev, (int64_t)cols, rows, cols, num_classes, confusion, metrics4);
+}
+
 extern "C" zn_status zn_sgd_update(zn_ctx *ctx, float *weights, const float *grads, size_t count, float learning_rate,
                                    float weight_decay) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;

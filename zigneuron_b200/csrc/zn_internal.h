@@ -169,6 +169,10 @@ zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev);
 zn_status zn_k_sumsq(zn_ctx *ctx, const zn_seg *segs, int nseg, double *sumsq_dev);
 zn_status zn_k_norm_combine(zn_ctx *ctx, const double *sumsq_dev, int count, float *norm_factor_dev);
 
+// metrics.evaluateClassification on fp32 device blocks; confusion / metrics4 are host memory (either may be null).
+zn_status zn_k_classification_metrics(zn_ctx *ctx, const float *out_dev, int64_t ld_o, const float *tgt_dev, int64_t ld_t,
+                                      size_t rows, size_t cols, size_t num_classes, uint64_t *confusion, float *metrics4);
+
 struct zn_opt_args {
     float *w; float *g; float *m; float *v; size_t count;
     float lr, wd, beta1, beta2, eps, bc1, bc2;

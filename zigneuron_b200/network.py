@@ -116,6 +116,20 @@ class Network:
         self._ck(lib.zn_net_forward(self.handle, ptr(x), rows, ptr(out)))
         return out
 
+    def evaluateClassification(self, input, target, num_classes, rows=None):
+        """Network.forward on the block, then metrics.evaluateClassification (src/metrics.zig:239-264), on the device."""
+        if isinstance(input, np.ndarray):
+            input = np.ascontiguousarray(input, np.float32)
+        if isinstance(target, np.ndarray):
+            target = np.ascontiguousarray(target, np.float32)
+        if rows is None:
+            rows = input.size // self.shapes[0][0]
+        cm = np.zeros((num_classes, num_classes), np.uint64)
+        m = np.zeros(4, np.float32)
+        self._ck(lib.zn_net_evaluate_classification(self.handle, ptr(input), ptr(target), rows, num_classes,
+                                                    cm.ctypes.data, m.ctypes.data))
+        return cm, dict(zip(("accuracy", "precision", "recall", "f1_score"), (float(v) for v in m)))
+
     # Network.trainStep, src/network.zig:481
     def trainStep(self, input, target, learning_rate, loss_fn, rows=None):
         if rows is None:
