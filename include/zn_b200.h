@@ -248,6 +248,14 @@ ZN_API zn_status zn_net_last_clip(zn_net *net, float *norm_out, float *factor_ou
  * in the other as long as every layer is Dense. */
 ZN_API zn_status zn_net_save(zn_net *net, const char *path);
 ZN_API zn_status zn_net_load(zn_ctx *ctx, zn_precision precision, const char *path, zn_net **out);
+/* Optimizer state beside the .znn file: per layer the optimizer kind, its hyper-parameters, the
+ * step count t and the state tensors (Adam / AdamW m and v, momentum velocity, RMSprop g_avg;
+ * src/optimizer.zig:81-88,169-184,236-250,311-320).  The reference's file format has no place
+ * for them (src/serialization.zig:165-183 writes weights and bias only), so a run restarted from
+ * a .znn alone restarts the moments; with this file it continues exactly.  The layout is this
+ * library's own ("ZNO\0", version 1).  Loading needs a network of the same layer shapes. */
+ZN_API zn_status zn_net_save_optimizer(zn_net *net, const char *path);
+ZN_API zn_status zn_net_load_optimizer(zn_net *net, const char *path);
 /* Pinned host memory for the pipelined step's inputs. */
 ZN_API zn_status zn_host_alloc(zn_ctx *ctx, size_t count, float **out_host);
 ZN_API zn_status zn_host_free(zn_ctx *ctx, float *host);

@@ -386,3 +386,48 @@ def test_znn_save_and_load(be, tmp_path):
     bad.write_bytes(want[:-5])
     with pytest.raises(zn.ZnError):
         zn.Network.load(be, str(bad))
+
+
+@pytest.mark.parametrize("opt", ["adam", "adamw", "momentum", "rmsprop", "sgd"])
+@pytest.mark.parametrize("prec", [P.FP32_SIMT, P.BF16_TC])
+def test_resume_with_optimizer_state(be, tmp_path, opt, prec):
+    """A run saved after 3 steps (.znn + optimizer state) and resumed in a fresh network continues bit for bit;
+    resumed from the .znn alone (all the reference's format holds, src/serialization.zig:165-183) it does not,
+    because the moments and the step count restart."""
+    rng = np.random.default_rng(21)
+    B, dims, acts = 64, [(24, 40), (40, 16), (16, 4)], ["relu", "tanh", "linear"]
+    x = rng.standard_normal((B, 24)).astype(np.float32)
+    t = rng.standard_normal((B, 4)).astype(np.float32)
+    kinds = {"adam": zn.Adam(weight_decay=0.01), "adamw": zn.AdamW(), "momentum": zn.Sgd(momentum=0.9),
+             "rmsprop": zn.Rmsprop(rho=0.8), "sgd": zn.Sgd(weight_decay=0.01)}
+    lr = 0.05 if opt in ("momentum", "sgd") else 1e-3
+    a = build_pair(be, prec, dims, acts, seed=21, bias_scale=0.1)[0]
+    a.setOptimizer(kinds[opt])
+    for _ in range(3):
+        a.trainStep(x, t, lr, zn.Loss.mse)
+    znn, zno = tmp_path / "net.znn", tmp_path / "net.zno"
+    a.save(znn)
+    a.saveOptimizer(zno)
+    b = zn.Network.load(be, znn, prec)
+    b.loadOptimizer(zno)
+    c = zn.Network.load(be, znn, prec)
+    c.setOptimizer(kinds[opt])
+    for _ in range(3):
+        la = a.trainStep(x, t, lr, zn.Loss.mse)
+        lb = b.trainStep(x, t, lr, zn.Loss.mse)
+        c.trainStep(x, t, lr, zn.Loss.mse)
+        assert la == lb
+    for i in range(3):
+        (Wa, ba), (Wb, bb), (Wc, _) = a.getWeights(i), b.getWeights(i), c.getWeights(i)
+        assert np.array_equal(Wa, Wb) and np.array_equal(ba, bb), (opt, i)
+        if opt != "sgd":
+            assert not np.array_equal(Wa, Wc), (opt, i)
+    # shape and format checks
+    other = zn.Network(be, prec)
+    other.addDense(24, 8, "relu")
+    with pytest.raises(zn.ZnError):
+        other.loadOptimizer(zno)
+    with pytest.raises(zn.ZnError):
+        b.loadOptimizer(znn)                     # wrong magic
+    for n in (a, b, c, other):
+        n.deinit()

@@ -90,6 +90,8 @@ SIGNATURES = {
     "zn_net_last_clip": (i32, [vp, pf, pf]),
     "zn_net_save": (i32, [vp, C.c_char_p]),
     "zn_net_load": (i32, [vp, i32, C.c_char_p, pvp]),
+    "zn_net_save_optimizer": (i32, [vp, C.c_char_p]),
+    "zn_net_load_optimizer": (i32, [vp, C.c_char_p]),
     "zn_host_alloc": (i32, [vp, sz, pvp]),
     "zn_host_free": (i32, [vp, vp]),
     "zn_distribute_workload": (i32, [sz, sz, sz, psz, psz]),

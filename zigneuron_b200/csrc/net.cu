@@ -855,6 +855,87 @@ extern "C" zn_status zn_net_load(zn_ctx *ctx, zn_precision precision, const char
     return ZN_OK;
 }
 
+// Optimizer state beside a .znn file.  The reference's format holds weights and biases only
+// (src/serialization.zig:165-183), so a run resumed from it restarts Adam's moments and step count; this
+// second file carries what Optimizer keeps per layer (src/optimizer.zig:81-88, :169-184, :236-250, :311-320):
+//   "ZNO\0", u32 version = 1, u32 layer count, then per layer
+//   u32 kind (0 sgd, 1 adam, 2 momentum sgd, 3 adamw, 4 rmsprop), u32 input size, u32 output size, u64 t,
+//   f32 beta1, beta2, eps, weight_decay, momentum, rho, u32 state tensors S (0, 1 or 2),
+//   S x { f32 [in*out] weight-shaped part, f32 [out] bias-shaped part }     (m then v; velocity; g_avg)
+namespace {
+constexpr uint32_t ZNO_VERSION = 1;
+int state_tensors(int opt) { return opt == OPT_SGD ? 0 : (opt == OPT_ADAM || opt == OPT_ADAMW) ? 2 : 1; }
+}   // namespace
+
+extern "C" zn_status zn_net_save_optimizer(zn_net *n, const char *path) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!path) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "save_optimizer: null path");
+    FILE *f = fopen(path, "wb");
+    if (!f) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "save_optimizer: cannot open %s", path);
+    bool ok = fwrite("ZNO\0", 1, 4, f) == 4 && put_u32(f, ZNO_VERSION) && put_u32(f, (uint32_t)n->layers.size());
+    std::vector<float> host;
+    for (size_t i = 0; i < n->layers.size() && ok; ++i) {
+        const Layer &l = n->layers[i];
+        const uint64_t t = l.t;
+        const float hp[6] = {l.beta1, l.beta2, l.eps, l.wd, l.momentum, l.rho};
+        const int S = state_tensors(l.opt);
+        ok = put_u32(f, (uint32_t)l.opt) && put_u32(f, (uint32_t)l.in) && put_u32(f, (uint32_t)l.out) &&
+             fwrite(&t, 8, 1, f) == 1 && fwrite(hp, 4, 6, f) == 6 && put_u32(f, (uint32_t)S);
+        for (int k = 0; k < S && ok; ++k) {
+            const float *src = k == 0 ? l.m : l.v;
+            host.resize(l.len);
+            if (!src || cudaMemcpyAsync(host.data(), src, l.len * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+                cudaStreamSynchronize(ctx->stream) != cudaSuccess) { ok = false; break; }
+            ok = fwrite(host.data(), sizeof(float), l.in * l.out, f) == l.in * l.out &&
+                 fwrite(host.data() + l.b_off, sizeof(float), l.out, f) == l.out;
+        }
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) return zn_fail(ctx, ZN_ERR_CUDA, "save_optimizer: writing %s failed", path);
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_net_load_optimizer(zn_net *n, const char *path) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!path) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load_optimizer: null path");
+    FILE *f = fopen(path, "rb");
+    if (!f) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "load_optimizer: cannot open %s", path);
+    char magic[4];
+    uint32_t version = 0, count = 0;
+    zn_status st = ZN_OK;
+    if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "ZNO\0", 4) != 0) st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "InvalidMagic: %s is not an optimizer-state file", path);
+    else if (!get_u32(f, &version) || version != ZNO_VERSION) st = zn_fail(ctx, ZN_ERR_UNSUPPORTED, "UnsupportedVersion %u", version);
+    else if (!get_u32(f, &count) || count != n->layers.size()) st = zn_fail(ctx, ZN_ERR_SHAPE, "load_optimizer: file has %u layers, the network %zu", count, n->layers.size());
+    std::vector<float> host;
+    for (uint32_t i = 0; i < count && st == ZN_OK; ++i) {
+        Layer &l = n->layers[i];
+        uint32_t kind = 0, in = 0, o = 0, S = 0;
+        uint64_t t = 0;
+        float hp[6];
+        if (!get_u32(f, &kind) || !get_u32(f, &in) || !get_u32(f, &o) || fread(&t, 8, 1, f) != 1 || fread(hp, 4, 6, f) != 6 || !get_u32(f, &S)) {
+            st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load_optimizer: truncated layer header"); break;
+        }
+        if (kind > OPT_RMSPROP || (int)S != state_tensors((int)kind)) { st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load_optimizer: layer %u has kind %u with %u state tensors", i, kind, S); break; }
+        if (in != l.in || o != l.out) { st = zn_fail(ctx, ZN_ERR_SHAPE, "load_optimizer: layer %u is %u x %u in the file, %zu x %zu in the network", i, in, o, l.in, l.out); break; }
+        l.opt = (int)kind; l.t = (size_t)t;
+        l.beta1 = hp[0]; l.beta2 = hp[1]; l.eps = hp[2]; l.wd = hp[3]; l.momentum = hp[4]; l.rho = hp[5];
+        if (S > 0) st = reset_state(n, l, S == 2);
+        for (uint32_t k = 0; k < S && st == ZN_OK; ++k) {
+            host.assign(l.blk + 4, 0.0f);
+            if (fread(host.data(), sizeof(float), l.in * l.out, f) != l.in * l.out || fread(host.data() + l.b_off, sizeof(float), l.out, f) != l.out) {
+                st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load_optimizer: truncated state of layer %u", i); break;
+            }
+            float *dst = k == 0 ? l.m : l.v;
+            if (cudaMemcpyAsync(dst, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+                cudaStreamSynchronize(ctx->stream) != cudaSuccess) st = zn_fail(ctx, ZN_ERR_CUDA, "load_optimizer: upload failed");
+        }
+    }
+    fclose(f);
+    return st;
+}
+
 extern "C" zn_status zn_net_set_data_parallel(zn_net *n, size_t global_rows) {
     ZN_TRY(check_net(n, true));
     if (global_rows > 0 && !zn_dp_active(n->ctx))

@@ -163,6 +163,13 @@ class Network:
     def save(self, path):
         self._ck(lib.zn_net_save(self.handle, os.fsencode(path)))
 
+    def saveOptimizer(self, path):
+        """Optimizer kind, hyper-parameters, step count and state tensors of every layer (not part of .znn)."""
+        self._ck(lib.zn_net_save_optimizer(self.handle, os.fsencode(path)))
+
+    def loadOptimizer(self, path):
+        self._ck(lib.zn_net_load_optimizer(self.handle, os.fsencode(path)))
+
     @classmethod
     def load(cls, backend, path, precision=None):
         net = cls.__new__(cls)
