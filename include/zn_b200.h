@@ -71,7 +71,8 @@ typedef enum {
     ZN_ACT_LINEAR = 4, ZN_ACT_GELU = 5, ZN_ACT_LEAKY_RELU = 6, ZN_ACT_ELU = 7
 } zn_activation;
 
-/* Same order as `Loss` in src/loss.zig:12-22.  MSE and CROSS_ENTROPY_LOGITS are on the path. */
+/* Same order as `Loss` in src/loss.zig:12-22.  All but KL_DIVERGENCE are taken (that one splits a single
+ * output vector into [mu | log_var], src/loss.zig:62-92, and has no batched form): ZN_ERR_UNSUPPORTED. */
 typedef enum {
     ZN_LOSS_MSE = 0, ZN_LOSS_CROSS_ENTROPY = 1, ZN_LOSS_CROSS_ENTROPY_LOGITS = 2,
     ZN_LOSS_BINARY_CROSS_ENTROPY = 3, ZN_LOSS_KL_DIVERGENCE = 4

@@ -228,7 +228,62 @@ ZO_API void zo_ce_logits_backward(const float *logits, const float *target, floa
     for (size_t i = 0; i < n; ++i) g[i] = (g[i] / sum_exp) - target[i];
 }
 
-/* Row-wise batching of the two functions above: gradient per row with no 1/B
+/* Loss.crossEntropyForward, src/loss.zig:110-169: despite the enum's comment it takes LOGITS; the
+ * exponent is clamped to [-50, 50], every target entry above 0.5 contributes and the result is
+ * their mean; degenerate inputs give 0. */
+ZO_API float zo_ce_forward(const float *o, const float *t, size_t n) {
+    if (n == 0) return 0;
+    float mx = -INFINITY;
+    for (size_t i = 0; i < n; ++i) if (o[i] > mx) mx = o[i];
+    if (mx == -INFINITY) return 0;
+    float lse = 0;
+    for (size_t i = 0; i < n; ++i) {
+        const float diff = o[i] - mx;
+        const float cd = diff > 50 ? 50 : (diff < -50 ? -50 : diff);
+        lse += expf(cd);
+    }
+    if (!isfinite(lse) || lse <= 0) return 0;
+    lse = logf(lse) + mx;
+    float loss_sum = 0, count = 0;
+    for (size_t i = 0; i < n; ++i)
+        if (t[i] > 0.5f) { loss_sum += lse - o[i]; count += 1; }
+    if (count == 0) return 0;
+    return loss_sum / count;
+}
+
+/* Loss.crossEntropyBackward, src/loss.zig:171-196: softmax(output) - target. */
+ZO_API void zo_ce_backward(const float *o, const float *t, float *g, size_t n) {
+    zo_ce_logits_backward(o, t, g, n);      /* the same arithmetic, statement for statement */
+}
+
+/* Loss.binaryCrossEntropyForward, src/loss.zig:255-274 (outputs are probabilities). */
+ZO_API float zo_bce_forward(const float *o, const float *t, size_t n) {
+    float sum = 0;
+    const float eps = 1e-7f;
+    for (size_t i = 0; i < n; ++i) {
+        float p = o[i];
+        if (p < eps) p = eps;
+        if (p > 1 - eps) p = 1 - eps;
+        float q = 1 - p;
+        if (q < eps) q = eps;
+        if (q > 1 - eps) q = 1 - eps;
+        sum -= t[i] * logf(p) + (1 - t[i]) * logf(q);
+    }
+    return sum / (float)n;
+}
+
+/* Loss.binaryCrossEntropyBackward, src/loss.zig:286-302: (p - t) / n, n = elements handed in. */
+ZO_API void zo_bce_backward(const float *o, const float *t, float *g, size_t n, size_t divisor) {
+    const float nf = (float)divisor, eps = 1e-7f;
+    for (size_t i = 0; i < n; ++i) {
+        float p = o[i];
+        if (p < eps) p = eps;
+        if (p > 1.0f - eps) p = 1.0f - eps;
+        g[i] = (p - t[i]) / nf;
+    }
+}
+
+/* Row-wise batching of the per-vector cross-entropies: gradient per row with no 1/B
  * (kernels/loss.cu:123-155), loss = mean over rows (kernels/loss.cu:175-213,
  * `total_loss / num_samples`); each row uses the src/loss.zig formulas. */
 ZO_API float zo_ce_logits_rows(const float *logits, const float *target, float *g,
@@ -241,16 +296,26 @@ ZO_API float zo_ce_logits_rows(const float *logits, const float *target, float *
     return total / (float)rows;
 }
 
-/* src/loss.zig:34-60 dispatch.  `rows` > 1 selects the row-wise CE above; MSE
- * is flat over all rows*cols elements either way. */
+static int loss_is_flat(int loss) { return loss == ZO_MSE || loss == ZO_BCE; }
+
+/* src/loss.zig:34-60 dispatch.  MSE and BCE are flat over all rows*cols elements; the
+ * cross-entropies are taken row by row and averaged over the rows (one row: the plain call). */
 ZO_API float zo_loss_forward(int loss, const float *o, const float *t, size_t rows, size_t cols) {
     if (loss == ZO_MSE) return zo_mse_forward(o, t, rows * cols);
+    if (loss == ZO_BCE) return zo_bce_forward(o, t, rows * cols);
+    if (loss == ZO_CE) {
+        if (rows == 1) return zo_ce_forward(o, t, cols);
+        float total = 0;
+        for (size_t r = 0; r < rows; ++r) total += zo_ce_forward(o + r * cols, t + r * cols, cols);
+        return total / (float)rows;
+    }
     if (rows == 1) return zo_ce_logits_forward(o, t, cols);
     return zo_ce_logits_rows(o, t, NULL, rows, cols);
 }
 
 ZO_API void zo_loss_backward(int loss, const float *o, const float *t, float *g, size_t rows, size_t cols) {
     if (loss == ZO_MSE) { zo_mse_backward(o, t, g, rows * cols); return; }
+    if (loss == ZO_BCE) { zo_bce_backward(o, t, g, rows * cols, rows * cols); return; }
     for (size_t r = 0; r < rows; ++r)
         zo_ce_logits_backward(o + r * cols, t + r * cols, g + r * cols, cols);
 }
@@ -569,6 +634,9 @@ static float net_gradients(zo_net *net, const float *x, const float *t, size_t r
             grad[i] = 2 * (last->y_cache[i] - t[i]) / nf;
         }
         loss_val = sum / nf;
+    } else if (loss == ZO_BCE) {                     /* flat like MSE: the divisor is the (global) element count */
+        zo_bce_backward(last->y_cache, t, grad, rows * cols, mse_count);
+        loss_val = zo_bce_forward(last->y_cache, t, rows * cols) * ((float)(rows * cols) / (float)mse_count);
     } else {
         zo_loss_backward(loss, last->y_cache, t, grad, rows, cols);
         loss_val = zo_loss_forward(loss, last->y_cache, t, rows, cols);
@@ -656,7 +724,7 @@ ZO_API float zo_net_shard_gradients(zo_net *net, const float *x, const float *t,
                                     size_t global_rows, int loss) {
     const size_t cols = net->layers[net->count - 1].out;
     const float l = net_gradients(net, x, t, rows, loss, global_rows * cols, 0);
-    return (loss == ZO_MSE) ? l : l * (float)rows;
+    return loss_is_flat(loss) ? l : l * (float)rows;
 }
 
 /* Second half of a data-parallel step: gradients already summed into the

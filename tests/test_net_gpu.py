@@ -309,6 +309,25 @@ def test_network_evaluate_classification(be, prec):
         gnet.evaluateClassification(x, t, 2)                 # outputs have 3 classes: error.InvalidClass
 
 
+@pytest.mark.parametrize("prec,tol", [(P.FP32_EXACT, 1e-5), (P.FP32_SIMT, 1e-5), (P.BF16_TC, 2e-2)])
+def test_bce_and_plain_cross_entropy_training(be, prec, tol):
+    """Sigmoid output + binary cross-entropy, and linear output + Loss.cross_entropy (src/loss.zig:110-196,255-302):
+    four training steps against the oracle."""
+    rng = np.random.default_rng(29)
+    B = 128
+    x = rng.standard_normal((B, 16)).astype(np.float32)
+    for loss_g, loss_o, last, t in [
+        (zn.Loss.binary_cross_entropy, zo.BCE, "sigmoid", (rng.uniform(0, 1, (B, 5)) > 0.5).astype(np.float32)),
+        (zn.Loss.cross_entropy, zo.CE, "linear", np.eye(5, dtype=np.float32)[rng.integers(0, 5, B)]),
+    ]:
+        gnet, onet = build_pair(be, prec, [(16, 32), (32, 5)], ["relu", last], seed=29, bias_scale=0.1)
+        for _ in range(4):
+            lg = gnet.trainStep(x, t, 0.05, loss_g)
+            lo = onet.train_step(x, t, B, 0.05, loss_o)
+            assert abs(lg - lo) <= tol * max(1.0, abs(lo)), (loss_g, lg, lo)
+        compare_params(gnet, onet, tol, f"{prec.name} {loss_g.name}")
+
+
 def test_pipelined_step_equals_blocking_step(be):
     rng = np.random.default_rng(4)
     B, dims, acts = 128, [(32, 64), (64, 16)], ["relu", "linear"]

@@ -283,7 +283,53 @@ def test_losses(be):
         want = zo.loss_forward(zo.CE_LOGITS, o, t, rows, cols)
         assert abs(got - want) <= 1e-5 * max(1.0, abs(want)), (rows, cols)
     with pytest.raises(zn.ZnError):
-        be.lossForward(zn.Loss.binary_cross_entropy, o, t, rows)
+        be.lossForward(zn.Loss.kl_divergence, o, t, rows)
+
+
+def test_cross_entropy_and_bce_losses(be):
+    """Loss.cross_entropy (src/loss.zig:110-196) and Loss.binary_cross_entropy (:255-302)."""
+    # golden: src/test/unit/loss.zig:63-113
+    got = be.lossForward(zn.Loss.cross_entropy, np.array([1, 0], np.float32), np.array([1, 0], np.float32))
+    assert abs(got - 0.31326169) < 1e-6
+    g = np.empty(2, np.float32)
+    be.lossBackward(zn.Loss.cross_entropy, np.zeros(2, np.float32), np.array([1, 0], np.float32), g)
+    assert np.allclose(g, [-0.5, 0.5], atol=1e-6)
+    got = be.lossForward(zn.Loss.binary_cross_entropy, np.array([0.01, 0.99], np.float32), np.array([0, 1], np.float32))
+    assert abs(got - 0.01005034) < 1e-6
+    be.lossBackward(zn.Loss.binary_cross_entropy, np.array([0.7, 0.3], np.float32), np.array([1, 0], np.float32), g)
+    assert np.allclose(g, [-0.15, 0.15], atol=1e-6)
+    rng = np.random.default_rng(28)
+    bx = zn.Backend(precision=zn.Precision.FP32_EXACT)
+    for rows, cols in [(1, 3), (150, 3), (1024, 10), (33, 1000)]:
+        o = (rng.standard_normal((rows, cols)) * 2).astype(np.float32)
+        t = np.eye(cols, dtype=np.float32)[rng.integers(0, cols, rows)]
+        t[rng.integers(0, rows, rows // 8), rng.integers(0, cols, rows // 8)] = 1.0        # some multi-hot rows
+        t[rng.integers(0, rows, max(rows // 16, 1))] = 0.0                                   # some rows without a target
+        g = np.empty((rows, cols), np.float32)
+        be.lossBackward(zn.Loss.cross_entropy, o, t, g, rows)
+        assert_close(g, zo.loss_backward(zo.CE, o, t, rows, cols), 1e-5, f"ce grad {rows}x{cols}")
+        want = zo.loss_forward(zo.CE, o, t, rows, cols)
+        for b_, tol in ((be, 2e-6), (bx, 1e-6)):
+            got = b_.lossForward(zn.Loss.cross_entropy, o, t, rows)
+            assert abs(got - want) <= tol * max(1.0, abs(want)), (rows, cols, got, want)
+        p = rng.uniform(0, 1, (rows, cols)).astype(np.float32)
+        p[rng.integers(0, rows, max(rows // 10, 1)), rng.integers(0, cols, max(rows // 10, 1))] = 0.0       # clamped
+        p[rng.integers(0, rows, max(rows // 10, 1)), rng.integers(0, cols, max(rows // 10, 1))] = 1.0
+        tb = (rng.uniform(0, 1, (rows, cols)) > 0.5).astype(np.float32)
+        be.lossBackward(zn.Loss.binary_cross_entropy, p, tb, g, rows)
+        assert np.array_equal(g, zo.loss_backward(zo.BCE, p, tb, rows, cols))
+        want = zo.loss_forward(zo.BCE, p, tb, rows, cols)
+        exact64 = float(np.mean(-(tb * np.log(np.clip(p, np.float32(1e-7), np.float32(1) - np.float32(1e-7)).astype(np.float64))
+                                  + (1 - tb) * np.log(np.clip(np.float32(1) - np.clip(p, np.float32(1e-7), np.float32(1) - np.float32(1e-7)),
+                                                              np.float32(1e-7), np.float32(1) - np.float32(1e-7)).astype(np.float64)))))
+        got = be.lossForward(zn.Loss.binary_cross_entropy, p, tb, rows)
+        assert abs(got - exact64) <= 2e-6 * exact64, (rows, cols, got, exact64)
+        got = bx.lossForward(zn.Loss.binary_cross_entropy, p, tb, rows)          # the reference's running f32 sum
+        assert abs(got - want) <= 2e-6 * want, (rows, cols, got, want)
+    bx.deinit()
+    # degenerate rows of cross_entropy give 0
+    assert be.lossForward(zn.Loss.cross_entropy, np.array([1, 2, 3], np.float32), np.zeros(3, np.float32)) == 0.0
+    assert be.lossForward(zn.Loss.cross_entropy, np.full(3, -np.inf, np.float32), np.array([1, 0, 0], np.float32)) == 0.0
 
 
 def test_optimizers(be):

@@ -78,6 +78,34 @@ def test_loss_golden():
         assert np.allclose(got, f32(case["expected"]), atol=case["tol"], rtol=0)
 
 
+def test_remaining_losses_golden():
+    kat = KAT["losses_n2"]
+    for case in kat["ce_forward"]:
+        got = zo.loss_forward(zo.CE, f32(case["o"]), f32(case["t"]), 1, len(case["o"]))
+        assert abs(got - case["expected"]) < case["tol"] and 0 <= got < 1.0
+    for case in kat["ce_backward"]:
+        got = zo.loss_backward(zo.CE, f32(case["o"]), f32(case["t"]), 1, len(case["o"])).reshape(-1)
+        assert np.allclose(got, f32(case["expected"]), atol=case["tol"], rtol=0)
+    for case in kat["bce_forward"]:
+        got = zo.loss_forward(zo.BCE, f32(case["o"]), f32(case["t"]), 1, len(case["o"]))
+        assert abs(got - case["expected"]) < case["tol"] and 0 <= got < 0.1
+    for case in kat["bce_backward"]:
+        got = zo.loss_backward(zo.BCE, f32(case["o"]), f32(case["t"]), 1, len(case["o"])).reshape(-1)
+        assert np.allclose(got, f32(case["expected"]), atol=case["tol"], rtol=0)
+    # degenerate inputs of crossEntropyForward give 0 (src/loss.zig:126-129, :144-146, :166-167)
+    assert zo.loss_forward(zo.CE, np.full(3, -np.inf, np.float32), f32([1, 0, 0]), 1, 3) == 0.0
+    assert zo.loss_forward(zo.CE, f32([1, 2, 3]), f32([0, 0, 0]), 1, 3) == 0.0
+    # two entries above 0.5: the mean of their losses
+    o = f32([0.5, -1.0, 2.0])
+    lse = np.log(np.exp(o - 2.0).sum()) + 2.0
+    got = zo.loss_forward(zo.CE, o, f32([1, 0, 1]), 1, 3)
+    assert abs(got - ((lse - 0.5) + (lse - 2.0)) / 2) < 1e-6
+    # BCE clamps probabilities to [1e-7, 1 - 1e-7]
+    got = zo.loss_forward(zo.BCE, f32([0.0, 1.0]), f32([1.0, 0.0]), 1, 2)
+    one_minus = np.float32(1.0) - (np.float32(1.0) - np.float32(1e-7))      # 1.19e-7 in f32, not 1e-7
+    assert abs(got - (-np.log(np.float32(1e-7)) - np.log(one_minus)) / 2) < 1e-5
+
+
 def test_optimizer_golden():
     for case in KAT["sgd"]:
         got = zo.sgd_update(f32(case["w"]), f32(case["g"]), case["lr"])

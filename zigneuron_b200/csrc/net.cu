@@ -344,10 +344,13 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     return ZN_OK;
 }
 
+// kl_divergence (src/loss.zig:62-92) splits ONE output vector into [mu | log_var] and has no batched meaning.
+bool loss_supported(int loss) { return loss >= ZN_LOSS_MSE && loss <= ZN_LOSS_BINARY_CROSS_ENTROPY; }
+
 float loss_from_sum(const zn_net *n, float sum, size_t rows, int loss) {
     const size_t total_rows = (n->global_rows > 0 && zn_dp_active(n->ctx)) ? n->global_rows : rows;
     const size_t cols = n->layers.back().out;
-    if (loss == ZN_LOSS_MSE) return sum / (float)(total_rows * cols);
+    if (loss == ZN_LOSS_MSE || loss == ZN_LOSS_BINARY_CROSS_ENTROPY) return sum / (float)(total_rows * cols);
     return total_rows > 1 ? sum / (float)total_rows : sum;
 }
 
@@ -680,8 +683,7 @@ extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const floa
     zn_ctx *ctx = n->ctx;
     if (!input || !target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "train_step: null operand");
     if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "train_step: zero rows");
-    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
-        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
+    if (!loss_supported(loss)) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
     if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "pipelined steps in flight; wait for them first");
     const size_t in = n->layers[0].in, out = n->layers.back().out;
     Slot &s = n->slots[0];
@@ -711,8 +713,7 @@ extern "C" zn_status zn_net_submit_step(zn_net *n, const float *host_input, cons
     zn_ctx *ctx = n->ctx;
     if (!host_input || !host_target) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "submit_step: null operand");
     if (rows == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "submit_step: zero rows");
-    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
-        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
+    if (!loss_supported(loss)) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
     if (n->inflight >= 2) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "two steps already in flight");
     const size_t in = n->layers[0].in, out = n->layers.back().out;
     const int idx = (n->head + n->inflight) & 1;
@@ -752,8 +753,7 @@ extern "C" zn_status zn_net_train(zn_net *n, const float *inputs, const float *t
     zn_ctx *ctx = n->ctx;
     if (!inputs || !targets) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "train: null operand");
     if (samples == 0) return zn_fail(ctx, ZN_ERR_SHAPE, "train: no samples");
-    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
-        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
+    if (!loss_supported(loss)) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path", (int)loss);
     if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "pipelined steps in flight");
     const size_t in = n->layers[0].in, out = n->layers.back().out;
     Slot &s = n->slots[0];

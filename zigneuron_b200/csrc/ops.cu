@@ -223,7 +223,8 @@ extern "C" zn_status zn_loss_forward(zn_ctx *ctx, zn_loss loss, const float *out
     ZN_CUDA(ctx, cudaMemcpyAsync(ctx->pinned_scalar, ctx->stage[3], sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     const float sum = ctx->pinned_scalar[0];
-    *loss_out = (loss == ZN_LOSS_MSE) ? sum / (float)(rows * cols) : (rows > 1 ? sum / (float)rows : sum);
+    const bool flat = loss == ZN_LOSS_MSE || loss == ZN_LOSS_BINARY_CROSS_ENTROPY;
+    *loss_out = flat ? sum / (float)(rows * cols) : (rows > 1 ? sum / (float)rows : sum);
     return zn_check_device_status(ctx);
 }
 

@@ -304,13 +304,51 @@ __global__ void mse_kernel(const float *__restrict__ out, int64_t ld_o, const fl
     if (threadIdx.x == 0) partial[blockIdx.x] = s;
 }
 
+// Binary cross-entropy on probabilities (src/loss.zig:255-302): p clamped to [1e-7, 1 - 1e-7], so is 1 - p;
+// loss term -(t*log(p) + (1-t)*log(1-p)), grad = (p - t)/n.  partial[block] = sum of the block's terms.
+__device__ __forceinline__ float bce_term(float o, float t, float &p) {
+    const float eps = 1e-7f;
+    p = o;
+    if (p < eps) p = eps;
+    if (p > 1.f - eps) p = 1.f - eps;
+    float q = __fsub_rn(1.f, p);
+    if (q < eps) q = eps;
+    if (q > 1.f - eps) q = 1.f - eps;
+    return __fadd_rn(__fmul_rn(t, logf(p)), __fmul_rn(__fsub_rn(1.f, t), logf(q)));
+}
+
+template <typename T>
+__global__ void bce_kernel(const float *__restrict__ out, int64_t ld_o, const float *__restrict__ target,
+                           T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float n_div,
+                           float *__restrict__ partial) {
+    const int64_t total = rows * cols;
+    float s = 0.f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i % cols;
+        const float t = target[i];
+        float p;
+        s -= bce_term(out[r * ld_o + c], t, p);
+        if (grad) grad[r * ld_g + c] = from_f32<T>(__fdiv_rn(__fsub_rn(p, t), n_div));
+    }
+    s = block_sum(s);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+// Row loss of Loss.crossEntropyForward (src/loss.zig:110-169), the variant WITHOUT "_logits" in its name,
+// which takes logits all the same: exponents clamped to [-50, 50], every target entry above 0.5
+// contributes lse - o, the row's loss is their mean, degenerate rows give 0.
+__device__ __forceinline__ float ce_plain_row_loss(float mx, float sum_clamped, float loss_sum, float count) {
+    if (mx == -INFINITY || !isfinite(sum_clamped) || sum_clamped <= 0.f || count == 0.f) return 0.f;
+    return __fdiv_rn(loss_sum, count);
+}
+
 // Softmax cross-entropy with logits, one warp per row (src/loss.zig:202-254 per row;
 // rows batched as kernels/loss.cu:123-155): grad = exp(l-max)/sum - t, row loss =
 // -(l[target] - (log(sum) + max)) with target = first column whose t > 0.5.
 template <typename T>
 __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const float *__restrict__ target,
                           T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float *__restrict__ partial,
-                          int exact) {
+                          int exact, int plain) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     float loss_acc = 0.f;
     for (int64_t r = (int64_t)blockIdx.x * wpb + w; r < rows; r += (int64_t)gridDim.x * wpb) {
@@ -337,7 +375,20 @@ __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const 
             for (int64_t c = lane; c < cols; c += 32)
                 g[c] = from_f32<T>(__fsub_rn(__fdiv_rn(expf(l[c] - mx), se), t[c]));
         }
-        if (lane == 0 && first != INT64_MAX) loss_acc += -(l[first] - (logf(se) + mx));
+        if (!plain) {
+            if (lane == 0 && first != INT64_MAX) loss_acc += -(l[first] - (logf(se) + mx));
+        } else {
+            float sec = 0.f;
+            for (int64_t c = lane; c < cols; c += 32) sec += expf(fminf(50.f, fmaxf(-50.f, l[c] - mx)));
+            sec = warp_sum(sec);
+            const float lse = logf(sec) + mx;
+            float ls = 0.f, cnt = 0.f;
+            for (int64_t c = lane; c < cols; c += 32)
+                if (t[c] > 0.5f) { ls += lse - l[c]; cnt += 1.f; }
+            ls = warp_sum(ls);
+            cnt = warp_sum(cnt);
+            if (lane == 0) loss_acc += ce_plain_row_loss(mx, sec, ls, cnt);
+        }
     }
     loss_acc = block_sum(loss_acc);
     if (threadIdx.x == 0) partial[blockIdx.x] = loss_acc;
@@ -355,6 +406,21 @@ __global__ void loss_sum_exact_kernel(int loss, const float *__restrict__ out, i
                 const float d = __fsub_rn(o[c], t[c]);
                 total = __fadd_rn(total, __fmul_rn(d, d));
             }
+        } else if (loss == ZN_LOSS_BINARY_CROSS_ENTROPY) {
+            for (int64_t c = 0; c < cols; ++c) {
+                float p;
+                total = __fsub_rn(total, bce_term(o[c], t[c], p));
+            }
+        } else if (loss == ZN_LOSS_CROSS_ENTROPY) {
+            float mx = -INFINITY;
+            for (int64_t c = 0; c < cols; ++c) if (o[c] > mx) mx = o[c];
+            float sec = 0.f;
+            for (int64_t c = 0; c < cols; ++c) sec = __fadd_rn(sec, expf(fminf(50.f, fmaxf(-50.f, __fsub_rn(o[c], mx)))));
+            const float lse = __fadd_rn(logf(sec), mx);
+            float ls = 0.f, cnt = 0.f;
+            for (int64_t c = 0; c < cols; ++c)
+                if (t[c] > 0.5f) { ls = __fadd_rn(ls, __fsub_rn(lse, o[c])); cnt += 1.f; }
+            total = __fadd_rn(total, ce_plain_row_loss(mx, sec, ls, cnt));
         } else {
             float mx = o[0];
             for (int64_t c = 1; c < cols; ++c) if (o[c] > mx) mx = o[c];
@@ -612,11 +678,13 @@ extern "C" zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, s
 
 zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const float *target, void *grad, bool grad_bf16,
                     int64_t ld_g, int64_t rows, int64_t cols, float mse_divisor, float *loss_sum_dev, bool exact) {
-    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS)
-        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path (mse and cross_entropy_logits are)", loss);
+    if (loss != ZN_LOSS_MSE && loss != ZN_LOSS_CROSS_ENTROPY_LOGITS && loss != ZN_LOSS_CROSS_ENTROPY && loss != ZN_LOSS_BINARY_CROSS_ENTROPY)
+        return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "loss %d is not on the Dense path (kl_divergence has no batched form)", loss);
     const int64_t total = rows * cols;
+    const bool flat = loss == ZN_LOSS_MSE || loss == ZN_LOSS_BINARY_CROSS_ENTROPY;
     int grid;
     if (loss == ZN_LOSS_MSE) grid = grid_for(ctx, (total + 3) / 4, 4);
+    else if (flat) grid = grid_for(ctx, total, 4);
     else grid = grid_for(ctx, rows * 32, 8);
     ZN_TRY(zn_scratch_reserve(ctx, (size_t)grid));
     zn_launch_scope scope(ctx, ZN_PROF_LOSS, 0, (double)total * (8 + (grad ? (grad_bf16 ? 2 : 4) : 0)), 2);
@@ -625,11 +693,17 @@ zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const
             mse_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
         else
             mse_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
-    } else {
+    } else if (loss == ZN_LOSS_BINARY_CROSS_ENTROPY) {
         if (grad_bf16)
-            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0);
+            bce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
         else
-            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0);
+            bce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+    } else {
+        const int plain = loss == ZN_LOSS_CROSS_ENTROPY ? 1 : 0;
+        if (grad_bf16)
+            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain);
+        else
+            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain);
     }
     if (exact) loss_sum_exact_kernel<<<1, 1, 0, ctx->stream>>>(loss, out, ld_o, target, rows, cols, loss_sum_dev);
     else sum_partials_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, grid, loss_sum_dev);
