@@ -13,6 +13,7 @@
 
 #include <cstring>
 
+#include <cstdlib>
 #include "zn_internal.h"
 
 namespace {
@@ -26,6 +27,11 @@ struct NcclApi {
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    // optional (NCCL >= 2.19): memory the collectives can work on in place
+    ncclResult_t (*MemAlloc)(void **, size_t) = nullptr;
+    ncclResult_t (*MemFree)(void *) = nullptr;
+    ncclResult_t (*CommRegister)(const ncclComm_t, void *, size_t, void **) = nullptr;
+    ncclResult_t (*CommDeregister)(const ncclComm_t, void *) = nullptr;
     bool ok = false;
 };
 
@@ -48,6 +54,10 @@ NcclApi &api() {
     ZN_SYM(AllReduce, "ncclAllReduce");
     ZN_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     ZN_SYM(GetErrorString, "ncclGetErrorString");
+    ZN_SYM(MemAlloc, "ncclMemAlloc");
+    ZN_SYM(MemFree, "ncclMemFree");
+    ZN_SYM(CommRegister, "ncclCommRegister");
+    ZN_SYM(CommDeregister, "ncclCommDeregister");
 #undef ZN_SYM
     a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.GetErrorString;
     return a;
@@ -64,9 +74,42 @@ bool zn_dp_active(const zn_ctx *ctx) { return ctx && ctx->dp && ctx->dp->world >
 
 zn_status zn_dp_allreduce(zn_ctx *ctx, float *buf, size_t count, cudaStream_t stream) {
     if (!zn_dp_active(ctx)) return ZN_OK;
+    // diagnostic: time a step without its exchange (the ranks then diverge; never for results)
+    static const bool skip = getenv("ZN_DP_SKIP_ALLREDUCE") != nullptr;
+    if (skip) return ZN_OK;
     ncclResult_t r = api().AllReduce(buf, buf, count, ncclFloat32, ncclSum, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllReduce: %s", api().GetErrorString(r));
     return ZN_OK;
+}
+
+// A gradient block allocated by NCCL and registered with the communicator.  On NVSwitch machines NCCL can
+// then reduce it in place through the switch (NVLS) instead of staging it through its own buffers, which takes
+// fewer SMs and less HBM traffic away from the GEMMs the exchange runs under.  Returns ZN_ERR_NOT_AVAILABLE
+// (nothing allocated, nothing reported) when this NCCL has no such interface or registration is switched
+// off with ZN_DP_NO_REGISTER; the caller then keeps its ordinary allocation.
+zn_status zn_dp_alloc_registered(zn_ctx *ctx, size_t bytes, void **ptr_out, void **handle_out) {
+    *ptr_out = nullptr;
+    *handle_out = nullptr;
+    static const bool off = getenv("ZN_DP_NO_REGISTER") != nullptr;
+    if (off || !zn_dp_active(ctx) || !api().MemAlloc || !api().MemFree || !api().CommRegister || !api().CommDeregister)
+        return ZN_ERR_NOT_AVAILABLE;
+    void *p = nullptr, *h = nullptr;
+    if (api().MemAlloc(&p, bytes) != ncclSuccess || !p) { cudaGetLastError(); return ZN_ERR_NOT_AVAILABLE; }
+    if (api().CommRegister(ctx->dp->comm, p, bytes, &h) != ncclSuccess) {
+        api().MemFree(p);
+        cudaGetLastError();
+        return ZN_ERR_NOT_AVAILABLE;
+    }
+    *ptr_out = p;
+    *handle_out = h;
+    return ZN_OK;
+}
+
+void zn_dp_free_registered(zn_ctx *ctx, void *ptr, void *handle) {
+    if (!ptr) return;
+    // after zn_dp_destroy the communicator, and with it the registration, is gone already
+    if (handle && ctx && ctx->dp && ctx->dp->comm && api().CommDeregister) api().CommDeregister(ctx->dp->comm, handle);
+    if (api().MemFree) api().MemFree(ptr);
 }
 
 static_assert(sizeof(ncclUniqueId) == 128, "the C ABI carries the NCCL id as 128 bytes");

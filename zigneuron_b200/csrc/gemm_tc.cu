@@ -595,12 +595,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // the leader's barrier); `empty` and `tmem_full` are signalled in both CTAs by one multicast
 // tcgen05.commit; the epilogue warps of both CTAs arrive on the leader's `tmem_empty`.
 
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 6;                        // default ring depth; 4 and 5 are built as well (see zn_gemm_tc)
 constexpr int HALF = 128;                         // rows of A, and columns of B, staged per CTA
 constexpr int A2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int B2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int STAGE2_BYTES = A2_STAGE + B2_STAGE;
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256 + BIAS_SMEM;
+constexpr int smem2_bytes(int stages) { return stages * STAGE2_BYTES + 1024 + 256 + BIAS_SMEM; }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -650,7 +650,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
     }
 }
 
-template <typename ET>
+template <typename ET, int NST>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
     constexpr bool TF32 = sizeof(ET) == 4;
@@ -664,17 +664,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
-    const uint32_t bars = base + STAGES2 * STAGE2_BYTES;
+    const uint32_t bars = base + NST * STAGE2_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
-    auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + b); };
-    auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + 2 + b); };
-    auto sfull_bar = [&](int q) { return bars + 8u * (2 * STAGES2 + 4 + q); };
-    auto sempty_bar = [&](int q) { return bars + 8u * (2 * STAGES2 + 4 + TQ + q); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + STAGES2 * STAGE2_BYTES + 8 * (2 * STAGES2 + 4 + 2 * TQ));
+    auto empty_bar = [&](int s) { return bars + 8u * (NST + s); };
+    auto tfull_bar = [&](int b) { return bars + 8u * (2 * NST + b); };
+    auto tempty_bar = [&](int b) { return bars + 8u * (2 * NST + 2 + b); };
+    auto sfull_bar = [&](int q) { return bars + 8u * (2 * NST + 4 + q); };
+    auto sempty_bar = [&](int q) { return bars + 8u * (2 * NST + 4 + TQ + q); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + NST * STAGE2_BYTES + 8 * (2 * NST + 4 + 2 * TQ));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *tile_ring = reinterpret_cast<volatile int *>(tmem_slot + 2);
-    float *bias_smem = reinterpret_cast<float *>(gen + STAGES2 * STAGE2_BYTES + 256);
+    float *bias_smem = reinterpret_cast<float *>(gen + NST * STAGE2_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
@@ -682,7 +682,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
-        for (int s = 0; s < STAGES2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps x 2 CTAs
         // tile-index ring: the leader's producer publishes into both CTAs; its `empty` side counts every reader
         // of the pair: leader MMA thread + 4 leader epilogue warps + peer producer + 4 peer epilogue warps
@@ -761,7 +761,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         for (int c = 0; c < HALF / CH; ++c)
                             tma_load_2d_pair(sb + c * (BK * ROW_BYTES), &tmB, n0 + c * CH, k0, lead_full);
                     }
-                    if (++s == STAGES2) { s = 0; phase ^= 1u; }
+                    if (++s == NST) { s = 0; phase ^= 1u; }
                 }
             }
         }
@@ -800,7 +800,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         tc_mma_pair<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
                     }
                     tc_commit_pair(empty_bar(s));         // frees the stage in both CTAs
-                    if (++s == STAGES2) { s = 0; phase ^= 1u; }
+                    if (++s == NST) { s = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit_pair(tfull_bar(buf));   // accumulator complete, in both CTAs
             }
@@ -982,21 +982,30 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, HALF, false));
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | ((uint32_t)((2 * HALF) >> 4) << 24);   // M = 256 across the pair
         const long long pair_tiles = (long long)((m + 2 * HALF - 1) / (2 * HALF)) * p.num_n_tiles;
-        const int max_clusters = ctx->sm_count / 2;
+        int max_clusters = ctx->sm_count / 2 - (e.reserve_sms + 1) / 2;
+        if (max_clusters < 1) max_clusters = 1;
         const int clusters = (int)(pair_tiles < max_clusters ? pair_tiles : max_clusters);
+        // ZN_TC_PAIR_STAGES = 4 or 5 (diagnostic): a shallower operand ring leaves 62 / 94 KB of the SM's shared
+        // memory to kernels that share the SM with this one, instead of 30 KB
+        static const int nst = [] { const char *e = getenv("ZN_TC_PAIR_STAGES"); const int v = e ? atoi(e) : STAGES2; return (v == 4 || v == 5) ? v : STAGES2; }();
+        using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const TcParams);
+        PairFn fn;
+        if (elem_type == 0) fn = nst == 4 ? gemm_tc_pair_kernel<__nv_bfloat16, 4> : nst == 5 ? gemm_tc_pair_kernel<__nv_bfloat16, 5> : gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>;
+        else fn = nst == 4 ? gemm_tc_pair_kernel<float, 4> : nst == 5 ? gemm_tc_pair_kernel<float, 5> : gemm_tc_pair_kernel<float, STAGES2>;
         static uint64_t pair_attr_mask = 0;
         if (!(pair_attr_mask & dev_bit)) {
-            ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_pair_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES));
-            ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES));
-            cudaFuncSetAttribute(gemm_tc_pair_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-            cudaFuncSetAttribute(gemm_tc_pair_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            for (PairFn f : {(PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 5>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>,
+                             (PairFn)gemm_tc_pair_kernel<float, 4>, (PairFn)gemm_tc_pair_kernel<float, 5>, (PairFn)gemm_tc_pair_kernel<float, STAGES2>}) {
+                ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2)));
+                cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            }
             cudaGetLastError();
             pair_attr_mask |= dev_bit;
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(2 * clusters));
         cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = SMEM2_BYTES;
+        cfg.dynamicSmemBytes = smem2_bytes(nst);
         cfg.stream = ctx->stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1005,12 +1014,12 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (elem_type == 0) ZN_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<__nv_bfloat16>, tmA, tmB, p));
-        else ZN_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<float>, tmA, tmB, p));
+        ZN_CUDA(ctx, cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p));
         return ZN_OK;
     }
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
-    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    const int sms = ctx->sm_count - e.reserve_sms > 0 ? ctx->sm_count - e.reserve_sms : 1;
+    const int grid = (int)(tiles < sms ? tiles : sms);
     if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
     else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
     ZN_CUDA(ctx, cudaGetLastError());

@@ -22,6 +22,9 @@
 
 zn_status zn_dp_allreduce(zn_ctx *ctx, float *buf, size_t count, cudaStream_t stream);   // dp.cu
 bool zn_dp_active(const zn_ctx *ctx);
+// Gradient memory NCCL can reduce in place (dp.cu); ZN_ERR_NOT_AVAILABLE = keep the ordinary allocation.
+zn_status zn_dp_alloc_registered(zn_ctx *ctx, size_t bytes, void **ptr_out, void **handle_out);
+void zn_dp_free_registered(zn_ctx *ctx, void *ptr, void *handle);
 
 namespace {
 
@@ -34,6 +37,8 @@ struct Layer {
     int act = ZN_ACT_LINEAR;
     size_t b_off = 0, len = 0, blk = 0;   // bias offset, used length, allocated length (multiple of 4) before the tail
     float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
+    void *grads_reg = nullptr;            // registration handle of grads when it comes from NCCL
+    bool grads_nccl = false;              // grads was allocated by NCCL and is registered with the communicator
     void *w_op = nullptr;                 // operand copy of W (tensor-core modes), null when W itself is usable
     int64_t ld_w = 0;
     int opt = OPT_SGD;                    // OPT_* below
@@ -253,7 +258,9 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         ZN_CUDA(ctx, cudaEventRecord(l.grads_ready, s_main));
         ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.grads_ready, 0));
         ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.bias_done, 0));
-        if (dp) ZN_TRY(zn_dp_allreduce(ctx, l.grads, l.blk + (idx + 1 == L ? 1 : 0), s_comm));
+        // the last layer's block carries the loss sum in its tail; the other three tail floats stay zero and
+        // ride along so that every exchanged count is a multiple of four floats
+        if (dp) ZN_TRY(zn_dp_allreduce(ctx, l.grads, l.blk + (idx + 1 == L ? 4 : 0), s_comm));
         if (!exact) {
             zn_lane_guard lane(ctx, ZN_LANE_COMM);
             const zn_seg segs[2] = {{l.grads, l.in * l.out}, {l.grads + l.b_off, l.out}};
@@ -269,6 +276,10 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
             if (prev_act == ZN_ACT_RELU) { ep.mask = n->acts[idx]; ep.ld_mask = n->lds[idx]; }
             if (n->tc) { ep.out_t = n->gwork[cur ^ 1]; ep.ld_out_t = n->lds[idx]; }
             else { ep.out_f32 = (float *)n->gwork[cur ^ 1]; ep.ld_out_f32 = n->lds[idx]; }
+            // The exchange of layer 0's gradients is the one nothing else hides: its kernel must start the moment
+            // gW is done, not after this last GEMM has taken every SM.  Leave it room (ZN_DP_RESERVE_SMS, diagnostic).
+            static const int reserve = getenv("ZN_DP_RESERVE_SMS") ? atoi(getenv("ZN_DP_RESERVE_SMS")) : 0;
+            if (dp && idx == 0) ep.reserve_sms = reserve;
             const void *w = l.w_op ? l.w_op : (const void *)l.params;
             const int64_t ldw = l.w_op ? l.ld_w : (int64_t)l.out;
             ZN_TRY(net_gemm(n, 2, g, ld_g, w, ldw, (int64_t)rows, (int64_t)l.in, (int64_t)l.out, ep));
@@ -430,7 +441,9 @@ extern "C" void zn_net_destroy(zn_net *n) {
     }
     free_acts(n);
     for (Layer &l : n->layers) {
-        cudaFree(l.params); cudaFree(l.grads); cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
+        if (l.grads_nccl) zn_dp_free_registered(n->ctx, l.grads, l.grads_reg);
+        else cudaFree(l.grads);
+        cudaFree(l.params); cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
         for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated})
             if (ev) cudaEventDestroy(ev);
     }
@@ -941,5 +954,22 @@ extern "C" zn_status zn_net_set_data_parallel(zn_net *n, size_t global_rows) {
     if (global_rows > 0 && !zn_dp_active(n->ctx))
         return zn_fail(n->ctx, ZN_ERR_NOT_AVAILABLE, "call zn_dp_init on the context first");
     n->global_rows = global_rows;
+    if (global_rows > 0) {
+        // Move the gradient blocks into memory NCCL allocates and registers, so that the per-layer all-reduce
+        // works on them in place.  Every rank does this in the same order; without the interface the blocks stay.
+        zn_ctx *ctx = n->ctx;
+        for (Layer &l : n->layers) {
+            if (l.grads_nccl) continue;
+            const size_t bytes = (l.blk + 4) * sizeof(float);
+            void *p = nullptr, *h = nullptr;
+            if (zn_dp_alloc_registered(ctx, bytes, &p, &h) != ZN_OK) break;
+            ZN_CUDA(ctx, cudaMemsetAsync(p, 0, bytes, ctx->stream));
+            ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(l.grads);
+            l.grads = (float *)p;
+            l.grads_reg = h;
+            l.grads_nccl = true;
+        }
+    }
     return ZN_OK;
 }

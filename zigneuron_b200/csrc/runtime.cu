@@ -71,9 +71,15 @@ extern "C" zn_status zn_ctx_create(int32_t device, zn_ctx **out) {
     cudaError_t e = cudaSetDevice(device);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->opt_stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking);
+    // The side lanes carry short kernels on the step's critical chain (exchange of the last gradients, their
+    // norm, the update the next forward waits for).  At the highest priority their blocks are placed before
+    // those of the next persistent GEMM whenever SMs fall free.  ZN_FLAT_PRIORITIES: all lanes equal (diagnostic).
+    int prio_least = 0, prio_greatest = 0;
+    if (e == cudaSuccess) e = cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest);
+    const int side = getenv("ZN_FLAT_PRIORITIES") ? prio_least : prio_greatest;
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, side);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&ctx->opt_stream, cudaStreamNonBlocking, side);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&ctx->aux_stream, cudaStreamNonBlocking, side);
     for (int i = 0; i < 4 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&ctx->lane_join[i], cudaEventDisableTiming);
     ctx->lanes[ZN_LANE_MAIN].stream = ctx->stream;
     ctx->lanes[ZN_LANE_COMM].stream = ctx->comm_stream;

@@ -121,6 +121,7 @@ struct zn_epilogue {
     void *out_t = nullptr;             // only the tensor-core path: output in the operand type
     int64_t ld_out_t = 0;
     int accumulate = 0;                // += into out_f32
+    int reserve_sms = 0;               // tensor-core path: leave this many SMs to kernels on other streams
 };
 
 // fp32 CUDA-core GEMM.  A(i,p) = a[i*a_rs + p*a_cs], B(p,j) = b[p*b_rs + j*b_cs].
