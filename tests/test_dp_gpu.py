@@ -42,6 +42,9 @@ def _build(zn, be, prec, Ws, bs, adam):
 
 def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    # the last GEMM of a data-parallel step runs its first rows on fewer SMs: 64 of each rank's 100 rows here,
+    # so that both of its launches are exercised
+    os.environ.setdefault("ZN_DP_RESERVE_ROWS", "64")
     import zigneuron_b200 as zn
     prec = zn.Precision(prec_value)
     loss = zn.Loss.mse if loss_name == "mse" else zn.Loss.cross_entropy_logits
@@ -64,7 +67,7 @@ def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value):
     net.setDataParallel(B)
     lo, hi = zn.Backend.distributeWorkload(B, world, rank)
     losses = [net.trainStep(x[lo:hi], t[lo:hi], LR, loss) for _ in range(STEPS)]
-    out = {"losses": np.array(losses, np.float32)}
+    out = {"losses": np.array(losses, np.float32), "gx": net.getInputGrad(hi - lo)}
     for i in range(len(DIMS)):
         W, b = net.getWeights(i)
         out[f"W{i}"], out[f"b{i}"] = W, b
@@ -96,6 +99,10 @@ def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name,
     net = _build(zn, be, prec, Ws, bs, adam)
     one = [net.trainStep(x, t, LR, loss) for _ in range(STEPS)]
     assert np.allclose(r0["losses"], one, rtol=max(tol, 1e-5), atol=1e-6)
+    # the input gradient of the last step: each rank holds the rows of its shard (CE gradients carry no 1/B and
+    # MSE uses the global divisor, so the shards are the rows of the one-GPU result)
+    gx = net.getInputGrad(B)
+    assert rel_l2(np.concatenate([r0["gx"], r1["gx"]]), gx) <= max(tol, 1e-5)
     for i in range(len(DIMS)):
         assert rel_l2(r0[f"W{i}"], net.getWeights(i)[0]) <= tol
     net.deinit()
