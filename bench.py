@@ -385,7 +385,13 @@ def run_gemm_sweep(args):
 
 def run_other_config(args):
     """BASELINE configs[1] (784-512-256-10, batch 1024, Adam, CE with logits, seed 1) and configs[2] (the wide MLP at
-    batch 8192 with SGD, seed 2), inputs resident on the device.  Extra lines for the results table."""
+    batch 8192 with SGD, seed 2), inputs resident on the device.  Extra lines for the results table.
+    wide_mlp_adam_shard is the same wide MLP with Adam at batch 8192: what ONE rank of the 8-GPU data-parallel
+    step computes, without the exchange; with --trace it gives the lane timeline of that step."""
+    if args.trace:
+        os.environ["ZN_TRACE_FILE"] = os.path.abspath(args.trace)
+        if os.path.exists(args.trace):
+            os.remove(args.trace)
     import zigneuron_b200 as zn
     if args.workload == "mlp784":
         dims, acts, B, seed, loss, lr = [(784, 512), (512, 256), (256, 10)], ["relu", "relu", "linear"], 1024, 1, zn.Loss.cross_entropy_logits, 1e-3
@@ -393,6 +399,8 @@ def run_other_config(args):
     else:
         dims, acts, B, seed, loss, lr = DIMS, ACTS, 8192, 2, zn.Loss.mse, 1e-3
         precisions = [("bf16", zn.Precision.BF16_TC), ("tf32", zn.Precision.TF32_TC)]
+        if args.workload == "wide_mlp_adam_shard":
+            precisions = precisions[:1]
     rng = np.random.default_rng(seed)
     if args.workload == "mlp784":
         x = rng.random((B, 784), dtype=np.float32)
@@ -409,7 +417,7 @@ def run_other_config(args):
             net.addDense(a, b, act)
             scale = np.sqrt((2.0 if act == "relu" else 1.0) / a) if args.workload != "mlp784" else np.sqrt(2.0 / (a + b))
             net.setWeights(i, ((wr.random((a, b), dtype=np.float32) * 2 - 1) * np.float32(scale)).astype(np.float32), np.zeros(b, np.float32))
-        if args.workload == "mlp784":
+        if args.workload in ("mlp784", "wide_mlp_adam_shard"):
             net.setOptimizer(zn.Adam())
         dx, dt = be.tensor(x), be.tensor(t)
         losses = [net.trainStep(dx, dt, lr, loss, rows=B) for _ in range(args.warmup)]
@@ -421,6 +429,11 @@ def run_other_config(args):
         print(json.dumps({"workload": args.workload, "precision": pname, "batch": B, "ms_per_step": ms,
                           "samples_per_s": B / (ms / 1e3), "tflops": flop / (ms / 1e3) / 1e12,
                           "loss_first": losses[0], "loss_last": losses[-1]}), flush=True)
+        if args.trace:
+            be.profile(True)
+            for _ in range(3):
+                net.trainStep(dx, dt, lr, loss, rows=B)
+            be.profile(False)
         net.deinit()
         dx.free()
         dt.free()
@@ -429,7 +442,9 @@ def run_other_config(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="wide_mlp_dp", choices=["wide_mlp_dp", "gemm_sweep", "mlp784", "wide_mlp_sgd"])
+    ap.add_argument("--workload", default="wide_mlp_dp", choices=["wide_mlp_dp", "gemm_sweep", "mlp784", "wide_mlp_sgd", "wide_mlp_adam_shard"])
+    ap.add_argument("--trace", default=None, help="after timing, run 3 more steps with every launch written to this file "
+                    "as 'family lane start_ms end_ms' (lanes: 0 main, 1 comm, 2 opt, 3 aux)")
     ap.add_argument("--sizes", default="1024x1024x1024,4096x4096x4096,8192x8192x8192,65536x512x512")
     ap.add_argument("--precisions", default="bf16,tf32,fp32")
     ap.add_argument("--gpus", type=int, default=1)
@@ -442,7 +457,7 @@ def main():
         args.warmup = 3
     if args.workload == "gemm_sweep":
         run_gemm_sweep(args)
-    elif args.workload in ("mlp784", "wide_mlp_sgd"):
+    elif args.workload in ("mlp784", "wide_mlp_sgd", "wide_mlp_adam_shard"):
         run_other_config(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -126,6 +126,7 @@ extern "C" void zn_ctx_destroy(zn_ctx *ctx) {
     for (auto &slot : ctx->prof)
         for (auto &p : slot.pending) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
     for (auto ev : ctx->event_pool) cudaEventDestroy(ev);
+    if (ctx->trace_origin) cudaEventDestroy(ctx->trace_origin);
     if (ctx->timer0) cudaEventDestroy(ctx->timer0);
     if (ctx->timer1) cudaEventDestroy(ctx->timer1);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -313,10 +314,23 @@ zn_launch_scope::~zn_launch_scope() {
     if (!e0) return;
     cudaEventRecord(e1, ctx->stream);
     ctx->prof[family].pending.emplace_back(e0, e1);
+    if (ctx->trace_origin) ctx->trace.push_back({family, ctx->lane, e0, e1});
 }
 
 static void drain_profile(zn_ctx *ctx) {
     zn_sync_all_lanes(ctx);
+    if (ctx->trace_origin && !ctx->trace.empty()) {
+        if (FILE *f = fopen(ctx->trace_path, "a")) {
+            for (const zn_trace_rec &r : ctx->trace) {
+                float t0 = 0, t1 = 0;
+                if (cudaEventElapsedTime(&t0, ctx->trace_origin, r.e0) == cudaSuccess &&
+                    cudaEventElapsedTime(&t1, ctx->trace_origin, r.e1) == cudaSuccess)
+                    fprintf(f, "%d %d %.4f %.4f\n", r.family, r.lane, t0, t1);
+            }
+            fclose(f);
+        }
+        ctx->trace.clear();
+    }
     for (auto &slot : ctx->prof) {
         for (auto &p : slot.pending) {
             float ms = 0;
@@ -332,6 +346,10 @@ extern "C" zn_status zn_profile_enable(zn_ctx *ctx, int32_t on) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
     if (!on && ctx->profiling) drain_profile(ctx);
     ctx->profiling = on != 0;
+    if (on && !ctx->trace_origin && (ctx->trace_path = getenv("ZN_TRACE_FILE")) != nullptr) {
+        ZN_CUDA(ctx, cudaEventCreate(&ctx->trace_origin));
+        ZN_CUDA(ctx, cudaEventRecord(ctx->trace_origin, ctx->stream));
+    }
     return ZN_OK;
 }
 

@@ -20,6 +20,8 @@ struct zn_prof_slot {
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;   // recorded, not yet read back
 };
 
+struct zn_trace_rec { int family, lane; cudaEvent_t e0, e1; };   // one launch of a traced run
+
 struct zn_dp_state;   // dp.cu
 
 struct zn_ctx {
@@ -60,6 +62,11 @@ struct zn_ctx {
     bool profiling = false;
     zn_prof_slot prof[ZN_PROF_FAMILY_COUNT];
     std::vector<cudaEvent_t> event_pool;
+    // ZN_TRACE_FILE=<path> (diagnostic): while profiling is on, every launch is also written as a line
+    // "family lane start_ms end_ms" (times from the moment profiling was switched on) when the profile is read
+    const char *trace_path = nullptr;
+    cudaEvent_t trace_origin = nullptr;
+    std::vector<zn_trace_rec> trace;
     cudaEvent_t timer0 = nullptr, timer1 = nullptr;
     // Two work counters for the persistent GEMM's dynamic tile scheduler, used in turn by successive launches
     // on the main stream (each launch clears the one the next launch will use).
