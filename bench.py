@@ -30,6 +30,7 @@ sys.path.insert(0, ROOT)
 DIMS = [(4096, 8192), (8192, 8192), (8192, 8192), (8192, 4096)]
 ACTS = ["relu", "relu", "relu", "linear"]
 GLOBAL_BATCH = 65536
+SHARD_UPDATE_DEFAULT = False
 SEED = 3
 LR = 1e-3
 BLOCK_ROWS = 1024                     # data is generated in blocks of rows keyed by (seed, stream, block)
@@ -241,6 +242,9 @@ def run_ours(args):
     net.setOptimizer(zn.Adam(beta1=0.9, beta2=0.999, eps=1e-8))
     if world > 1:
         net.setDataParallel(GLOBAL_BATCH)
+        shard_update = SHARD_UPDATE_DEFAULT if args.shard_update is None else bool(args.shard_update)
+        if shard_update:
+            net.setUpdateSharding(True)
 
     lo, hi = zn.Backend.distributeWorkload(GLOBAL_BATCH, world, rank)
     rows = hi - lo
@@ -452,6 +456,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--shard-update", type=int, default=None, choices=[0, 1],
+                    help="N > 1: split the parameter update over the ranks (reduce-scatter / update / all-gather)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

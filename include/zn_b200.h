@@ -275,6 +275,13 @@ ZN_API zn_status zn_dp_unique_id(uint8_t id_out[128]);
 ZN_API zn_status zn_dp_init(zn_ctx *ctx, int32_t rank, int32_t world, const uint8_t id[128]);
 ZN_API zn_status zn_dp_destroy(zn_ctx *ctx);
 ZN_API zn_status zn_net_set_data_parallel(zn_net *net, size_t global_rows);
+/* Optional, after zn_net_set_data_parallel: split the parameter update over the ranks.  Per layer a
+ * reduce-scatter of the gradients, each rank clips and updates its own 1/world piece, then an all-gather of
+ * the updated weights; results as before up to the order NCCL adds in.  While it is on, zn_net_get_grads and
+ * zn_net_save_optimizer fail with ZN_ERR_NOT_AVAILABLE (a rank holds its own piece only) and FP32_EXACT is
+ * refused.  No counterpart in the reference, whose multi-GPU layer has no collective at all
+ * (src/cuda_multi_gpu.zig). */
+ZN_API zn_status zn_net_set_update_sharding(zn_net *net, int32_t on);
 
 /* ---- measurement ------------------------------------------------------------------ */
 /* Per-kernel-family CUDA-event timing on the compute stream. */

@@ -40,7 +40,7 @@ def _build(zn, be, prec, Ws, bs, adam):
     return net
 
 
-def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value):
+def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value, shard=False):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     # the last GEMM of a data-parallel step runs its first rows on fewer SMs: 64 of each rank's 100 rows here,
     # so that both of its launches are exercised
@@ -65,6 +65,8 @@ def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value):
     be.dp_init(rank, world, uid)
     net = _build(zn, be, prec, Ws, bs, adam)
     net.setDataParallel(B)
+    if shard:
+        net.setUpdateSharding(True)
     lo, hi = zn.Backend.distributeWorkload(B, world, rank)
     losses = [net.trainStep(x[lo:hi], t[lo:hi], LR, loss) for _ in range(STEPS)]
     out = {"losses": np.array(losses, np.float32), "gx": net.getInputGrad(hi - lo)}
@@ -76,9 +78,10 @@ def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value):
     be.deinit()
 
 
+@pytest.mark.parametrize("shard", [False, True], ids=["replicated", "sharded"])
 @pytest.mark.parametrize("loss_name,adam,prec_name,tol", [("mse", False, "FP32_SIMT", 1e-5), ("ce", True, "FP32_SIMT", 2e-3),
-                                                           ("mse", False, "BF16_TC", 2e-2)])
-def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name, tol):
+                                                           ("mse", False, "BF16_TC", 2e-2), ("mse", True, "BF16_TC", 2e-2)])
+def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name, tol, shard):
     import zigneuron_b200 as zn
     if zn.Backend.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -86,7 +89,7 @@ def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name,
     from oracle import zn_oracle as zo
     from util import rel_l2
     prec = zn.Precision[prec_name]
-    mp.spawn(_rank, args=(2, str(tmp_path / "uid"), str(tmp_path), loss_name, adam, int(prec)), nprocs=2, join=True)
+    mp.spawn(_rank, args=(2, str(tmp_path / "uid"), str(tmp_path), loss_name, adam, int(prec), shard), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "r0.npz"), np.load(tmp_path / "r1.npz")
     # both ranks end with identical parameters and report the same (global) loss
     assert np.array_equal(r0["losses"], r1["losses"])
@@ -117,4 +120,9 @@ def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name,
     want = [onet.train_step(x, t, B, LR, zo.MSE if loss_name == "mse" else zo.CE_LOGITS) for _ in range(STEPS)]
     assert np.allclose(r0["losses"], want, rtol=max(tol, 2e-5), atol=1e-6)
     for i in range(len(DIMS)):
-        assert rel_l2(r0[f"W{i}"], onet.get_params(i)[0]) <= tol
+        if adam and prec_name == "BF16_TC":
+            # Adam turns bf16-sized gradient differences into steps of about lr; at lr 0.05 only the bound that
+            # Adam itself implies is meaningful against the fp32 oracle (the one-GPU bf16 run above is matched)
+            assert np.abs(r0[f"W{i}"] - onet.get_params(i)[0]).max() <= 2.2 * STEPS * LR
+        else:
+            assert rel_l2(r0[f"W{i}"], onet.get_params(i)[0]) <= tol

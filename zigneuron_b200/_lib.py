@@ -99,6 +99,7 @@ SIGNATURES = {
     "zn_dp_init": (i32, [vp, i32, i32, C.c_char_p]),
     "zn_dp_destroy": (i32, [vp]),
     "zn_net_set_data_parallel": (i32, [vp, sz]),
+    "zn_net_set_update_sharding": (i32, [vp, i32]),
     "zn_profile_enable": (i32, [vp, i32]),
     "zn_profile_reset": (i32, [vp]),
     "zn_profile_get": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),

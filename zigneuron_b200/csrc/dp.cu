@@ -25,6 +25,8 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     // optional (NCCL >= 2.19): memory the collectives can work on in place
@@ -52,6 +54,8 @@ NcclApi &api() {
     ZN_SYM(CommDestroy, "ncclCommDestroy");
     ZN_SYM(CommAbort, "ncclCommAbort");
     ZN_SYM(AllReduce, "ncclAllReduce");
+    ZN_SYM(ReduceScatter, "ncclReduceScatter");
+    ZN_SYM(AllGather, "ncclAllGather");
     ZN_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     ZN_SYM(GetErrorString, "ncclGetErrorString");
     ZN_SYM(MemAlloc, "ncclMemAlloc");
@@ -79,6 +83,34 @@ zn_status zn_dp_allreduce(zn_ctx *ctx, float *buf, size_t count, cudaStream_t st
     if (skip) return ZN_OK;
     ncclResult_t r = api().AllReduce(buf, buf, count, ncclFloat32, ncclSum, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllReduce: %s", api().GetErrorString(r));
+    return ZN_OK;
+}
+
+int zn_dp_rank(const zn_ctx *ctx) { return zn_dp_active(ctx) ? ctx->dp->rank : 0; }
+int zn_dp_world(const zn_ctx *ctx) { return zn_dp_active(ctx) ? ctx->dp->world : 1; }
+bool zn_dp_can_shard(const zn_ctx *ctx) { return zn_dp_active(ctx) && api().ReduceScatter && api().AllGather; }
+
+zn_status zn_dp_allreduce_f64(zn_ctx *ctx, double *buf, size_t count, cudaStream_t stream) {
+    if (!zn_dp_active(ctx)) return ZN_OK;
+    ncclResult_t r = api().AllReduce(buf, buf, count, ncclFloat64, ncclSum, ctx->dp->comm, stream);
+    if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllReduce(f64): %s", api().GetErrorString(r));
+    return ZN_OK;
+}
+
+// In place on a block of world * shard floats: afterwards rank r holds the sum over ranks of its own piece
+// [r * shard, (r + 1) * shard); the other pieces keep this rank's partial values.
+zn_status zn_dp_reduce_scatter(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream) {
+    if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "reduce-scatter needs an initialised communicator");
+    ncclResult_t r = api().ReduceScatter(buf, buf + (size_t)ctx->dp->rank * shard, shard, ncclFloat32, ncclSum, ctx->dp->comm, stream);
+    if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclReduceScatter: %s", api().GetErrorString(r));
+    return ZN_OK;
+}
+
+// In place: every rank contributes its own piece [r * shard, (r + 1) * shard) and ends with all of them.
+zn_status zn_dp_all_gather(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream) {
+    if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "all-gather needs an initialised communicator");
+    ncclResult_t r = api().AllGather(buf + (size_t)ctx->dp->rank * shard, buf, shard, ncclFloat32, ctx->dp->comm, stream);
+    if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllGather: %s", api().GetErrorString(r));
     return ZN_OK;
 }
 

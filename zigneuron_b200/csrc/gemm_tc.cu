@@ -25,6 +25,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <atomic>
+
 #include "zn_internal.h"
 #include "zn_act.cuh"
 
@@ -921,9 +923,9 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const int es = elem_type == 0 ? 2 : 4;
     const int bk = ROW_BYTES / es, ch = ROW_BYTES / es;
 
-    static uint64_t attr_set_mask = 0;   // cudaFuncSetAttribute is per device
+    static std::atomic<uint64_t> attr_set_mask{0};   // cudaFuncSetAttribute is per device
     const uint64_t dev_bit = 1ull << (ctx->device & 63);
-    if (!(attr_set_mask & dev_bit)) {
+    if (!(attr_set_mask.load() & dev_bit)) {
         ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           SMEM_BYTES));
         ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -934,7 +936,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
         cudaGetLastError();
-        attr_set_mask |= dev_bit;
+        attr_set_mask.fetch_or(dev_bit);
     }
 
     CUtensorMap tmA, tmB;
@@ -992,15 +994,15 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         PairFn fn;
         if (elem_type == 0) fn = nst == 4 ? gemm_tc_pair_kernel<__nv_bfloat16, 4> : nst == 5 ? gemm_tc_pair_kernel<__nv_bfloat16, 5> : gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>;
         else fn = nst == 4 ? gemm_tc_pair_kernel<float, 4> : nst == 5 ? gemm_tc_pair_kernel<float, 5> : gemm_tc_pair_kernel<float, STAGES2>;
-        static uint64_t pair_attr_mask = 0;
-        if (!(pair_attr_mask & dev_bit)) {
+        static std::atomic<uint64_t> pair_attr_mask{0};
+        if (!(pair_attr_mask.load() & dev_bit)) {
             for (PairFn f : {(PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 5>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>,
                              (PairFn)gemm_tc_pair_kernel<float, 4>, (PairFn)gemm_tc_pair_kernel<float, 5>, (PairFn)gemm_tc_pair_kernel<float, STAGES2>}) {
                 ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2)));
                 cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             }
             cudaGetLastError();
-            pair_attr_mask |= dev_bit;
+            pair_attr_mask.fetch_or(dev_bit);
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(2 * clusters));

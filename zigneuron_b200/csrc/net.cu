@@ -25,6 +25,12 @@ bool zn_dp_active(const zn_ctx *ctx);
 // Gradient memory NCCL can reduce in place (dp.cu); ZN_ERR_NOT_AVAILABLE = keep the ordinary allocation.
 zn_status zn_dp_alloc_registered(zn_ctx *ctx, size_t bytes, void **ptr_out, void **handle_out);
 void zn_dp_free_registered(zn_ctx *ctx, void *ptr, void *handle);
+int zn_dp_rank(const zn_ctx *ctx);
+int zn_dp_world(const zn_ctx *ctx);
+bool zn_dp_can_shard(const zn_ctx *ctx);
+zn_status zn_dp_allreduce_f64(zn_ctx *ctx, double *buf, size_t count, cudaStream_t stream);
+zn_status zn_dp_reduce_scatter(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream);
+zn_status zn_dp_all_gather(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream);
 
 namespace {
 
@@ -35,10 +41,12 @@ enum { OPT_SGD = 0, OPT_ADAM = 1, OPT_MOMENTUM = 2, OPT_ADAMW = 3, OPT_RMSPROP =
 struct Layer {
     size_t in = 0, out = 0;
     int act = ZN_ACT_LINEAR;
-    size_t b_off = 0, len = 0, blk = 0;   // bias offset, used length, allocated length (multiple of 4) before the tail
+    size_t b_off = 0, len = 0, blk = 0;   // bias offset, used length, used length rounded up to a multiple of 4
+    size_t cap = 0;                       // floats allocated per block: >= blk + 4; the last four are the tail
+    size_t shard = 0;                     // sharded update: floats per rank, world * shard >= blk
     float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
-    void *grads_reg = nullptr;            // registration handle of grads when it comes from NCCL
-    bool grads_nccl = false;              // grads was allocated by NCCL and is registered with the communicator
+    void *grads_reg = nullptr, *params_reg = nullptr;   // registration handles of blocks that come from NCCL
+    bool grads_nccl = false, params_nccl = false;       // the block was allocated by NCCL and is registered
     void *w_op = nullptr;                 // operand copy of W (tensor-core modes), null when W itself is usable
     int64_t ld_w = 0;
     int opt = OPT_SGD;                    // OPT_* below
@@ -47,6 +55,7 @@ struct Layer {
     size_t t = 0;
     // ordering between the lanes of a step (see step_dev)
     cudaEvent_t g_ready = nullptr, bias_done = nullptr, grads_ready = nullptr, reduced = nullptr, updated = nullptr;
+    cudaEvent_t stepped = nullptr;        // sharded update: this rank's piece of the layer has been updated
     bool update_pending = false;          // `updated` has been recorded and not yet waited for by the host
 };
 
@@ -78,6 +87,8 @@ struct zn_net {
     Slot slots[2];
     int head = 0, inflight = 0;
     size_t global_rows = 0;               // > 0: data parallel
+    bool shard_update = false;            // data parallel with the update split over the ranks (see step_dev)
+    cudaEvent_t norm_ready = nullptr;     // sharded update: the global sums of squares and the loss sum are in
     float last_norm = 0.f, last_factor = 1.f;
     const void *last_input_grad = nullptr;
     size_t last_rows = 0;
@@ -218,6 +229,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     const size_t L = n->layers.size();
     const bool exact = n->prec == ZN_FP32_EXACT;
     const bool dp = n->global_rows > 0 && zn_dp_active(ctx);
+    const bool shard = dp && n->shard_update && !exact;
     cudaStream_t s_main = ctx->lanes[ZN_LANE_MAIN].stream, s_comm = ctx->lanes[ZN_LANE_COMM].stream;
     cudaStream_t s_opt = ctx->lanes[ZN_LANE_OPT].stream, s_aux = ctx->lanes[ZN_LANE_AUX].stream;
     s_main = ctx->stream;   // lane 0 is active here; its slot in lanes[] is only refreshed on a switch
@@ -226,7 +238,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     Layer &last = n->layers[L - 1];
     const size_t out_cols = last.out;
     const size_t total_rows = dp ? n->global_rows : rows;
-    float *loss_slot = last.grads + last.blk;
+    float *loss_slot = last.grads + (last.cap - 4);   // first float of the tail
     int cur = 0;
     ZN_TRY(zn_k_loss(ctx, loss, final_output(n), (int64_t)out_cols, t_dev, n->gwork[cur], n->bf16, n->lds[L],
                      (int64_t)rows, (int64_t)out_cols, (float)(total_rows * out_cols), loss_slot, exact));
@@ -260,8 +272,20 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.bias_done, 0));
         // the last layer's block carries the loss sum in its tail; the other three tail floats stay zero and
         // ride along so that every exchanged count is a multiple of four floats
-        if (dp) ZN_TRY(zn_dp_allreduce(ctx, l.grads, l.blk + (idx + 1 == L ? 4 : 0), s_comm));
-        if (!exact) {
+        if (dp && !shard) ZN_TRY(zn_dp_allreduce(ctx, l.grads, idx + 1 == L ? l.cap : l.blk, s_comm));
+        if (shard) {
+            // sharded update: this rank ends with the summed gradients of its own piece of the block only, and
+            // squares just that piece (the padding inside a block is zero and adds nothing)
+            ZN_TRY(zn_dp_reduce_scatter(ctx, l.grads, l.shard, s_comm));
+            zn_lane_guard lane(ctx, ZN_LANE_COMM);
+            const size_t lo = (size_t)zn_dp_rank(ctx) * l.shard, hi = lo + l.shard < l.blk ? lo + l.shard : l.blk;
+            if (lo < hi) {
+                const zn_seg seg = {l.grads + lo, hi - lo};
+                ZN_TRY(zn_k_sumsq(ctx, &seg, 1, n->sumsq + idx));
+            } else {
+                ZN_CUDA(ctx, cudaMemsetAsync(n->sumsq + idx, 0, sizeof(double), s_comm));
+            }
+        } else if (!exact) {
             zn_lane_guard lane(ctx, ZN_LANE_COMM);
             const zn_seg segs[2] = {{l.grads, l.in * l.out}, {l.grads + l.b_off, l.out}};
             ZN_TRY(zn_k_sumsq(ctx, segs, 2, n->sumsq + idx));
@@ -321,6 +345,16 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         }
         ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars, true));
     } else {
+        if (shard) {
+            // one exchange of L + 1 doubles: every layer's sum of squares and the loss sum; the communication lane
+            // has every layer's reduce-scatter and square-sum in front of it
+            zn_lane_guard lane(ctx, ZN_LANE_COMM);
+            ZN_TRY(zn_k_f32_to_f64(ctx, loss_slot, n->sumsq + L));
+            ZN_TRY(zn_dp_allreduce_f64(ctx, n->sumsq, L + 1, s_comm));
+            ZN_TRY(zn_k_f64_to_f32(ctx, n->sumsq + L, loss_slot));
+            ZN_CUDA(ctx, cudaEventRecord(n->norm_ready, s_comm));
+            ZN_CUDA(ctx, cudaStreamWaitEvent(s_opt, n->norm_ready, 0));
+        }
         ZN_TRY(zn_k_norm_combine(ctx, n->sumsq, (int)L, n->scalars));
     }
     if (loss_dst) {
@@ -356,6 +390,32 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
             default: a.w_clamp = is_bias ? 50.0f : 100.0f; return zn_k_sgd(ctx, a, is_bias);
             }
         };
+        if (shard) {
+            // Each rank updates its own piece of the block (weights part and bias part of it separately, as the
+            // plain SGD path treats them differently), then the pieces are gathered in place and the operand
+            // copy of W is rebuilt from the gathered fp32 weights; the forward GEMM of this layer waits for that.
+            const size_t lo = (size_t)zn_dp_rank(ctx) * l.shard, hi = lo + l.shard;
+            const size_t region[2][2] = {{0, l.in * l.out}, {l.b_off, l.b_off + l.out}};
+            for (int part = 0; part < 2; ++part) {
+                const size_t a0 = lo > region[part][0] ? lo : region[part][0];
+                const size_t a1 = hi < region[part][1] ? hi : region[part][1];
+                if (a0 >= a1) continue;
+                a.w = l.params + a0; a.g = l.grads + a0; a.count = a1 - a0; a.shadow = nullptr;
+                a.m = l.m ? l.m + a0 : nullptr;
+                a.v = l.v ? l.v + a0 : nullptr;
+                ZN_TRY(update(part == 1));
+            }
+            ZN_CUDA(ctx, cudaEventRecord(l.stepped, s_opt));
+            ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.stepped, 0));
+            ZN_TRY(zn_dp_all_gather(ctx, l.params, l.shard, s_comm));
+            {
+                zn_lane_guard lane(ctx, ZN_LANE_COMM);
+                ZN_TRY(refresh_operand_copy(n, l));
+            }
+            ZN_CUDA(ctx, cudaEventRecord(l.updated, s_comm));
+            l.update_pending = true;
+            continue;
+        }
         // weights
         a.w = l.params; a.g = l.grads; a.m = l.m; a.v = l.v; a.count = l.in * l.out;
         a.shadow = l.w_op; a.shadow_bf16 = n->bf16; a.cols = (int64_t)l.out; a.ld_shadow = l.ld_w;
@@ -459,11 +519,14 @@ extern "C" void zn_net_destroy(zn_net *n) {
     for (Layer &l : n->layers) {
         if (l.grads_nccl) zn_dp_free_registered(n->ctx, l.grads, l.grads_reg);
         else cudaFree(l.grads);
-        cudaFree(l.params); cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
-        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated})
+        if (l.params_nccl) zn_dp_free_registered(n->ctx, l.params, l.params_reg);
+        else cudaFree(l.params);
+        cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
+        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated, l.stepped})
             if (ev) cudaEventDestroy(ev);
     }
     cudaFree(n->sumsq);
+    if (n->norm_ready) cudaEventDestroy(n->norm_ready);
     for (Slot &s : n->slots) {
         cudaFree(s.x); cudaFree(s.t);
         if (s.copied) cudaEventDestroy(s.copied);
@@ -490,12 +553,13 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     l.b_off = (size_t)round_up((int64_t)(input_size * output_size), 4);
     l.len = l.b_off + output_size;
     l.blk = (size_t)round_up((int64_t)l.len, 4);
-    const size_t alloc = (l.blk + 4) * sizeof(float);
+    l.cap = l.blk + 4;
+    const size_t alloc = l.cap * sizeof(float);
     ZN_CUDA(ctx, cudaMalloc((void **)&l.params, alloc));
     ZN_CUDA(ctx, cudaMalloc((void **)&l.grads, alloc));
     ZN_CUDA(ctx, cudaMemsetAsync(l.params, 0, alloc, ctx->stream));
     ZN_CUDA(ctx, cudaMemsetAsync(l.grads, 0, alloc, ctx->stream));
-    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated})
+    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated, &l.stepped})
         ZN_CUDA(ctx, cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
     if (n->tc) {
         const bool direct = !n->bf16 && output_size % 4 == 0;   // tf32 can read W itself when its pitch is TMA-legal
@@ -562,6 +626,8 @@ extern "C" zn_status zn_net_get_grads(zn_net *n, size_t layer, float *gw, float 
     zn_ctx *ctx = n->ctx;
     if (layer >= n->layers.size()) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "layer %zu out of range", layer);
     Layer &l = n->layers[layer];
+    if (n->shard_update && n->global_rows > 0 && zn_dp_active(ctx))
+        return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "with the update sharded each rank holds the summed gradients of its own piece only");
     if (gw) ZN_CUDA(ctx, cudaMemcpyAsync(gw, l.grads, l.in * l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
     if (gb) ZN_CUDA(ctx, cudaMemcpyAsync(gb, l.grads + l.b_off, l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
     ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -610,7 +676,7 @@ extern "C" zn_status zn_net_set_sgd(zn_net *n, int32_t layer, float weight_decay
 // Optimizer state blocks have the shape of the parameter block; `two` asks for the second one (Adam's v).
 static zn_status reset_state(zn_net *n, Layer &l, bool two) {
     zn_ctx *ctx = n->ctx;
-    const size_t bytes = (l.blk + 4) * sizeof(float);
+    const size_t bytes = l.cap * sizeof(float);
     if (!l.m) ZN_CUDA(ctx, cudaMalloc((void **)&l.m, bytes));
     ZN_CUDA(ctx, cudaMemsetAsync(l.m, 0, bytes, ctx->stream));
     if (two) {
@@ -884,6 +950,63 @@ extern "C" zn_status zn_net_load(zn_ctx *ctx, zn_precision precision, const char
     return ZN_OK;
 }
 
+namespace {
+
+// Moves one parameter-shaped block into an allocation of `floats` floats (zero-filled beyond what is copied).
+// `from_nccl`: try memory NCCL allocates and registers first.  The old block is released by its own kind.
+zn_status regrow_block(zn_net *n, float **blk, bool *is_nccl, void **reg, size_t old_floats, size_t floats, bool from_nccl, bool keep) {
+    zn_ctx *ctx = n->ctx;
+    void *p = nullptr, *h = nullptr;
+    bool nccl = false;
+    if (from_nccl && zn_dp_alloc_registered(ctx, floats * sizeof(float), &p, &h) == ZN_OK) nccl = true;
+    else ZN_CUDA(ctx, cudaMalloc(&p, floats * sizeof(float)));
+    ZN_CUDA(ctx, cudaMemsetAsync(p, 0, floats * sizeof(float), ctx->stream));
+    if (keep && *blk)
+        ZN_CUDA(ctx, cudaMemcpyAsync(p, *blk, (old_floats < floats ? old_floats : floats) * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*blk) {
+        if (is_nccl && *is_nccl) zn_dp_free_registered(ctx, *blk, reg ? *reg : nullptr);
+        else cudaFree(*blk);
+    }
+    *blk = (float *)p;
+    if (is_nccl) *is_nccl = nccl;
+    if (reg) *reg = h;
+    return ZN_OK;
+}
+
+}   // namespace
+
+// Data parallel with the update split over the ranks: per layer a reduce-scatter instead of the all-reduce, each
+// rank squares and updates only its own 1/world piece of the block, one exchange of L + 1 doubles carries the
+// global sums of squares and the loss, and an all-gather of the updated fp32 weights replaces the second half of
+// the all-reduce.  The bytes on NVLink are the same; the update's pass over the parameters and both optimizer
+// states, which does not shrink with the batch, is divided by the number of ranks.  Same results up to the order
+// in which NCCL adds the ranks' gradients.
+extern "C" zn_status zn_net_set_update_sharding(zn_net *n, int32_t on) {
+    ZN_TRY(check_net(n, true));
+    zn_ctx *ctx = n->ctx;
+    if (!on) { n->shard_update = false; return ZN_OK; }
+    if (n->global_rows == 0 || !zn_dp_active(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "call zn_net_set_data_parallel first");
+    if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "this NCCL has no reduce-scatter / all-gather");
+    if (n->prec == ZN_FP32_EXACT) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "FP32_EXACT sums every gradient in the reference's order on one rank; it cannot be sharded");
+    if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "steps in flight");
+    const size_t world = (size_t)zn_dp_world(ctx);
+    if (!n->norm_ready) ZN_CUDA(ctx, cudaEventCreateWithFlags(&n->norm_ready, cudaEventDisableTiming));
+    for (Layer &l : n->layers) {
+        l.shard = (size_t)round_up((int64_t)((l.blk + world - 1) / world), 4);
+        const size_t need = world * l.shard + 4;
+        if (need <= l.cap && l.params_nccl) continue;
+        const size_t cap = need > l.cap ? need : l.cap;
+        ZN_TRY(regrow_block(n, &l.params, &l.params_nccl, &l.params_reg, l.cap, cap, true, true));
+        ZN_TRY(regrow_block(n, &l.grads, &l.grads_nccl, &l.grads_reg, l.cap, cap, true, false));
+        if (l.m) ZN_TRY(regrow_block(n, &l.m, nullptr, nullptr, l.cap, cap, false, true));
+        if (l.v) ZN_TRY(regrow_block(n, &l.v, nullptr, nullptr, l.cap, cap, false, true));
+        l.cap = cap;
+    }
+    n->shard_update = true;
+    return ZN_OK;
+}
+
 // Optimizer state beside a .znn file.  The reference's format holds weights and biases only
 // (src/serialization.zig:165-183), so a run resumed from it restarts Adam's moments and step count; this
 // second file carries what Optimizer keeps per layer (src/optimizer.zig:81-88, :169-184, :236-250, :311-320):
@@ -900,6 +1023,8 @@ extern "C" zn_status zn_net_save_optimizer(zn_net *n, const char *path) {
     ZN_TRY(check_net(n, true));
     zn_ctx *ctx = n->ctx;
     if (!path) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "save_optimizer: null path");
+    if (n->shard_update && n->global_rows > 0 && zn_dp_active(ctx))
+        return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "with the update sharded each rank holds the optimizer state of its own piece only");
     FILE *f = fopen(path, "wb");
     if (!f) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "save_optimizer: cannot open %s", path);
     bool ok = fwrite("ZNO\0", 1, 4, f) == 4 && put_u32(f, ZNO_VERSION) && put_u32(f, (uint32_t)n->layers.size());
@@ -952,7 +1077,7 @@ extern "C" zn_status zn_net_load_optimizer(zn_net *n, const char *path) {
         l.beta1 = hp[0]; l.beta2 = hp[1]; l.eps = hp[2]; l.wd = hp[3]; l.momentum = hp[4]; l.rho = hp[5];
         if (S > 0) st = reset_state(n, l, S == 2);
         for (uint32_t k = 0; k < S && st == ZN_OK; ++k) {
-            host.assign(l.blk + 4, 0.0f);
+            host.assign(l.cap, 0.0f);
             if (fread(host.data(), sizeof(float), l.in * l.out, f) != l.in * l.out || fread(host.data() + l.b_off, sizeof(float), l.out, f) != l.out) {
                 st = zn_fail(ctx, ZN_ERR_INVALID_VALUE, "load_optimizer: truncated state of layer %u", i); break;
             }
@@ -976,7 +1101,7 @@ extern "C" zn_status zn_net_set_data_parallel(zn_net *n, size_t global_rows) {
         zn_ctx *ctx = n->ctx;
         for (Layer &l : n->layers) {
             if (l.grads_nccl) continue;
-            const size_t bytes = (l.blk + 4) * sizeof(float);
+            const size_t bytes = l.cap * sizeof(float);
             void *p = nullptr, *h = nullptr;
             if (zn_dp_alloc_registered(ctx, bytes, &p, &h) != ZN_OK) break;
             ZN_CUDA(ctx, cudaMemsetAsync(p, 0, bytes, ctx->stream));

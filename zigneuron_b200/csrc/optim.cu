@@ -8,6 +8,8 @@
 // src/backend.zig:2722-2772) and refreshes the tensor-core operand copy of the
 // weights.  12 bytes per parameter for SGD, 28 for Adam, plus the operand copy.
 #include <cstdlib>
+#include <atomic>
+
 #include "zn_internal.h"
 
 namespace {
@@ -321,10 +323,10 @@ __global__ void state1_vec4_kernel(zn_opt_args a) {
 // SM configured for maximum shared memory.  A kernel that lets the driver pick another shared-memory /
 // L1 split cannot share an SM with them and would only run between GEMM launches; ask for the same split.
 void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
-    static uint64_t done_mask = 0;
+    static std::atomic<uint64_t> done_mask{0};
     const uint64_t bit = 1ull << (ctx->device & 63);
-    if (done_mask & bit) return;
-    done_mask |= bit;
+    if (done_mask.load() & bit) return;
+    done_mask.fetch_or(bit);
     const int c = cudaSharedmemCarveoutMaxShared;
     const cudaFuncAttribute at = cudaFuncAttributePreferredSharedMemoryCarveout;
     cudaFuncSetAttribute(sq_partial_kernel, at, c);
@@ -437,10 +439,10 @@ zn_status zn_k_sumsq(zn_ctx *ctx, const zn_seg *segs, int nseg, double *sumsq_de
     if (blocks == 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "sum of squares: empty tensors");
     prefer_gemm_compatible_carveout(ctx);
     {
-        static uint64_t done_mask = 0;
+        static std::atomic<uint64_t> done_mask{0};
         const uint64_t bit = 1ull << (ctx->device & 63);
-        if (!(done_mask & bit)) {
-            done_mask |= bit;
+        if (!(done_mask.load() & bit)) {
+            done_mask.fetch_or(bit);
             cudaFuncSetAttribute(sumsq_final_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaFuncSetAttribute(norm_combine_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaGetLastError();
@@ -530,3 +532,23 @@ zn_status launch_state1(zn_ctx *ctx, const zn_opt_args &a) {
 
 zn_status zn_k_sgd_momentum(zn_ctx *ctx, const zn_opt_args &a) { return launch_state1<STATE1_MOMENTUM>(ctx, a); }
 zn_status zn_k_rmsprop(zn_ctx *ctx, const zn_opt_args &a) { return launch_state1<STATE1_RMSPROP>(ctx, a); }
+
+namespace {
+__global__ void f32_to_f64_kernel(const float *__restrict__ src, double *__restrict__ dst) { *dst = (double)*src; }
+__global__ void f64_to_f32_kernel(const double *__restrict__ src, float *__restrict__ dst) { *dst = (float)*src; }
+}   // namespace
+
+// One value between the float loss slot and the double array the ranks exchange with the sums of squares.
+zn_status zn_k_f32_to_f64(zn_ctx *ctx, const float *src, double *dst) {
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, 12.0);
+    f32_to_f64_kernel<<<1, 1, 0, ctx->stream>>>(src, dst);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+zn_status zn_k_f64_to_f32(zn_ctx *ctx, const double *src, float *dst) {
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, 12.0);
+    f64_to_f32_kernel<<<1, 1, 0, ctx->stream>>>(src, dst);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}

@@ -4,6 +4,8 @@
 // and grids that are multiples of the SM count; reductions are two-stage
 // (block partials in the context's scratch, then one block adds them in a fixed
 // order), so results do not depend on scheduling.
+#include <atomic>
+
 #include "zn_internal.h"
 #include "zn_act.cuh"
 
@@ -453,10 +455,10 @@ __global__ void sum_partials_kernel(const float *__restrict__ partial, int n, fl
 // for maximum shared memory; a kernel left to another shared-memory / L1 split cannot share an SM with
 // them.  Ask for the same split (see the same note in optim.cu).
 void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
-    static uint64_t done_mask = 0;
+    static std::atomic<uint64_t> done_mask{0};
     const uint64_t bit = 1ull << (ctx->device & 63);
-    if (done_mask & bit) return;
-    done_mask |= bit;
+    if (done_mask.load() & bit) return;
+    done_mask.fetch_or(bit);
     const int c = cudaSharedmemCarveoutMaxShared;
     const cudaFuncAttribute at = cudaFuncAttributePreferredSharedMemoryCarveout;
     cudaFuncSetAttribute(bias_reduce_partial_kernel<float, 4>, at, c);

@@ -176,6 +176,8 @@ zn_status zn_k_scale(zn_ctx *ctx, float *p, size_t n, const float *factor_dev);
 // writes norm / clip factor as zn_k_grad_norm does.
 zn_status zn_k_sumsq(zn_ctx *ctx, const zn_seg *segs, int nseg, double *sumsq_dev);
 zn_status zn_k_norm_combine(zn_ctx *ctx, const double *sumsq_dev, int count, float *norm_factor_dev);
+zn_status zn_k_f32_to_f64(zn_ctx *ctx, const float *src, double *dst);   // one value
+zn_status zn_k_f64_to_f32(zn_ctx *ctx, const double *src, float *dst);
 
 // metrics.evaluateClassification on fp32 device blocks; confusion / metrics4 are host memory (either may be null).
 zn_status zn_k_classification_metrics(zn_ctx *ctx, const float *out_dev, int64_t ld_o, const float *tgt_dev, int64_t ld_t,

@@ -196,5 +196,10 @@ class Network:
     def setDataParallel(self, global_rows):
         self._ck(lib.zn_net_set_data_parallel(self.handle, global_rows))
 
+    def setUpdateSharding(self, on=True):
+        """After setDataParallel: reduce-scatter / update 1/world of the parameters / all-gather instead of
+        all-reduce + full update on every rank."""
+        self._ck(lib.zn_net_set_update_sharding(self.handle, int(on)))
+
 
 __all__ = ["Network", "Sgd", "Adam", "Loss", "Activation"]
