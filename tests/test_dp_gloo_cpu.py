@@ -78,3 +78,88 @@ def test_two_rank_sum_equals_single_process(tmp_path, loss_name, adam):
         assert np.array_equal(r0[f"W{i}"], r1[f"W{i}"]) and np.array_equal(r0[f"b{i}"], r1[f"b{i}"])
         assert np.allclose(r0[f"W{i}"], W, rtol=1e-4, atol=2e-6)
         assert np.allclose(r0[f"b{i}"], b, rtol=1e-4, atol=2e-6)
+
+
+def _rank_sharded(rank, world, port, loss, adam, out_dir):
+    """The sharded update the library offers under data parallel, restated with the oracle's flat update functions:
+    reduce-scatter of each layer's [W | pad | b] block, sums of squares of the own piece, one all-reduce of
+    L + 1 doubles (squares and loss), update of the own piece, all-gather."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import zn_oracle as zo
+    net, x, t = _build(loss, adam)
+    B, L, lr = x.shape[0], 3, np.float32(0.05)
+    up4 = lambda v: (v + 3) // 4 * 4
+    state = [None] * L
+    losses = []
+    for step in range(3):
+        lo_r, hi_r = zo.distribute_round_robin(B, world, rank)
+        shard_loss = net.shard_gradients(x[lo_r:hi_r], t[lo_r:hi_r], hi_r - lo_r, B, loss)
+        scal = np.zeros(L + 1, np.float64)
+        scal[L] = shard_loss
+        pieces = []
+        for i in range(L):
+            (W, b), (gW, gb) = net.get_params(i), net.get_grads(i)
+            b_off = up4(W.size)
+            blk = up4(b_off + b.size)
+            shard = up4((blk + world - 1) // world)
+            g = np.zeros(world * shard, np.float32)
+            g[:W.size], g[b_off:b_off + b.size] = gW.ravel(), gb
+            gt = torch.from_numpy(g)
+            dist.all_reduce(gt)                               # gloo has no reduce-scatter: sum, then keep the own piece
+            lo, hi = rank * shard, (rank + 1) * shard
+            own = g[lo:hi].copy()
+            scal[i] = float((own.astype(np.float64) ** 2).sum())
+            pieces.append((W, b, b_off, shard, lo, hi, own))
+        st = torch.from_numpy(scal)
+        dist.all_reduce(st)
+        norm = np.float32(np.sqrt(np.float32(scal[:L].sum())))
+        factor = np.float32(1.0) / (norm + np.float32(1e-6)) if norm > 1.0 else np.float32(1.0)
+        for i, (W, b, b_off, shard, lo, hi, own) in enumerate(pieces):
+            p = np.zeros(world * shard, np.float32)
+            p[:W.size], p[b_off:b_off + b.size] = W.ravel(), b
+            own = own * factor if factor != 1.0 else own
+            if adam and state[i] is None:
+                state[i] = [np.zeros(world * shard, np.float32), np.zeros(world * shard, np.float32), 0]
+            if adam:
+                state[i][2] += 1
+                bc1, bc2 = zo.adam_bias_corrections(0.9, 0.999, state[i][2])
+            for part, (r0_, r1_) in enumerate([(0, W.size), (b_off, b_off + b.size)]):
+                a0, a1 = max(lo, r0_), min(hi, r1_)
+                if a0 >= a1:
+                    continue
+                gp = own[a0 - lo:a1 - lo]
+                if adam:
+                    m, v = state[i][0], state[i][1]
+                    p[a0:a1], m[a0:a1], v[a0:a1] = zo.adam_update(p[a0:a1], gp, m[a0:a1], v[a0:a1], lr, 0.9, 0.999, 1e-8, bc1, bc2)
+                elif part == 0:
+                    p[a0:a1] = zo.sgd_update(p[a0:a1], gp, lr, 0.0)
+                else:
+                    p[a0:a1] = zo.sgd_update_bias(p[a0:a1], gp, lr)
+            mine = torch.from_numpy(p[lo:hi].copy())
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            p = torch.cat(parts).numpy()
+            net.set_params(i, p[:W.size].reshape(W.shape), p[b_off:b_off + b.size])
+        losses.append(float(scal[L]) if loss == zo.MSE else float(scal[L]) / B)
+    np.savez(os.path.join(out_dir, f"r{rank}.npz"), losses=np.array(losses, np.float32),
+             **{f"W{i}": net.get_params(i)[0] for i in range(3)}, **{f"b{i}": net.get_params(i)[1] for i in range(3)})
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("loss_name,adam", [("mse", False), ("ce", True)])
+def test_sharded_update_equals_single_process(tmp_path, loss_name, adam):
+    from oracle import zn_oracle as zo
+    loss = zo.MSE if loss_name == "mse" else zo.CE_LOGITS
+    port = 29800 + (os.getpid() % 150) + (0 if adam else 1)
+    mp.spawn(_rank_sharded, args=(2, port, loss, adam, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "r0.npz"), np.load(tmp_path / "r1.npz")
+    net, x, t = _build(loss, adam)
+    want = [net.train_step(x, t, x.shape[0], 0.05, loss) for _ in range(3)]
+    assert np.allclose(r0["losses"], want, rtol=2e-5, atol=1e-6)
+    for i in range(3):
+        W, b = net.get_params(i)
+        assert np.array_equal(r0[f"W{i}"], r1[f"W{i}"]) and np.array_equal(r0[f"b{i}"], r1[f"b{i}"])
+        assert np.allclose(r0[f"W{i}"], W, rtol=1e-4, atol=2e-6)
+        assert np.allclose(r0[f"b{i}"], b, rtol=1e-4, atol=2e-6)
