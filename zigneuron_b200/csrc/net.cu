@@ -547,6 +547,7 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     if (!n->layers.empty() && n->layers.back().out != input_size)
         return zn_fail(ctx, ZN_ERR_SHAPE, "layer input %zu does not match previous output %zu", input_size, n->layers.back().out);
     if (n->inflight) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "steps in flight");
+    if (n->shard_update) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "add every layer before zn_net_set_update_sharding");
     if (n->layers.size() >= 16) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "at most 16 Dense layers per network");
     Layer l;
     l.in = input_size; l.out = output_size; l.act = act;
