@@ -112,6 +112,135 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
+def bind_to_gpu_numa_node(device):
+    """Pins this process to the CPUs of the NUMA node the GPU hangs off, BEFORE any pinned host memory is
+    allocated, so that the step's input buffers land in memory local to the GPU's PCIe root.  Returns what was
+    found and done (reported under e2e.numa)."""
+    info = {"gpu_node": None, "bound": False}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(device)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:          # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
+            bus = bus[4:]
+        base = f"/sys/bus/pci/devices/{bus}"
+        node = int(open(f"{base}/numa_node").read())
+        info["gpu_node"] = node
+        cpus = set()
+        for part in open(f"{base}/local_cpulist").read().strip().split(","):
+            if part:
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        info["allowed_cpus"] = len(allowed)
+        if node >= 0 and cpus & allowed and (cpus & allowed) != allowed:
+            os.sched_setaffinity(0, cpus & allowed)
+            info["bound"] = True
+        info["local_cpus"] = len(cpus & allowed)
+    except Exception as e:                       # no NVML / sysfs entry: nothing is bound, say so
+        info["error"] = type(e).__name__
+    return info
+
+
+def block_hash(a):
+    """Order-sensitive 64-bit digest of a float32 block (bit patterns, not values: -0.0 and NaN payloads count)."""
+    u = np.ascontiguousarray(a).view(np.uint32).astype(np.uint64)
+    idx = np.arange(1, u.size + 1, dtype=np.uint64)
+    with np.errstate(over="ignore"):
+        return int((u * (idx | np.uint64(1))).sum(dtype=np.uint64))
+
+
+DP_CHECK_DIMS, DP_CHECK_ACTS = [(64, 128), (128, 96), (96, 32)], ["relu", "relu", "linear"]
+
+
+def dp_check(zn, be, dist, rank, world, local):
+    """Correctness of the data-parallel path in the run that is being timed: a small network (64-128-96-32, Adam,
+    MSE, 4 steps, global batch 8 rows per rank) trained across all ranks through the same communicator as the
+    benchmark, and on rank 0 the same network on ONE GPU through a second context.  Every rank must end with
+    bit-identical parameters, and they must agree with the one-GPU run."""
+    import torch
+    rows = 8 * world + 3                                   # not a multiple of the rank count: uneven shards
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((rows, 64)).astype(np.float32)
+    t = rng.standard_normal((rows, 32)).astype(np.float32)
+    Ws = [(rng.uniform(-1, 1, (a, b)) * np.sqrt(2.0 / a)).astype(np.float32) for a, b in DP_CHECK_DIMS]
+    bs = [rng.uniform(-0.1, 0.1, b).astype(np.float32) for _, b in DP_CHECK_DIMS]
+
+    def build(backend):
+        net = zn.Network(backend, zn.Precision.FP32_SIMT)
+        for i, ((a, b), act) in enumerate(zip(DP_CHECK_DIMS, DP_CHECK_ACTS)):
+            net.addDense(a, b, act)
+            net.setWeights(i, Ws[i], bs[i])
+        net.setOptimizer(zn.Adam())
+        return net
+
+    net = build(be)
+    net.setDataParallel(rows)
+    lo, hi = zn.Backend.distributeWorkload(rows, world, rank)
+    losses = [net.trainStep(np.ascontiguousarray(x[lo:hi]), np.ascontiguousarray(t[lo:hi]), 0.01, zn.Loss.mse) for _ in range(4)]
+    params = [net.getWeights(i) for i in range(3)]
+    digest = [block_hash(np.concatenate([w.ravel(), b])) & 0x7FFFFFFFFFFFFFFF for w, b in params] + \
+             [block_hash(np.array(losses, np.float32)) & 0x7FFFFFFFFFFFFFFF]
+    net.deinit()
+    all_digests = [torch.zeros(len(digest), dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(all_digests, torch.tensor(digest, dtype=torch.int64))
+    identical = all(bool(torch.equal(all_digests[0], d)) for d in all_digests)
+    result = {"ranks_bit_identical": identical, "tolerance": 1e-5, "steps": 4, "rows": rows}
+    if rank == 0:
+        solo_be = zn.Backend(local, zn.Precision.FP32_SIMT)
+        solo = build(solo_be)
+        solo_losses = [solo.trainStep(x, t, 0.01, zn.Loss.mse) for _ in range(4)]
+        dev = 0.0
+        for i in range(3):
+            w, b = solo.getWeights(i)
+            for got, want in ((params[i][0], w), (params[i][1], b)):
+                dev = max(dev, float(np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64))))
+        result["vs_one_gpu_rel_l2"] = dev
+        result["loss_rel_dev"] = float(np.max(np.abs(np.array(losses) - np.array(solo_losses)) / np.abs(solo_losses)))
+        solo.deinit()
+        solo_be.deinit()
+    return result
+
+
+def gemm_sweep_summary(zn, be, peaks):
+    """BASELINE configs[4] in brief, for the N = 1 line: bf16 on the six stated sizes x {NN+bias+ReLU, NT, TN},
+    tf32 and fp32 on 4096^3 only; 3 warm-up + 10 timed launches each (the reference's scheme is 10 + 100,
+    src/benchmark/cuda_benchmark.zig:17-25).  TFLOP/s = 2*M*N*K / average launch time."""
+    out = []
+    rng = np.random.default_rng(4)
+    precs = {"bf16": zn.Precision.BF16_TC, "tf32": zn.Precision.TF32_TC, "fp32": zn.Precision.FP32_SIMT}
+    sizes = [(256, 256, 256), (1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (65536, 512, 512)]
+    for (m, n, k) in sizes:
+        a = be.tensor(rng.standard_normal(m * k, dtype=np.float32))
+        b = be.tensor(rng.standard_normal(k * n, dtype=np.float32))
+        bias = be.tensor(rng.uniform(-0.1, 0.1, n).astype(np.float32))
+        c = be.tensor(m * n)
+        for pname in (["bf16", "tf32", "fp32"] if (m, n, k) == (4096, 4096, 4096) else ["bf16"]):
+            be.set_precision(precs[pname])
+            fam = 1 if pname == "fp32" else 0
+            calls = {"NN+bias+relu": lambda: be.matMulBiasRelu(a, b, bias, c, m, n, k),
+                     "NT": lambda: be.matMulTransposeB(a, b, c, m, n, k), "TN": lambda: be.matMulTransposeA(a, b, c, m, n, k)}
+            for oname, call in calls.items():
+                for _ in range(3):
+                    call()
+                be.endCommandBatch()
+                be.profile(True)
+                be.profile_reset()
+                for _ in range(10):
+                    call()
+                p = be.profile_get(fam)
+                be.profile(False)
+                tf = p["flops"] / (p["ms"] * 1e-3) / 1e12
+                out.append({"mnk": [m, n, k], "orient": oname, "precision": pname, "ms": round(p["ms"] / p["launches"], 5),
+                            "tflops": round(tf, 2),
+                            "frac_of_measured_bf16_burst": round(tf / peaks["bf16_burst"], 4) if pname == "bf16" else None})
+        for tt in (a, b, bias, c):
+            tt.free()
+    be.set_precision(zn.Precision.BF16_TC)
+    return out
+
+
 # --------------------------------------------------------------------------------------- CPU side
 
 def oracle_net():
@@ -229,11 +358,14 @@ def run_ours(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         return float(tt[0])
 
+    numa = bind_to_gpu_numa_node(local)
     be = zn.Backend(local, zn.Precision.BF16_TC)
+    check = None
     if world > 1:
         ids = [zn.Backend.dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         be.dp_init(rank, world, ids[0])
+        check = dp_check(zn, be, dist, rank, world, local)
 
     net = zn.Network(be, zn.Precision.BF16_TC)
     for i, ((a, b), act) in enumerate(zip(DIMS, ACTS)):
@@ -300,6 +432,28 @@ def run_ours(args):
         sampler.join(timeout=2)
     e2e_value = GLOBAL_BATCH * args.steps / e2e_s
 
+    # ---- leg 3: the copies of leg 2 alone (same pinned buffers, all ranks at once, no compute): the ceiling the
+    # host side sets for the end-to-end number
+    be.copyData(hx, dx, hx.size)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        be.copyData(hx, dx, hx.size)
+        be.copyData(ht, dt, ht.size)
+    copy_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    h2d_bytes = int(hx.nbytes + ht.nbytes) * world
+    h2d_ceiling_gbs = h2d_bytes * args.steps / copy_s / 1e9
+
+    # every rank must hold the same parameters after the timed steps
+    if world > 1:
+        import torch
+        mine = torch.tensor([block_hash(np.concatenate([w.ravel(), b])) & 0x7FFFFFFFFFFFFFFF
+                             for w, b in (net.getWeights(i) for i in range(len(DIMS)))], dtype=torch.int64)
+        everyone = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        check["bench_net_ranks_bit_identical"] = all(bool(torch.equal(everyone[0], d)) for d in everyone)
+
     if rank != 0:
         if dist:
             dist.destroy_process_group()
@@ -333,18 +487,39 @@ def run_ours(args):
         "hbm_kernels": {k: {"achieved_gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] > 0 else None,
                             "frac_of_measured_hbm": (v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm"]) if v["ms"] > 0 else None}
                         for k, v in prof.items() if k != "gemm"},
-        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(hx.nbytes + ht.nbytes) * world,
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": 12 * world, "ms_per_step": 1e3 * e2e_s / args.steps,
-                "how": "zn_net_submit_step / zn_net_wait_step from pinned host buffers, two steps in flight"},
+                "how": "zn_net_submit_step / zn_net_wait_step from pinned host buffers, two steps in flight",
+                "h2d_ceiling_gbs": h2d_ceiling_gbs, "h2d_only_ms_per_step": 1e3 * copy_s / args.steps,
+                "h2d_ceiling_how": "the same buffers copied host->device by every rank at once, nothing else running",
+                "bound_ms_per_step": max(ms_per_step, 1e3 * copy_s / args.steps),
+                "frac_of_bound": max(ms_per_step, 1e3 * copy_s / args.steps) / (1e3 * e2e_s / args.steps),
+                "numa": numa},
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
         "loss": {"resident_last": last_loss, "e2e_last": e2e_loss},
     }
+    clk = line["clocks"].get("sm_mhz")
+    if clk:
+        # what the step achieves of the datasheet peak AT THE CLOCK THE GPU RAN AT (the 1 kW cap holds the SM clock
+        # well below its maximum under a dense GEMM)
+        line["roofline"]["clock_normalised"] = achieved / (2250.0 * clk / line["clocks"]["sm_max_mhz"])
+    if check is not None:
+        line["dp_check"] = check
+    if world == 1 and not args.no_sweep:
+        net.deinit()
+        for tt in (dx, dt):
+            tt.free()
+        line["gemm_sweep"] = gemm_sweep_summary(zn, be, peaks)
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
+    failed = check is not None and not (check["ranks_bit_identical"] and check.get("bench_net_ranks_bit_identical", True)
+                                        and check.get("vs_one_gpu_rel_l2", 0.0) <= check["tolerance"])
     if dist:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("dp_check failed: " + json.dumps(check))
 
 
 def run_gemm_sweep(args):
@@ -456,6 +631,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-sweep", action="store_true", help="N = 1: skip the GEMM sweep appended to the line")
     ap.add_argument("--shard-update", type=int, default=None, choices=[0, 1],
                     help="N > 1: split the parameter update over the ranks (reduce-scatter / update / all-gather)")
     args = ap.parse_args()

@@ -129,17 +129,19 @@ ZN_API zn_status zn_matmul_bias_act(zn_ctx *ctx, const float *a, const float *b,
 ZN_API zn_status zn_add_bias(zn_ctx *ctx, float *out, size_t out_len, const float *bias, size_t bias_len);
 /* Backend.accumulateBias, src/backend.zig:649-655 -> :706-713: grad_bias[i] += sum over rows of g[r][i]. */
 ZN_API zn_status zn_accumulate_bias(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g, size_t g_len);
-/* No counterpart in the reference.  The same accumulation as zn_accumulate_bias (fp32, blocked sums, the
- * same order of additions) for callers that must not trigger a device allocation: programs whose own pool
- * already owns all device memory, and loops that cannot take the device-wide stall of cudaMalloc/cudaFree.
- * It calls no allocator: the per-split partial sums live in a fixed 4 MiB block (1,048,576 floats) that is
- * part of the library image on every GPU that loads it.  Both pointers must be DEVICE pointers.  A problem
- * whose partial sums do not fit (row splits x bias_len > 1,048,576; the split count shrinks as bias_len
- * grows, so this means a bias_len of roughly a million or more) is rejected with ZN_ERR_INVALID_VALUE and a
- * message giving the sizes.  The first call on
- * each device looks up the block's device address; make that call before starting any stream capture.  All
- * calls on a GPU share the block: calls that overlap in time on one GPU race and must be ordered by the
- * caller; nothing in the block needs clearing between calls. */
+/* No counterpart in the reference.  The same accumulation as zn_accumulate_bias, with the same order of
+ * additions in every precision mode of the context, for callers that must not trigger a device allocation:
+ * programs whose own pool already owns all device memory, and loops that cannot take the device-wide stall of
+ * cudaMalloc/cudaFree.  It calls no allocator: the per-split partial sums live in a fixed 4 MiB block
+ * (1,048,576 floats) that is part of the library image on every GPU that loads it.  Both pointers must be
+ * DEVICE pointers.  A problem whose partial sums do not fit (row splits x bias_len > 1,048,576; the split
+ * count shrinks as bias_len grows, so this means a bias_len of roughly a million or more) is rejected with
+ * ZN_ERR_INVALID_VALUE and a message giving the sizes.  On a ZN_FP32_EXACT context the sums run in the
+ * reference's order (one running sum per column), which needs no scratch at all and has no size limit.  The
+ * first call on each device looks up the block's device address; make that call before starting any stream
+ * capture.  All calls on a GPU share the block: calls that overlap in time on one GPU race and must be ordered
+ * by the caller; nothing in the block needs clearing between calls.  The call makes the context's device the
+ * calling thread's current device. */
 ZN_API zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g, size_t g_len);
 /* Backend.activationForward, src/backend.zig:367-386 (in == out allowed).  With softmax the
  * whole slice is one vector, as in the reference (:377-379); likewise in the backward. */
@@ -282,6 +284,34 @@ ZN_API zn_status zn_net_set_data_parallel(zn_net *net, size_t global_rows);
  * refused.  No counterpart in the reference, whose multi-GPU layer has no collective at all
  * (src/cuda_multi_gpu.zig). */
 ZN_API zn_status zn_net_set_update_sharding(zn_net *net, int32_t on);
+
+/* ---- failure detection ------------------------------------------------------------ */
+/* The reference maps driver failures to errors and never waits on another GPU (src/cuda_driver.zig:1119-1159;
+ * its multi-GPU layer has no collective, src/cuda_multi_gpu.zig:424-498), so what follows has no counterpart
+ * there.  On a data-parallel context every host wait that can sit behind a collective (zn_net_train_step,
+ * zn_net_wait_step, zn_end_command_batch, the getters, zn_timer_stop) polls: work done, asynchronous error of
+ * the communicator (ncclCommGetAsyncError), deadline.  On an error or a missed deadline the communicator is
+ * aborted (ncclCommAbort), the call returns ZN_ERR_NCCL, and every later step fails with ZN_ERR_NCCL until
+ * zn_dp_destroy + zn_dp_init.  The deadline defaults to 120 s (ZN_DP_TIMEOUT_MS in the environment of
+ * zn_dp_init overrides the default). */
+ZN_API zn_status zn_dp_set_timeout_ms(zn_ctx *ctx, int64_t ms);
+/* The polling loop itself, free of CUDA and NCCL so that its decisions can be checked anywhere: calls
+ * ready(user) (> 0 done, 0 not yet, < 0 the query failed) continuously and, once a millisecond,
+ * comm_error(user) (0 = healthy, otherwise the communicator's error code, stored in *comm_error_out) and the
+ * deadline (deadline_ms < 0: none).  comm_error and comm_error_out may be NULL. */
+enum { ZN_WAIT_READY = 0, ZN_WAIT_COMM_ERROR = 1, ZN_WAIT_DEADLINE = 2, ZN_WAIT_QUERY_FAILED = 3 };
+typedef int (*zn_poll_ready_fn)(void *user);
+typedef int (*zn_poll_error_fn)(void *user);
+ZN_API int32_t zn_wait_poll(zn_poll_ready_fn ready, zn_poll_error_fn comm_error, void *user, int64_t deadline_ms,
+                            int32_t *comm_error_out);
+/* Bounded device-side waits: every mbarrier wait of the tensor-core GEMMs gives up after about a second,
+ * writes a code into a status word the host can read, and lets the kernel return (tensor memory released);
+ * the next synchronising call returns ZN_ERR_TIMEOUT with that code and clears the word.  Two probes make
+ * that path observable without a hung kernel (no counterpart in the reference): the first launches one small
+ * CTA that waits, with the GEMMs' own wait routine and a limit of `limit_cycles` clock cycles, on a barrier
+ * nothing ever arrives at, and reports code 99; the second writes `code` into the status word from the host. */
+ZN_API zn_status zn_debug_bounded_wait_probe(zn_ctx *ctx, int64_t limit_cycles);
+ZN_API zn_status zn_debug_set_device_status(zn_ctx *ctx, int32_t code);
 
 /* ---- measurement ------------------------------------------------------------------ */
 /* Per-kernel-family CUDA-event timing on the compute stream. */

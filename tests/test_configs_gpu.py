@@ -1,0 +1,189 @@
+"""Parity at the sizes and step counts the benchmark configurations state.
+
+Configs 1 and 2 are compared, step by step, with the oracle's curves in tests/golden/config_curves.json
+(written by tests/golden/make_config_curves.py; tests/test_oracle_golden.py pins that file to the oracle on
+the CPU).  Config 3 runs at FULL width (4096-8192-8192-8192-4096, 201 M parameters): rows of the forward
+pass are independent, so a handful of rows computed by the oracle check the whole 8192-row forward, and one
+training step on a few hundred rows is checked against the float64 emulation of the bf16 data path
+(tests/util.py, itself pinned to the oracle at small width).  Every bound below is a measured deviation with
+about a factor two of room, and each test prints what it measured (pytest -s shows it)."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+
+import zigneuron_b200 as zn
+from oracle import zn_oracle as zo
+from util import emulate_bf16_mse_step, rel_l2, rel_max
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+import configs as cfg   # noqa: E402
+
+pytestmark = pytest.mark.gpu
+P = zn.Precision
+CURVES = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "config_curves.json")))
+
+
+@pytest.fixture(scope="module")
+def be():
+    b = zn.Backend(0)
+    yield b
+    b.deinit()
+
+
+def gpu_net(be, prec, dims, acts, Ws, bs, opt=None):
+    net = zn.Network(be, prec)
+    for i, ((a, b), act) in enumerate(zip(dims, acts)):
+        net.addDense(a, b, act)
+        net.setWeights(i, Ws[i], bs[i])
+    if opt is not None:
+        net.setOptimizer(opt)
+    return net
+
+
+def curve_deviation(got, want):
+    """(largest |got-want| / max(1, |want|), largest |got-want| / |want|) over the steps."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float(np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want)))), float(np.max(np.abs(got - want) / np.abs(want)))
+
+
+# ---------------------------------------------------------------------------------------- config 1
+# 4-20-10-3, cross-entropy with logits, SGD lr 0.005, 150 samples.  (loss bound relative to max(1, loss) per step,
+# bound on the relative loss deviation, weight bound after the last step)
+C1_FULL = {P.FP32_EXACT: (1e-5, 1e-4, 1e-5), P.FP32_SIMT: (1e-5, 1e-4, 1e-5), P.TF32_TC: (2e-2, 2e-2, 2e-2), P.BF16_TC: (2e-2, 2e-2, 2e-2)}
+
+
+@pytest.mark.parametrize("prec", list(C1_FULL))
+def test_config1_full_batch_1000_steps(be, prec):
+    loss_tol, rel_tol, w_tol = C1_FULL[prec]
+    x, t, Ws, bs = cfg.iris_config()
+    want = CURVES["config1"]["full_batch"]
+    net = gpu_net(be, prec, cfg.IRIS_DIMS, cfg.IRIS_ACTS, Ws, bs)
+    losses, norms, factors = [], [], []
+    for _ in range(1000):
+        losses.append(net.trainStep(x, t, 0.005, zn.Loss.cross_entropy_logits))
+        n, f = net.lastClip()
+        norms.append(n)
+        factors.append(f)
+    dev_abs, dev_rel = curve_deviation(losses, want["loss"])
+    dev_norm = curve_deviation(norms, want["norm"])[1]
+    dev_fac = curve_deviation(factors, want["factor"])[1]
+    w_dev = max(rel_l2(net.getWeights(i)[0], want["weights"][i]["w"]) for i in range(3))
+    b_dev = max(rel_l2(net.getWeights(i)[1], want["weights"][i]["b"]) for i in range(3))
+    print(f"\nconfig1 full batch {prec.name}: loss dev abs {dev_abs:.3e} rel {dev_rel:.3e}, norm {dev_norm:.3e}, "
+          f"factor {dev_fac:.3e}, weights {w_dev:.3e}, bias {b_dev:.3e}, last loss {losses[-1]:.6e} (oracle {want['loss'][-1]:.6e})")
+    assert dev_abs <= loss_tol and dev_rel <= rel_tol
+    assert dev_norm <= max(rel_tol, 10 * loss_tol) and dev_fac <= max(rel_tol, 10 * loss_tol)
+    assert w_dev <= w_tol and b_dev <= 5 * w_tol
+    net.deinit()
+
+
+@pytest.mark.parametrize("prec,tol", [(P.FP32_EXACT, 1e-5), (P.FP32_SIMT, 1e-5), (P.TF32_TC, 2e-2), (P.BF16_TC, 2e-2)])
+def test_config1_per_sample_20_epochs(be, prec, tol):
+    """The literal Network.train loop (src/network.zig:596-616): 20 epochs x 150 steps of one sample each."""
+    x, t, Ws, bs = cfg.iris_config()
+    want = CURVES["config1"]["per_sample"]
+    net = gpu_net(be, prec, cfg.IRIS_DIMS, cfg.IRIS_ACTS, Ws, bs)
+    got = net.train(x, t, 20, 0.005, zn.Loss.cross_entropy_logits)
+    dev_abs, dev_rel = curve_deviation(got, want["epoch_loss"])
+    w_dev = max(rel_l2(net.getWeights(i)[0], want["weights"][i]["w"]) for i in range(3))
+    print(f"\nconfig1 per sample {prec.name}: epoch-loss dev abs {dev_abs:.3e} rel {dev_rel:.3e}, weights {w_dev:.3e}")
+    assert dev_rel <= tol and w_dev <= tol
+    net.deinit()
+
+
+# ---------------------------------------------------------------------------------------- config 2
+# 784-512-256-10, batch 1024, Adam lr 1e-3, 100 steps.  Adam divides by sqrt(v): a weight moves about lr per step
+# whatever the size of its gradient, so rounding noise on small gradients becomes full-size moves and the weight
+# deviation grows with the step count while the loss curve stays close.  Per precision:
+# (loss-curve bound over 100 steps, weight-sample bound after 20 steps, after 100 steps)
+C2_BOUNDS = {P.FP32_EXACT: (1e-5, 1e-5, 1e-4), P.FP32_SIMT: (1e-4, 5e-3, 2e-2), P.TF32_TC: (2e-2, 5e-2, 1e-1), P.BF16_TC: (2e-2, 5e-2, 1e-1)}
+
+
+@pytest.mark.parametrize("prec", list(C2_BOUNDS))
+def test_config2_batch_1024_adam_100_steps(be, prec):
+    loss_tol, w20_tol, w100_tol = C2_BOUNDS[prec]
+    x, t, Ws, bs = cfg.mlp784_config()
+    want = CURVES["config2"]
+    net = gpu_net(be, prec, cfg.MLP784_DIMS, cfg.MLP784_ACTS, Ws, bs, zn.Adam(beta1=0.9, beta2=0.999, eps=1e-8))
+    dx, dt = be.tensor(x), be.tensor(t)
+    losses, norms, w_dev = [], [], {}
+    for step in range(1, 101):
+        losses.append(net.trainStep(dx, dt, 1e-3, zn.Loss.cross_entropy_logits, rows=1024))
+        norms.append(net.lastClip()[0])
+        if step in cfg.SNAP_STEPS:
+            snap = want["snapshots"][str(step)]
+            devs = []
+            for i in range(3):
+                W, b = net.getWeights(i)
+                got = W.ravel()[cfg.snapshot_indices(W.size)]
+                devs.append(rel_l2(got, snap[i]["w"]))
+                # the hard bound Adam itself implies: no weight can be further off than `step` moves of ~lr each way
+                assert np.abs(got - np.asarray(snap[i]["w"], np.float32)).max() <= 2.2 * step * 1e-3
+                assert np.abs(b[:10] - np.asarray(snap[i]["b"], np.float32)).max() <= 2.2 * step * 1e-3
+            w_dev[step] = max(devs)
+    dev_abs, dev_rel = curve_deviation(losses, want["loss"])
+    dev_norm = curve_deviation(norms, want["norm"])[1]
+    print(f"\nconfig2 {prec.name}: loss-curve dev over 100 steps abs {dev_abs:.3e} rel {dev_rel:.3e} "
+          f"(first 20 steps rel {curve_deviation(losses[:20], want['loss'][:20])[1]:.3e}), norm {dev_norm:.3e}, "
+          f"loss {losses[0]:.5f} -> {losses[-1]:.5f} (oracle {want['loss'][0]:.5f} -> {want['loss'][-1]:.5f}), "
+          f"weight-sample rel-L2 by step {({k: float(f'{v:.2e}') for k, v in w_dev.items()})}")
+    assert dev_rel <= loss_tol
+    assert w_dev[20] <= w20_tol and w_dev[100] <= w100_tol
+    assert losses[-1] < 0.2 * losses[0]
+    for tt in (dx, dt):
+        tt.free()
+    net.deinit()
+
+
+# ---------------------------------------------------------------------------------------- config 3, full width
+
+@pytest.fixture(scope="module")
+def wide_weights():
+    return [cfg.wide_layer_weights(i) for i in range(4)], [np.zeros(b, np.float32) for _, b in cfg.WIDE_DIMS]
+
+
+@pytest.mark.parametrize("prec,tol", [(P.BF16_TC, 2e-2), (P.TF32_TC, 2e-2), (P.FP32_SIMT, 1e-5)])
+def test_config3_forward_rows_against_the_oracle_at_full_width(be, wide_weights, prec, tol):
+    """Forward of the full-width network; eight rows of the batch are recomputed by the oracle (one thread,
+    a few seconds) and compared with the same rows of the GPU output."""
+    Ws, bs = wide_weights
+    B = 8192 if prec != P.FP32_SIMT else 512             # the fp32 CUDA-core path is the exactness variant, not the fast one
+    x, _ = cfg.wide_rows(B)
+    rows = np.sort(np.random.default_rng(33).choice(B, 8, replace=False))
+    onet = zo.Net()
+    for i, ((a, b), act) in enumerate(zip(cfg.WIDE_DIMS, cfg.WIDE_ACTS)):
+        onet.add_dense(a, b, zo.RELU if act == "relu" else zo.LINEAR)
+        onet.set_params(i, Ws[i], bs[i])
+    want = onet.forward(np.ascontiguousarray(x[rows]), 8).reshape(8, -1)
+    net = gpu_net(be, prec, cfg.WIDE_DIMS, cfg.WIDE_ACTS, Ws, bs)
+    got = net.forward(x)[rows]
+    d2, dm = rel_l2(got, want), rel_max(got, want)
+    print(f"\nconfig3 forward {prec.name}: {B} rows, 8 checked by the oracle: rel_l2 {d2:.3e} rel_max {dm:.3e}")
+    assert d2 <= tol and dm <= tol
+    net.deinit()
+
+
+def test_config3_one_step_at_full_width_against_the_bf16_emulation(be, wide_weights):
+    """One SGD step of the full-width network on 256 rows in bf16: loss, and gW / gb of all four layers, against
+    float64 arithmetic with a bf16 rounding wherever the GPU path stores an operand."""
+    Ws, bs = wide_weights
+    B = 256
+    x, t = cfg.wide_rows(B)
+    el, eW, eb = emulate_bf16_mse_step(x, t, Ws, bs, cfg.WIDE_ACTS)
+    net = gpu_net(be, P.BF16_TC, cfg.WIDE_DIMS, cfg.WIDE_ACTS, Ws, bs)
+    lg = net.trainStep(x, t, 1e-3, zn.Loss.mse)
+    print(f"\nconfig3 step bf16 at full width, {B} rows: loss {lg:.6f} emulation {el:.6f}")
+    assert abs(lg - el) <= 1e-4 * el
+    assert net.lastClip()[1] == 1.0                      # MSE gradients over B*4096 elements: norm << 1, no clipping
+    for i in range(4):
+        gW, gb = net.getGrads(i)
+        dW, db = rel_l2(gW, eW[i]), rel_l2(gb, eb[i])
+        print(f"  layer {i}: gW rel_l2 {dW:.3e}  gb rel_l2 {db:.3e}")
+        assert dW <= 5e-3 and db <= 5e-3, (i, dW, db)
+    # the SGD update itself, on the layer whose gradient is largest: w - lr * g with fp32 master weights
+    W3, _ = net.getWeights(3)
+    assert rel_l2(W3 - Ws[3], -1e-3 * eW[3]) <= 5e-3
+    net.deinit()

@@ -126,3 +126,154 @@ def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name,
             assert np.abs(r0[f"W{i}"] - onet.get_params(i)[0]).max() <= 2.2 * STEPS * LR
         else:
             assert rel_l2(r0[f"W{i}"], onet.get_params(i)[0]) <= tol
+
+
+def _leaving_rank(rank, world, uid_path, out_dir):
+    """Rank 1 leaves after two steps, between steps, with nothing of its own in flight; rank 0 then starts a third
+    step whose first all-reduce can never complete and must get ZN_ERR_NCCL from the deadline, not a hang."""
+    import time
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import zigneuron_b200 as zn
+    prec = zn.Precision.FP32_SIMT
+    x, t, Ws, bs = _data("mse")
+    be = zn.Backend(rank, prec)
+    if rank == 0:
+        uid = zn.Backend.dp_unique_id()
+        with open(uid_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(uid_path + ".tmp", uid_path)
+    else:
+        for _ in range(600):
+            if os.path.exists(uid_path):
+                break
+            time.sleep(0.05)
+        uid = open(uid_path, "rb").read()
+    be.dp_init(rank, world, uid)
+    be.dp_set_timeout_ms(3000)
+    net = _build(zn, be, prec, Ws, bs, False)
+    net.setDataParallel(B)
+    lo, hi = zn.Backend.distributeWorkload(B, world, rank)
+    for _ in range(2):
+        net.trainStep(x[lo:hi], t[lo:hi], LR, zn.Loss.mse)
+    be.endCommandBatch()                       # every lane of this rank is idle
+    gone = os.path.join(out_dir, "rank1_gone")
+    if rank == 1:
+        net.deinit()
+        be.deinit()
+        open(gone, "w").close()
+        return
+    for _ in range(1200):                      # the survivor learns nothing on the host: it just takes the next step
+        if os.path.exists(gone):
+            break
+        time.sleep(0.05)
+    result = {}
+    t0 = time.perf_counter()
+    try:
+        net.trainStep(x[lo:hi], t[lo:hi], LR, zn.Loss.mse)
+        result["first"] = 0
+    except zn.ZnError as e:
+        result["first"], result["text"] = e.status, str(e)
+    result["seconds"] = time.perf_counter() - t0
+    try:
+        net.trainStep(x[lo:hi], t[lo:hi], LR, zn.Loss.mse)
+        result["second"] = 0
+    except zn.ZnError as e:
+        result["second"] = e.status
+    np.savez(os.path.join(out_dir, "survivor.npz"), first=result["first"], second=result["second"],
+             seconds=result["seconds"], text=result.get("text", ""))
+    net.deinit()
+    be.deinit()
+
+
+def test_survivor_of_a_lost_rank_gets_an_error_not_a_hang(tmp_path):
+    import zigneuron_b200 as zn
+    if zn.Backend.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_leaving_rank, args=(2, str(tmp_path / "uid"), str(tmp_path)), nprocs=2, join=True)
+    r = np.load(tmp_path / "survivor.npz")
+    assert int(r["first"]) == 10, str(r["text"])          # ZN_ERR_NCCL
+    assert "aborted" in str(r["text"])
+    assert 2.5 <= float(r["seconds"]) <= 20.0               # the 3 s deadline, not the 120 s default
+    assert int(r["second"]) == 10                            # the communicator stays refused until re-initialised
+
+
+# ---- config 4 at full width: 4096-8192-8192-8192-4096, bf16, Adam, global batch 2 x 1024 -------------------------
+
+WIDE_STEPS, WIDE_ROWS, WIDE_STRIDE = 2, 2048, 4099
+
+
+def _wide_setup(zn, be):
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import configs as cfg
+    net = zn.Network(be, zn.Precision.BF16_TC)
+    for i, ((a, b), act) in enumerate(zip(cfg.WIDE_DIMS, cfg.WIDE_ACTS)):
+        net.addDense(a, b, act)
+        net.setWeights(i, cfg.wide_layer_weights(i, seed=3), np.zeros(b, np.float32))
+    net.setOptimizer(zn.Adam(beta1=0.9, beta2=0.999, eps=1e-8))
+    x, t = cfg.wide_rows(WIDE_ROWS, seed=3)
+    return net, x, t
+
+
+def _wide_summary(net, losses):
+    import hashlib
+    out = {"losses": np.array(losses, np.float32)}
+    for i in range(4):
+        W, b = net.getWeights(i)
+        gW, gb = net.getGrads(i)
+        out[f"hash{i}"] = np.frombuffer(hashlib.sha256(W.tobytes() + b.tobytes()).digest(), np.uint8)
+        out[f"W{i}"], out[f"gW{i}"], out[f"gb{i}"] = W.ravel()[::WIDE_STRIDE].copy(), gW.ravel()[::WIDE_STRIDE].copy(), gb
+    return out
+
+
+def _wide_rank(rank, world, uid_path, out_dir):
+    import time
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import zigneuron_b200 as zn
+    be = zn.Backend(rank, zn.Precision.BF16_TC)
+    if rank == 0:
+        uid = zn.Backend.dp_unique_id()
+        with open(uid_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(uid_path + ".tmp", uid_path)
+    else:
+        for _ in range(1200):
+            if os.path.exists(uid_path):
+                break
+            time.sleep(0.05)
+        uid = open(uid_path, "rb").read()
+    be.dp_init(rank, world, uid)
+    net, x, t = _wide_setup(zn, be)
+    net.setDataParallel(WIDE_ROWS)
+    lo, hi = zn.Backend.distributeWorkload(WIDE_ROWS, world, rank)
+    losses = [net.trainStep(np.ascontiguousarray(x[lo:hi]), np.ascontiguousarray(t[lo:hi]), 1e-3, zn.Loss.mse)
+              for _ in range(WIDE_STEPS)]
+    np.savez(os.path.join(out_dir, f"wide{rank}.npz"), **_wide_summary(net, losses))
+    net.deinit()          # between steps, nothing in flight
+    be.deinit()
+
+
+def test_two_gpus_at_full_width_match_one_gpu(tmp_path):
+    """Config 4's network at its stated width on two ranks of 1024 rows each: both ranks end bit-identical, and
+    losses, summed gradients and updated weights agree with one GPU taking all 2048 rows."""
+    import zigneuron_b200 as zn
+    if zn.Backend.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from util import rel_l2
+    mp.spawn(_wide_rank, args=(2, str(tmp_path / "uid"), str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "wide0.npz"), np.load(tmp_path / "wide1.npz")
+    assert np.array_equal(r0["losses"], r1["losses"])
+    for i in range(4):
+        assert np.array_equal(r0[f"hash{i}"], r1[f"hash{i}"]), f"layer {i} differs between the ranks"
+    be = zn.Backend(0, zn.Precision.BF16_TC)
+    net, x, t = _wide_setup(zn, be)
+    one = _wide_summary(net, [net.trainStep(x, t, 1e-3, zn.Loss.mse) for _ in range(WIDE_STEPS)])
+    print(f"\nconfig4 full width, 2 ranks x 1024 rows: losses {r0['losses']} one GPU {one['losses']}")
+    assert np.allclose(r0["losses"], one["losses"], rtol=1e-4)
+    for i in range(4):
+        dg, db, dw = rel_l2(r0[f"gW{i}"], one[f"gW{i}"]), rel_l2(r0[f"gb{i}"], one[f"gb{i}"]), rel_l2(r0[f"W{i}"], one[f"W{i}"])
+        print(f"  layer {i}: gW {dg:.3e} gb {db:.3e} W {dw:.3e}")
+        assert dg <= 2e-2 and db <= 2e-2 and dw <= 2e-2
+    net.deinit()
+    be.deinit()

@@ -450,3 +450,26 @@ def test_resume_with_optimizer_state(be, tmp_path, opt, prec):
         b.loadOptimizer(znn)                     # wrong magic
     for n in (a, b, c, other):
         n.deinit()
+
+
+@pytest.mark.parametrize("act,scale_of", [("relu", lambda i, o: np.sqrt(2.0 / i)), ("leaky_relu", lambda i, o: np.sqrt(2.0 / i)),
+                                          ("linear", lambda i, o: np.sqrt(1.0 / i)), ("sigmoid", lambda i, o: np.sqrt(2.0 / (i + o))),
+                                          ("tanh", lambda i, o: np.sqrt(2.0 / (i + o))), ("softmax", lambda i, o: np.sqrt(2.0 / (i + o))),
+                                          ("gelu", lambda i, o: np.sqrt(2.0 / (i + o))), ("elu", lambda i, o: np.sqrt(2.0 / (i + o)))])
+def test_add_dense_initial_distribution(be, act, scale_of):
+    """Dense.init (src/layer.zig:326-339): W ~ U(-1,1) * scale(act), b = 0.  The values come from another
+    generator than Zig's, so the DISTRIBUTION is what is checked: support, mean, variance, and that two layers
+    of one network do not repeat each other (the reference seeds each layer from a counter)."""
+    n_in, n_out = 300, 200
+    net = zn.Network(be, P.FP32_SIMT)
+    net.addDense(n_in, n_out, act)
+    net.addDense(n_out, n_in, act)
+    W, b = net.getWeights(0)
+    W2, _ = net.getWeights(1)
+    scale = scale_of(n_in, n_out)
+    assert W.shape == (n_in, n_out) and not b.any()
+    assert np.abs(W).max() <= scale * (1 + 1e-6) and np.abs(W).max() >= 0.999 * scale
+    assert abs(W.mean()) <= 4 * scale / np.sqrt(3 * W.size)              # 4 sigma of the mean of 60,000 draws
+    assert abs(W.var() - scale ** 2 / 3) <= 0.03 * scale ** 2 / 3          # U(-s, s) has variance s^2 / 3
+    assert abs(np.corrcoef(W.ravel(), W2.T.ravel()[:W.size])[0, 1]) < 0.02
+    net.deinit()

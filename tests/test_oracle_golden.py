@@ -304,3 +304,58 @@ def test_per_sample_train_is_sequence_of_single_steps():
     losses = [[b.train_step(x[s], t[s], 1, 0.01, zo.MSE) for s in range(4)] for _ in range(2)]
     assert np.allclose(ep, [np.float32(sum(np.float32(v) for v in l)) / 4 for l in losses], rtol=1e-6)
     assert np.array_equal(a.get_params(0)[0], b.get_params(0)[0])
+
+
+# ---- the oracle's curves on configurations 1 and 2 (tests/golden/config_curves.json) ---------------------------
+
+def _curves():
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import configs as cfg
+    return cfg, json.load(open(os.path.join(os.path.dirname(__file__), "golden", "config_curves.json")))
+
+
+def _oracle_net(dims, acts, Ws, bs, adam):
+    net = zo.Net()
+    for i, ((a, b), act) in enumerate(zip(dims, acts)):
+        net.add_dense(a, b, zo.RELU if act == "relu" else zo.LINEAR)
+        net.set_params(i, Ws[i], bs[i])
+        if adam:
+            net.set_adam(i)
+    return net
+
+
+def test_config1_curves_are_the_oracles():
+    """The committed 1000-step and 20-epoch curves of configuration 1 are what the oracle computes today, bit for bit."""
+    cfg, curves = _curves()
+    x, t, Ws, bs = cfg.iris_config()
+    net = _oracle_net(cfg.IRIS_DIMS, cfg.IRIS_ACTS, Ws, bs, False)
+    losses = [net.train_step(x, t, 150, 0.005, zo.CE_LOGITS) for _ in range(1000)]
+    want = curves["config1"]["full_batch"]
+    assert np.array_equal(np.array(losses, np.float32), np.array(want["loss"], np.float32))
+    for i in range(3):
+        assert np.array_equal(net.get_params(i)[0].ravel(), np.array(want["weights"][i]["w"], np.float32))
+    assert losses[-1] < 0.05 * losses[0]
+    net = _oracle_net(cfg.IRIS_DIMS, cfg.IRIS_ACTS, Ws, bs, False)
+    epoch = net.train(x, t, 20, 0.005, zo.CE_LOGITS)
+    assert np.array_equal(np.asarray(epoch, np.float32), np.array(curves["config1"]["per_sample"]["epoch_loss"], np.float32))
+
+
+def test_config2_curve_starts_as_the_oracle_does():
+    """Configuration 2 at its stated batch of 1024 costs the oracle seconds per step, so only the first two of the
+    100 committed steps are recomputed here: loss, gradient norm, clip factor and the weight samples, bit for bit."""
+    cfg, curves = _curves()
+    x, t, Ws, bs = cfg.mlp784_config()
+    net = _oracle_net(cfg.MLP784_DIMS, cfg.MLP784_ACTS, Ws, bs, True)
+    want = curves["config2"]
+    assert len(want["loss"]) == 100 and want["loss"][-1] < 0.2 * want["loss"][0]
+    for step in (1, 2):
+        loss = net.train_step(x, t, 1024, 1e-3, zo.CE_LOGITS)
+        norm, factor = net.last_clip()
+        assert np.float32(loss) == np.float32(want["loss"][step - 1])
+        assert np.float32(norm) == np.float32(want["norm"][step - 1]) and np.float32(factor) == np.float32(want["factor"][step - 1])
+        for i in range(3):
+            W, b = net.get_params(i)
+            snap = want["snapshots"][str(step)][i]
+            assert np.array_equal(W.ravel()[cfg.snapshot_indices(W.size)], np.array(snap["w"], np.float32))
+            assert np.array_equal(b[:10], np.array(snap["b"], np.float32))

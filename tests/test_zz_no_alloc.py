@@ -35,6 +35,30 @@ def test_noalloc_bias_accumulation_matches_regular_entry_point():
     be.deinit()
 
 
+def test_noalloc_follows_the_exact_mode_of_the_context():
+    """On a FP32_EXACT context the regular entry point adds each column's rows in ascending order (the reference's
+    cpuAccumulateBias); the no-allocation entry point must do the same, bit for bit, on two calls in a row."""
+    be = zn.Backend(0, zn.Precision.FP32_EXACT)
+    rng = np.random.default_rng(22)
+    for rows, cols in [(1500, 257), (65, 1030)]:
+        g = rng.standard_normal((rows, cols)).astype(np.float32)
+        gb0 = rng.standard_normal(cols).astype(np.float32)
+        dg = be.tensor(g)
+        want_t, got_t = be.tensor(gb0), be.tensor(gb0)
+        be.accumulateBias(want_t, dg)
+        be.accumulateBiasNoAlloc(got_t, dg)
+        be.endCommandBatch()
+        want, got = want_t.numpy(), got_t.numpy()
+        seq = gb0.copy()
+        for r in range(rows):                       # the reference's order: gb[c] += g[r][c], r ascending
+            seq += g[r]
+        assert np.array_equal(want, seq), (rows, cols)
+        assert np.array_equal(got, want), (rows, cols)
+        for t in (dg, want_t, got_t):
+            t.free()
+    be.deinit()
+
+
 def test_noalloc_rejects_what_does_not_fit_and_host_pointers():
     be = zn.Backend(0)
     cols = 1_100_000                                # one row: 1 split x 1.1e6 columns > 1,048,576 floats of scratch

@@ -100,6 +100,10 @@ SIGNATURES = {
     "zn_dp_destroy": (i32, [vp]),
     "zn_net_set_data_parallel": (i32, [vp, sz]),
     "zn_net_set_update_sharding": (i32, [vp, i32]),
+    "zn_dp_set_timeout_ms": (i32, [vp, C.c_int64]),
+    "zn_wait_poll": (i32, [vp, vp, vp, C.c_int64, C.POINTER(i32)]),
+    "zn_debug_bounded_wait_probe": (i32, [vp, C.c_int64]),
+    "zn_debug_set_device_status": (i32, [vp, i32]),
     "zn_profile_enable": (i32, [vp, i32]),
     "zn_profile_reset": (i32, [vp]),
     "zn_profile_get": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),

@@ -264,6 +264,21 @@ class Backend:
     def dp_init(self, rank, world, unique_id):
         self._ck(lib.zn_dp_init(self.handle, rank, world, unique_id))
 
+    def dp_set_timeout_ms(self, ms):
+        """Deadline of every host wait that may sit behind a collective; past it the communicator is aborted
+        and the call fails with ZN_ERR_NCCL."""
+        self._ck(lib.zn_dp_set_timeout_ms(self.handle, int(ms)))
+
+    def dp_destroy(self):
+        self._ck(lib.zn_dp_destroy(self.handle))
+
+    # ---- failure-path probes
+    def debug_bounded_wait_probe(self, limit_cycles):
+        self._ck(lib.zn_debug_bounded_wait_probe(self.handle, int(limit_cycles)))
+
+    def debug_set_device_status(self, code):
+        self._ck(lib.zn_debug_set_device_status(self.handle, int(code)))
+
     @staticmethod
     def distributeWorkload(total, parts, index):
         """MultiCudaContext.distributeWorkload(.round_robin), src/cuda_multi_gpu.zig:247-265."""

@@ -15,7 +15,10 @@ OBJ = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "libzn_b200.so")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+# ZN_DIAG=1 in the environment of the build adds -DZN_DIAG: the timing-only switches that give wrong results
+# (a step without its gradient exchange, overridden descriptor strides) exist in such builds only.
 FLAGS = [
+    *(["-DZN_DIAG"] if os.environ.get("ZN_DIAG") else []),
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "-I", os.path.join(ROOT, "include"), "-I", CSRC,
@@ -35,7 +38,10 @@ def _stale(target, deps):
 
 def _compile(src, force):
     obj = os.path.join(OBJ, src[:-3] + ".o")
-    deps = [os.path.join(CSRC, src), os.path.join(CSRC, "zn_internal.h"), os.path.join(ROOT, "include", "zn_b200.h")]
+    # every header of the package is a dependency of every object (an edited activation formula in zn_act.cuh
+    # must rebuild both GEMM families and the row-wise kernels)
+    headers = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".h", ".cuh"))]
+    deps = [os.path.join(CSRC, src), *headers, os.path.join(ROOT, "include", "zn_b200.h")]
     if force or _stale(obj, deps):
         subprocess.check_call([NVCC, *FLAGS, "-c", os.path.join(CSRC, src), "-o", obj])
     return obj

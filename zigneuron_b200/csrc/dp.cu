@@ -11,9 +11,10 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
 
-#include <cstdlib>
 #include "zn_internal.h"
 
 namespace {
@@ -72,15 +73,128 @@ NcclApi &api() {
 struct zn_dp_state {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
+    int64_t timeout_ms = 120000;   // deadline of every host wait that may sit behind a collective
+    bool failed = false;           // the communicator reported an error or missed the deadline and was aborted
 };
 
 bool zn_dp_active(const zn_ctx *ctx) { return ctx && ctx->dp && ctx->dp->world > 1; }
 
+// ---- failure detection ---------------------------------------------------------------------------
+//
+// A rank that dies or falls out of step leaves the others inside a collective that never completes.  Every
+// host wait that can sit behind a collective therefore polls instead of blocking: is the work done, has the
+// communicator reported an asynchronous error, has the deadline passed.  The loop itself knows nothing of
+// CUDA or NCCL (it takes the three questions as callbacks), so its decisions can be tested on a machine
+// without either.
+extern "C" int32_t zn_wait_poll(zn_poll_ready_fn ready, zn_poll_error_fn comm_error, void *user, int64_t deadline_ms,
+                                int32_t *comm_error_out) {
+    using clock = std::chrono::steady_clock;
+    if (comm_error_out) *comm_error_out = 0;
+    if (!ready) return ZN_WAIT_QUERY_FAILED;
+    const clock::time_point t0 = clock::now();
+    clock::time_point next_check = t0;
+    for (;;) {
+        const int r = ready(user);
+        if (r > 0) return ZN_WAIT_READY;
+        if (r < 0) return ZN_WAIT_QUERY_FAILED;
+        const clock::time_point now = clock::now();
+        if (now < next_check) continue;                      // spin on `ready`; the other questions once a millisecond
+        next_check = now + std::chrono::milliseconds(1);
+        if (comm_error) {
+            const int e = comm_error(user);
+            if (e != 0) {
+                if (comm_error_out) *comm_error_out = e;
+                return ZN_WAIT_COMM_ERROR;
+            }
+        }
+        if (deadline_ms >= 0 && now - t0 > std::chrono::milliseconds(deadline_ms)) return ZN_WAIT_DEADLINE;
+    }
+}
+
+namespace {
+
+struct WaitTarget { zn_ctx *ctx; cudaEvent_t event; cudaStream_t stream; cudaError_t cuda_error; };
+
+int target_ready(void *user) {
+    WaitTarget *w = static_cast<WaitTarget *>(user);
+    const cudaError_t e = w->event ? cudaEventQuery(w->event) : cudaStreamQuery(w->stream);
+    if (e == cudaSuccess) return 1;
+    if (e == cudaErrorNotReady) { cudaGetLastError(); return 0; }
+    w->cuda_error = e;
+    return -1;
+}
+
+int target_comm_error(void *user) {
+    WaitTarget *w = static_cast<WaitTarget *>(user);
+    zn_dp_state *dp = w->ctx->dp;
+    if (!dp || !dp->comm || !api().CommGetAsyncError) return 0;
+    ncclResult_t async = ncclSuccess;
+    const ncclResult_t r = api().CommGetAsyncError(dp->comm, &async);
+    if (r != ncclSuccess) return (int)r;
+    return (async == ncclSuccess || async == ncclInProgress) ? 0 : (int)async;
+}
+
+// Ends the communicator: its kernels in flight give up, the streams drain, later collectives are refused.
+void abort_comm(zn_ctx *ctx) {
+    zn_dp_state *dp = ctx->dp;
+    if (!dp || !dp->comm) return;
+    if (api().CommAbort) api().CommAbort(dp->comm);
+    dp->comm = nullptr;
+    dp->failed = true;
+}
+
+zn_status wait_target(zn_ctx *ctx, WaitTarget &w, const char *what) {
+    int32_t comm_err = 0;
+    const int32_t r = zn_wait_poll(target_ready, target_comm_error, &w, ctx->dp->timeout_ms, &comm_err);
+    if (r == ZN_WAIT_READY) return ZN_OK;
+    if (r == ZN_WAIT_QUERY_FAILED) return zn_cuda_status(ctx, w.cuda_error, what);
+    abort_comm(ctx);
+    // what the aborted collective held back can finish now; give it a bounded time to do so
+    WaitTarget drain = w;
+    zn_wait_poll(target_ready, nullptr, &drain, 5000, nullptr);
+    if (r == ZN_WAIT_COMM_ERROR)
+        return zn_fail(ctx, ZN_ERR_NCCL, "%s: the communicator reported '%s'; it has been aborted", what,
+                       api().GetErrorString ? api().GetErrorString((ncclResult_t)comm_err) : "an error");
+    return zn_fail(ctx, ZN_ERR_NCCL, "%s: no completion within %lld ms (a peer rank is missing or stuck); the communicator "
+                   "has been aborted", what, (long long)ctx->dp->timeout_ms);
+}
+
+}   // namespace
+
+// Host waits of a data-parallel context.  Without a live communicator they are the plain blocking calls.
+zn_status zn_wait_event(zn_ctx *ctx, cudaEvent_t ev) {
+    if (!zn_dp_active(ctx) || !ctx->dp->comm) { ZN_CUDA(ctx, cudaEventSynchronize(ev)); return ZN_OK; }
+    WaitTarget w{ctx, ev, nullptr, cudaSuccess};
+    return wait_target(ctx, w, "waiting for a training step");
+}
+
+zn_status zn_wait_stream(zn_ctx *ctx, cudaStream_t s) {
+    if (!zn_dp_active(ctx) || !ctx->dp->comm) { ZN_CUDA(ctx, cudaStreamSynchronize(s)); return ZN_OK; }
+    WaitTarget w{ctx, nullptr, s, cudaSuccess};
+    return wait_target(ctx, w, "waiting for a stream");
+}
+
+static zn_status comm_gone(zn_ctx *ctx) {
+    return zn_fail(ctx, ZN_ERR_NCCL, "the communicator was aborted after an error or a missed deadline; "
+                                     "call zn_dp_destroy and zn_dp_init to rejoin");
+}
+
+extern "C" zn_status zn_dp_set_timeout_ms(zn_ctx *ctx, int64_t ms) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!ctx->dp) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "call zn_dp_init first");
+    if (ms <= 0) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "dp_set_timeout_ms: %lld is not a positive time", (long long)ms);
+    ctx->dp->timeout_ms = ms;
+    return ZN_OK;
+}
+
 zn_status zn_dp_allreduce(zn_ctx *ctx, float *buf, size_t count, cudaStream_t stream) {
     if (!zn_dp_active(ctx)) return ZN_OK;
-    // diagnostic: time a step without its exchange (the ranks then diverge; never for results)
+    if (!ctx->dp->comm) return comm_gone(ctx);
+#ifdef ZN_DIAG
+    // diagnostic builds only (-DZN_DIAG): time a step without its exchange (the ranks then diverge; never for results)
     static const bool skip = getenv("ZN_DP_SKIP_ALLREDUCE") != nullptr;
     if (skip) return ZN_OK;
+#endif
     ncclResult_t r = api().AllReduce(buf, buf, count, ncclFloat32, ncclSum, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllReduce: %s", api().GetErrorString(r));
     return ZN_OK;
@@ -92,6 +206,7 @@ bool zn_dp_can_shard(const zn_ctx *ctx) { return zn_dp_active(ctx) && api().Redu
 
 zn_status zn_dp_allreduce_f64(zn_ctx *ctx, double *buf, size_t count, cudaStream_t stream) {
     if (!zn_dp_active(ctx)) return ZN_OK;
+    if (!ctx->dp->comm) return comm_gone(ctx);
     ncclResult_t r = api().AllReduce(buf, buf, count, ncclFloat64, ncclSum, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllReduce(f64): %s", api().GetErrorString(r));
     return ZN_OK;
@@ -101,6 +216,7 @@ zn_status zn_dp_allreduce_f64(zn_ctx *ctx, double *buf, size_t count, cudaStream
 // [r * shard, (r + 1) * shard); the other pieces keep this rank's partial values.
 zn_status zn_dp_reduce_scatter(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream) {
     if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "reduce-scatter needs an initialised communicator");
+    if (!ctx->dp->comm) return comm_gone(ctx);
     ncclResult_t r = api().ReduceScatter(buf, buf + (size_t)ctx->dp->rank * shard, shard, ncclFloat32, ncclSum, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclReduceScatter: %s", api().GetErrorString(r));
     return ZN_OK;
@@ -109,6 +225,7 @@ zn_status zn_dp_reduce_scatter(zn_ctx *ctx, float *buf, size_t shard, cudaStream
 // In place: every rank contributes its own piece [r * shard, (r + 1) * shard) and ends with all of them.
 zn_status zn_dp_all_gather(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream) {
     if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "all-gather needs an initialised communicator");
+    if (!ctx->dp->comm) return comm_gone(ctx);
     ncclResult_t r = api().AllGather(buf + (size_t)ctx->dp->rank * shard, buf, shard, ncclFloat32, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllGather: %s", api().GetErrorString(r));
     return ZN_OK;
@@ -123,7 +240,7 @@ zn_status zn_dp_alloc_registered(zn_ctx *ctx, size_t bytes, void **ptr_out, void
     *ptr_out = nullptr;
     *handle_out = nullptr;
     static const bool off = getenv("ZN_DP_NO_REGISTER") != nullptr;
-    if (off || !zn_dp_active(ctx) || !api().MemAlloc || !api().MemFree || !api().CommRegister || !api().CommDeregister)
+    if (off || !zn_dp_active(ctx) || !ctx->dp->comm || !api().MemAlloc || !api().MemFree || !api().CommRegister || !api().CommDeregister)
         return ZN_ERR_NOT_AVAILABLE;
     void *p = nullptr, *h = nullptr;
     if (api().MemAlloc(&p, bytes) != ncclSuccess || !p) { cudaGetLastError(); return ZN_ERR_NOT_AVAILABLE; }
@@ -174,6 +291,10 @@ extern "C" zn_status zn_dp_init(zn_ctx *ctx, int32_t rank, int32_t world, const 
             return zn_fail(ctx, ZN_ERR_NCCL, "ncclCommInitRank: %s", api().GetErrorString(r));
         }
     }
+    if (const char *e = getenv("ZN_DP_TIMEOUT_MS")) {
+        const long long v = atoll(e);
+        if (v > 0) st->timeout_ms = v;
+    }
     ctx->dp = st;
     return ZN_OK;
 }
@@ -182,8 +303,8 @@ extern "C" zn_status zn_dp_destroy(zn_ctx *ctx) {
     if (!ctx) return ZN_ERR_NOT_INITIALIZED;
     if (!ctx->dp) return ZN_OK;
     if (ctx->dp->comm) {
-        cudaStreamSynchronize(ctx->comm_stream);
-        api().CommDestroy(ctx->dp->comm);
+        zn_wait_stream(ctx, ctx->comm_stream);                 // may abort the communicator and clear the pointer
+        if (ctx->dp->comm) api().CommDestroy(ctx->dp->comm);
     }
     delete ctx->dp;
     ctx->dp = nullptr;

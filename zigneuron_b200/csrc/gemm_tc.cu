@@ -105,14 +105,14 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 }
 // Bounded wait.  Returns false when the CTA has been aborted or the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                          int code) {
+                                          int code, long long limit = WAIT_LIMIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 __threadfence_system();
@@ -425,7 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
         for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }   // MMA thread + 4 epilogue warps
-        if (blockIdx.x == 0) *p.next_counter = 0u;
+        if (blockIdx.x == 0 && p.dynamic_tiles) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -689,7 +689,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // tile-index ring: the leader's producer publishes into both CTAs; its `empty` side counts every reader
         // of the pair: leader MMA thread + 4 leader epilogue warps + peer producer + 4 peer epilogue warps
         for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 10); }
-        if (blockIdx.x == 0) *p.next_counter = 0u;
+        if (blockIdx.x == 0 && p.dynamic_tiles) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -859,6 +859,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
+// One CTA, one barrier that nothing arrives at: the wait runs out after `limit` cycles, the waiting thread raises
+// the abort flag and records code 99, and every thread leaves through the ordinary end of the kernel.
+__global__ void bounded_wait_probe_kernel(int *status, long long limit) {
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ int abort_flag_s;
+    const uint32_t bar = smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        abort_flag_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int *abort_flag = &abort_flag_s;
+    if (threadIdx.x == 0) mbar_wait(bar, 0u, abort_flag, status, 99, limit);
+    __syncthreads();
+}
+
 // ---- host side ----------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -915,6 +932,17 @@ zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int6
 
 }   // namespace
 
+extern "C" zn_status zn_debug_bounded_wait_probe(zn_ctx *ctx, int64_t limit_cycles) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (limit_cycles < 0 || limit_cycles > 2000000000LL)
+        return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "bounded_wait_probe: limit of %lld cycles outside 0..2e9", (long long)limit_cycles);
+    ZN_CUDA(ctx, cudaSetDevice(ctx->device));
+    ctx->launches += 1;
+    bounded_wait_probe_kernel<<<1, 64, 0, ctx->stream>>>(ctx->status_dev, (long long)limit_cycles);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
 zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, bool a_mn, const void *b, int64_t ldb,
                      bool b_mn, int64_t m, int64_t n, int64_t k, const zn_epilogue &e) {
     if (!a || !b || (!e.out_f32 && !e.out_t)) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "gemm: null operand");
@@ -958,10 +986,12 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
               ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     p.mn_lbo = (uint32_t)(bk * ROW_BYTES);
     p.mn_sbo = tf32 ? 512 : 1024;
-    if (const char *dbg = getenv("ZN_TC_MN_STRIDES")) {   // diagnostic override "lbo,sbo" in bytes
+#ifdef ZN_DIAG
+    if (const char *dbg = getenv("ZN_TC_MN_STRIDES")) {   // diagnostic builds only (-DZN_DIAG): override "lbo,sbo" in bytes
         unsigned l = 0, sb = 0;
         if (sscanf(dbg, "%u,%u", &l, &sb) == 2) { p.mn_lbo = l; p.mn_sbo = sb; }
     }
+#endif
     p.bias = e.bias; p.act = e.act; p.mask = e.mask; p.ld_mask = e.ld_mask;
     p.out_f32 = e.out_f32; p.ld_out_f32 = e.ld_out_f32; p.out_t = e.out_t; p.ld_out_t = e.ld_out_t;
     p.accumulate = e.accumulate;
@@ -970,11 +1000,20 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         ZN_CUDA(ctx, cudaMalloc((void **)&ctx->tile_counters, 2 * sizeof(unsigned int)));
         ZN_CUDA(ctx, cudaMemsetAsync(ctx->tile_counters, 0, 2 * sizeof(unsigned int), ctx->stream));
     }
+    // The two work counters are used in turn by successive launches ON THE MAIN LANE (each clears the one its
+    // successor will use).  A GEMM issued on any other lane would race with them, so it walks its tiles in the
+    // fixed round-robin order and touches neither counter.
+    static const int dyn = getenv("ZN_TC_STATIC_TILES") ? 0 : 1;
+    p.dynamic_tiles = (dyn && ctx->lane == ZN_LANE_MAIN) ? 1 : 0;
     p.tile_counter = ctx->tile_counters + (ctx->tile_counter_turn & 1);
     p.next_counter = ctx->tile_counters + ((ctx->tile_counter_turn + 1) & 1);
-    ctx->tile_counter_turn += 1;
-    static const int dyn = getenv("ZN_TC_STATIC_TILES") ? 0 : 1;
-    p.dynamic_tiles = dyn;
+    if (p.dynamic_tiles) ctx->tile_counter_turn += 1;
+    // a launch that fails never cleared its successor's counter: start both from zero again
+    auto launch_failed = [&](cudaError_t e, const char *what) {
+        cudaMemsetAsync(ctx->tile_counters, 0, 2 * sizeof(unsigned int), ctx->stream);
+        ctx->tile_counter_turn = 0;
+        return zn_cuda_status(ctx, e, what);
+    };
 
     zn_launch_scope scope(ctx, ZN_PROF_GEMM_TC, 2.0 * m * n * k,
                           (double)es * (m * k + k * n) + (e.out_f32 ? 4.0 : (double)es) * m * n);
@@ -1016,7 +1055,8 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        ZN_CUDA(ctx, cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p));
+        const cudaError_t le = cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p);
+        if (le != cudaSuccess) return launch_failed(le, "launch of the two-CTA tensor-core GEMM");
         return ZN_OK;
     }
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
@@ -1024,6 +1064,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
     else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
-    ZN_CUDA(ctx, cudaGetLastError());
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return launch_failed(le, "launch of the tensor-core GEMM");
     return ZN_OK;
 }

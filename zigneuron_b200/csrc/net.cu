@@ -796,7 +796,7 @@ extern "C" zn_status zn_net_train_step(zn_net *n, const float *input, const floa
     ZN_TRY(step_dev(n, x_dev, t_dev, rows, lr, (int)loss, s.loss_host, s.done));
     // The loss and the norm are final once every layer is reduced; the parameter updates keep running on
     // the optimizer lane and the next step (or any getter) orders itself after them.
-    ZN_CUDA(ctx, cudaEventSynchronize(s.done));
+    ZN_TRY(zn_wait_event(ctx, s.done));
     n->last_norm = s.loss_host[1];
     n->last_factor = s.loss_host[2];
     if (loss_out) *loss_out = loss_from_sum(n, s.loss_host[0], rows, (int)loss);
@@ -833,7 +833,7 @@ extern "C" zn_status zn_net_wait_step(zn_net *n, float *loss_out) {
     zn_ctx *ctx = n->ctx;
     if (n->inflight == 0) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "no step in flight");
     Slot &s = n->slots[n->head];
-    ZN_CUDA(ctx, cudaEventSynchronize(s.done));
+    ZN_TRY(zn_wait_event(ctx, s.done));
     s.busy = false;
     n->head ^= 1;
     n->inflight -= 1;

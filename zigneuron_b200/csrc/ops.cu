@@ -29,7 +29,11 @@ struct Operand {
 
 zn_status resolve(zn_ctx *ctx, int slot, const float *p, size_t count, bool copy_in, Operand *out) {
     out->count = count;
-    if (zn_is_device_ptr(p)) {
+    const int owner = zn_ptr_device(p);
+    if (owner >= 0) {
+        // a kernel of this context cannot be handed another GPU's memory (a TMA descriptor over it must not exist)
+        if (owner != ctx->device)
+            return zn_fail(ctx, ZN_ERR_INVALID_DEVICE, "operand lives on device %d, the context on device %d", owner, ctx->device);
         out->dev = const_cast<float *>(p);
         return ZN_OK;
     }

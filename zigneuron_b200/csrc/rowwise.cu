@@ -619,25 +619,25 @@ constexpr size_t ZN_NOALLOC_SCRATCH_FLOATS = (size_t)1 << 20;
 static __device__ __align__(256) float zn_noalloc_scratch[ZN_NOALLOC_SCRATCH_FLOATS];
 
 // In host code `zn_noalloc_scratch` is only a stand-in for the symbol, not an address a kernel can use; the
-// device address is looked up once per device, with that device current, and cached here.
+// device address is looked up once per device, with that device current, and cached here.  The cache is
+// atomic: two threads that meet in the first call on a device both look the address up and store the same value.
 static float *noalloc_scratch_address(zn_ctx *ctx, zn_status *status) {
-    static float *per_device[64] = {nullptr};
+    static std::atomic<float *> per_device[64];
     *status = ZN_OK;
     if (ctx->device < 0 || ctx->device >= 64) {
         *status = zn_fail(ctx, ZN_ERR_INVALID_DEVICE, "device index %d outside the supported range", ctx->device);
         return nullptr;
     }
-    if (!per_device[ctx->device]) {
-        float *p = nullptr;
-        cudaError_t e = cudaSetDevice(ctx->device);
-        if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&p, zn_noalloc_scratch);
+    float *p = per_device[ctx->device].load(std::memory_order_acquire);
+    if (!p) {
+        cudaError_t e = cudaGetSymbolAddress((void **)&p, zn_noalloc_scratch);   // the caller made ctx->device current
         if (e != cudaSuccess || !p) {
             *status = zn_cuda_status(ctx, e == cudaSuccess ? cudaErrorInvalidSymbol : e, "cudaGetSymbolAddress(zn_noalloc_scratch)");
             return nullptr;
         }
-        per_device[ctx->device] = p;
+        per_device[ctx->device].store(p, std::memory_order_release);
     }
-    return per_device[ctx->device];
+    return p;
 }
 
 extern "C" zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, size_t bias_len, const float *g,
@@ -650,7 +650,18 @@ extern "C" zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, s
     if (!zn_is_device_ptr(grad_bias) || !zn_is_device_ptr(g))
         return zn_fail(ctx, ZN_ERR_INVALID_VALUE,
                        "accumulate_bias_noalloc: operands must be device pointers (staging host memory would allocate)");
+    // every call, not only the first: the calling thread's current device may be another GPU
+    ZN_CUDA(ctx, cudaSetDevice(ctx->device));
+    prefer_gemm_compatible_carveout(ctx);
     const int64_t cols = (int64_t)bias_len, rows = (int64_t)(g_len / bias_len);
+    if (ctx->precision == ZN_FP32_EXACT) {
+        // The reference's order of additions (one running sum per column, rows ascending), as zn_accumulate_bias
+        // gives on such a context.  That kernel keeps its sum in a register: no scratch of any kind, no size limit.
+        ctx->launches += 1;
+        bias_reduce_exact_kernel<float><<<(unsigned)((cols + 127) / 128), 128, 0, ctx->stream>>>(g, cols, rows, cols, grad_bias, 1);
+        ZN_CUDA(ctx, cudaGetLastError());
+        return ZN_OK;
+    }
     // same split of the rows as zn_accumulate_bias, so both entry points add in the same order
     const int strip = 32 * 4;
     const int strips = (int)((cols + strip - 1) / strip);

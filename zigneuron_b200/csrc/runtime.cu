@@ -153,6 +153,13 @@ zn_status zn_check_device_status(zn_ctx *ctx) {
     return ZN_OK;
 }
 
+extern "C" zn_status zn_debug_set_device_status(zn_ctx *ctx, int32_t code) {
+    if (!ctx) return ZN_ERR_NOT_INITIALIZED;
+    if (!ctx->status_host) return zn_fail(ctx, ZN_ERR_NOT_INITIALIZED, "context has no status word");
+    *ctx->status_host = code;
+    return ZN_OK;
+}
+
 void zn_lane_switch(zn_ctx *ctx, int lane) {
     if (lane == ctx->lane) return;
     zn_ctx::lane_state &cur = ctx->lanes[ctx->lane];
@@ -170,7 +177,7 @@ zn_status zn_sync_all_lanes(zn_ctx *ctx) {
     zn_lane_switch(ctx, ZN_LANE_MAIN);
     for (int i = 0; i < 4; ++i) {
         cudaStream_t s = i == ZN_LANE_MAIN ? ctx->stream : ctx->lanes[i].stream;
-        if (s) ZN_CUDA(ctx, cudaStreamSynchronize(s));
+        if (s) ZN_TRY(zn_wait_stream(ctx, s));
     }
     return ZN_OK;
 }
@@ -205,6 +212,17 @@ bool zn_is_device_ptr(const void *p) {
         return false;
     }
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Device that owns a device pointer, or -1 for host memory and unknown addresses.
+int zn_ptr_device(const void *p) {
+    if (!p) return -1;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return (a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged) ? a.device : -1;
 }
 
 zn_status zn_scratch_reserve(zn_ctx *ctx, size_t floats) {
@@ -388,7 +406,7 @@ extern "C" zn_status zn_timer_stop(zn_ctx *ctx, float *ms_out) {
     if (!ctx->timer0 || !ms_out) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "timer not started or null output");
     ZN_TRY(zn_join_lanes_into_main(ctx));   // work still running on the other lanes belongs to the timed region
     ZN_CUDA(ctx, cudaEventRecord(ctx->timer1, ctx->stream));
-    ZN_CUDA(ctx, cudaEventSynchronize(ctx->timer1));
+    ZN_TRY(zn_wait_event(ctx, ctx->timer1));
     ZN_CUDA(ctx, cudaEventElapsedTime(ms_out, ctx->timer0, ctx->timer1));
     return zn_check_device_status(ctx);
 }

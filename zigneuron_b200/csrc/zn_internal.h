@@ -106,12 +106,17 @@ struct zn_lane_guard {                            // active lane for the lifetim
     zn_lane_guard(zn_ctx *c, int lane) : ctx(c), prev(c->lane) { zn_lane_switch(c, lane); }
     ~zn_lane_guard() { zn_lane_switch(ctx, prev); }
 };
+// Host waits.  On a data-parallel context they poll (work done? communicator error? deadline?) instead of
+// blocking, abort the communicator on an error or a missed deadline, and return ZN_ERR_NCCL (dp.cu).
+zn_status zn_wait_event(zn_ctx *ctx, cudaEvent_t ev);
+zn_status zn_wait_stream(zn_ctx *ctx, cudaStream_t s);
 zn_status zn_sync_all_lanes(zn_ctx *ctx);         // host waits for every lane
 zn_status zn_join_lanes_into_main(zn_ctx *ctx);   // the main stream waits (on the device) for the other lanes
 
 zn_status zn_scratch_reserve(zn_ctx *ctx, size_t floats);
 zn_status zn_check_device_status(zn_ctx *ctx);   // reads the pinned status word after a sync
 bool zn_is_device_ptr(const void *p);
+int zn_ptr_device(const void *p);                 // owning device of a device pointer, -1 for host memory
 
 // ---- kernels (each launcher enqueues on ctx->stream and returns) ------------------
 
