@@ -601,11 +601,13 @@ def run_other_config(args):
         dx, dt = be.tensor(x), be.tensor(t)
         losses = [net.trainStep(dx, dt, lr, loss, rows=B) for _ in range(args.warmup)]
         be.endCommandBatch()
+        launches0 = be.launch_count()
         be.timer_start()
         for _ in range(args.steps):
             losses.append(net.trainStep(dx, dt, lr, loss, rows=B))
         ms = be.timer_stop() / args.steps
         print(json.dumps({"workload": args.workload, "precision": pname, "batch": B, "ms_per_step": ms,
+                          "launches_per_step": (be.launch_count() - launches0) / args.steps,
                           "samples_per_s": B / (ms / 1e3), "tflops": flop / (ms / 1e3) / 1e12,
                           "loss_first": losses[0], "loss_last": losses[-1]}), flush=True)
         if args.trace:

@@ -16,7 +16,12 @@
  * Arithmetic that lives in Zig's standard library (std.math.exp, @log,
  * std.math.pow, @sqrt, std.math.tanh) is restated with libm expf/logf/powf/
  * sqrtf/tanhf; the difference is at most an ulp or two, inside every
- * tolerance the reference's own tests use.
+ * tolerance the reference's own tests use.  The exp and log of the softmax and
+ * cross-entropy paths are evaluated in double precision and rounded once
+ * (zo_exp1 / zo_log1): that is the correctly rounded float in all but isolated
+ * cases, a definition that does not move with the libm at hand, and one a GPU
+ * can reproduce bit for bit.  An ulp there matters: under Adam a one-ulp
+ * difference in a softmax sends a 100-step run down another path.
  *
  * Pinning: the known-answer values of the reference's unit tests
  * (tests/golden/reference_kat.json, transcribed from the files under src/test/unit)
@@ -28,6 +33,9 @@
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
+
+static inline float zo_exp1(float x) { return (float)exp((double)x); }
+static inline float zo_log1(float x) { return (float)log((double)x); }
 #include <string.h>
 
 #define ZO_API __attribute__((visibility("default")))
@@ -164,7 +172,7 @@ ZO_API void zo_softmax_forward(const float *in, float *out, size_t n) {
     float max_val = -INFINITY;
     for (size_t i = 0; i < n; ++i) if (in[i] > max_val) max_val = in[i];
     float sum = 0;
-    for (size_t i = 0; i < n; ++i) { out[i] = expf(in[i] - max_val); sum += out[i]; }
+    for (size_t i = 0; i < n; ++i) { out[i] = zo_exp1(in[i] - max_val); sum += out[i]; }
     if (sum > 0) { for (size_t i = 0; i < n; ++i) out[i] /= sum; }
     else { const float u = 1.0f / (float)n; for (size_t i = 0; i < n; ++i) out[i] = u; }
 }
@@ -211,8 +219,8 @@ ZO_API float zo_ce_logits_forward(const float *logits, const float *target, size
     float mx = logits[0];
     for (size_t i = 1; i < n; ++i) if (logits[i] > mx) mx = logits[i];
     float sum_exp = 0;
-    for (size_t i = 0; i < n; ++i) sum_exp += expf(logits[i] - mx);
-    const float lse = logf(sum_exp) + mx;
+    for (size_t i = 0; i < n; ++i) sum_exp += zo_exp1(logits[i] - mx);
+    const float lse = zo_log1(sum_exp) + mx;
     float loss = 0;
     for (size_t i = 0; i < n; ++i) if (target[i] > 0.5f) { loss = -(logits[i] - lse); break; }
     return loss;
@@ -224,7 +232,7 @@ ZO_API void zo_ce_logits_backward(const float *logits, const float *target, floa
     float mx = logits[0];
     for (size_t i = 1; i < n; ++i) if (logits[i] > mx) mx = logits[i];
     float sum_exp = 0;
-    for (size_t i = 0; i < n; ++i) { g[i] = expf(logits[i] - mx); sum_exp += g[i]; }
+    for (size_t i = 0; i < n; ++i) { g[i] = zo_exp1(logits[i] - mx); sum_exp += g[i]; }
     for (size_t i = 0; i < n; ++i) g[i] = (g[i] / sum_exp) - target[i];
 }
 
@@ -240,10 +248,10 @@ ZO_API float zo_ce_forward(const float *o, const float *t, size_t n) {
     for (size_t i = 0; i < n; ++i) {
         const float diff = o[i] - mx;
         const float cd = diff > 50 ? 50 : (diff < -50 ? -50 : diff);
-        lse += expf(cd);
+        lse += zo_exp1(cd);
     }
     if (!isfinite(lse) || lse <= 0) return 0;
-    lse = logf(lse) + mx;
+    lse = zo_log1(lse) + mx;
     float loss_sum = 0, count = 0;
     for (size_t i = 0; i < n; ++i)
         if (t[i] > 0.5f) { loss_sum += lse - o[i]; count += 1; }

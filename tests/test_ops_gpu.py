@@ -95,8 +95,10 @@ def test_gemm_accumulate(be, orient):
     assert_close(_gpu(be, orient, sa, sb, m, n, k, c=c0, acc=True), want, 2e-2)
 
 
+# Short main loops (K up to 1024 bf16 / 512 tf32 values) and single row tiles run the one-CTA kernel, the rest the
+# two-CTA kernel: the last three shapes have more than one row tile AND a long K in both precisions.
 TC_SHAPES = [(128, 256, 64), (256, 512, 256), (300, 200, 100), (130, 10, 256), (1024, 512, 784), (64, 2048, 1500),
-             (2048, 1024, 512)]
+             (2048, 1024, 512), (384, 320, 2304), (300, 520, 1100), (513, 260, 4100)]
 
 
 @pytest.mark.parametrize("prec", [P.BF16_TC, P.TF32_TC])
@@ -462,3 +464,49 @@ def test_argument_errors(be):
         be.addBias(np.zeros(5, np.float32), np.zeros(2, np.float32))
     with pytest.raises(zn.ZnError):
         be.matMul(None, a, a, 2, 2, 1)
+
+
+_FORCED_KERNEL_SNIPPET = r"""
+import sys
+import numpy as np
+sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+import zigneuron_b200 as zn
+from util import assert_close, round_bf16, trunc_tf32
+be = zn.Backend(0)
+rng = np.random.default_rng(11)
+for prec, rnd in ((zn.Precision.BF16_TC, round_bf16), (zn.Precision.TF32_TC, trunc_tf32)):
+    be.set_precision(prec)
+    for m, n, k in [(256, 512, 256), (300, 200, 100), (1024, 512, 784), (2048, 1024, 512), (300, 520, 1100), (513, 260, 96)]:
+        a, b = rnd(rng.standard_normal((m, k)).astype(np.float32)), rnd(rng.standard_normal((k, n)).astype(np.float32))
+        bias = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+        want = a.astype(np.float64) @ b.astype(np.float64)
+        c = np.zeros((m, n), np.float32)
+        be.matMul(a, b, c, m, n, k)
+        assert_close(c, want, 1e-5, f"NN {{prec.name}} {{(m, n, k)}}")
+        be.matMulTransposeB(a, np.ascontiguousarray(b.T), c, m, n, k)
+        assert_close(c, want, 1e-5, f"NT {{prec.name}} {{(m, n, k)}}")
+        be.matMulTransposeA(np.ascontiguousarray(a.T), b, c, m, n, k)
+        assert_close(c, want, 1e-5, f"TN {{prec.name}} {{(m, n, k)}}")
+        be.matMulBiasRelu(a, b, bias, c, m, n, k)
+        assert_close(c, np.maximum(want + bias, 0), 1e-5, f"bias+relu {{prec.name}} {{(m, n, k)}}")
+        c[:] = 1.0
+        be.matMul(a, b, c, m, n, k, accumulate=True)
+        assert_close(c, want + 1.0, 1e-5, f"accumulate {{prec.name}} {{(m, n, k)}}")
+print("forced-kernel checks ok")
+"""
+
+
+@pytest.mark.parametrize("env", [{"ZN_TC_PAIR": "2"}, {"ZN_TC_PAIR": "2", "ZN_TC_STAGED_STORE": "1"}, {"ZN_TC_PAIR": "0"}],
+                         ids=["two-CTA everywhere", "two-CTA with staged TMA stores", "one-CTA everywhere"])
+def test_each_tensor_core_kernel_on_shapes_the_default_routes_elsewhere(env):
+    """The library picks the one-CTA or the two-CTA kernel by shape, and the two-CTA kernel's shared-memory-staged
+    bulk-store epilogue is an option.  The choices are read once per process, so each forced combination runs in a
+    process of its own, over shapes (ragged edges included) that the default routing would send to the other kernel."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = _FORCED_KERNEL_SNIPPET.format(root=root, tests=os.path.join(root, "tests"))
+    r = subprocess.run([sys.executable, "-c", code], env={**os.environ, **env}, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "forced-kernel checks ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+

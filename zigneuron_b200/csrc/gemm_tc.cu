@@ -66,6 +66,11 @@ struct TcParams {
     // Each launch also clears the counter the NEXT launch on the stream will use.
     unsigned int *tile_counter, *next_counter;
     int dynamic_tiles;       // 0: plain round-robin over the grid (diagnostic)
+    // Output path of the two-CTA kernel: 0 = each thread stores its row straight to global memory; 1 / 2 = the
+    // epilogue warps stage 32 x 32 blocks of fp32 (1) or 16-bit (2) results in shared memory and hand them to the
+    // TMA unit (tensor map tmC), which writes whole 128-byte lines and clips at the edges of C.
+    int out_mode;
+    int band;                // m-tiles per band of the tile order (see tile_coords)
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -148,6 +153,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// Bulk tensor store of one shared-memory box into C (this GPU's own memory, no multicast), as a bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most N of this thread's bulk groups may still be READING their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// orders this thread's ordinary shared-memory writes before later reads of them by the TMA unit
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -185,6 +207,18 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, written so that the compiler treats the 32 registers of an earlier tc_ld32 as produced HERE: no
+// read of them can be scheduled above the wait when other work sits between the load and the wait.
+__device__ __forceinline__ void tc_wait_ld_into(uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :
+        : "memory");
+}
 
 // Shared-memory matrix descriptor, descriptor version 1.  layout_type 2 = 128-byte swizzle on 16-byte
 // units; 1 = 128-byte swizzle on 32-byte units, the only swizzled layout the tensor cores accept for an
@@ -210,8 +244,9 @@ __device__ __forceinline__ float act_apply(int act, float v) {
     }
 }
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int &tm, int &tn) {
-    constexpr int G = 16;   // m-tiles per band: keeps a wave's A and B strips resident in L2
+// Tile order: bands of G m-tiles, inside a band m fastest.  The CTAs of a wave then share G strips of A and about
+// (CTAs / G) strips of B, which they read in step (one DRAM read per strip and wave, the rest L2 hits).
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int G, int &tm, int &tn) {
     const int per_band = G * num_n;
     const int band = t / per_band, first_m = band * G;
     const int rows = min(num_m - first_m, G);
@@ -232,14 +267,13 @@ __device__ __forceinline__ void ld_global_v8(const void *p, uint32_t (&w)[8]) {
                  : "l"(p));
 }
 
-// Fused epilogue for 32 consecutive columns of one output row held by this thread:
-// bias, activation, activation-derivative mask, accumulate, stores (fp32 and/or operand type).
+// The arithmetic of the epilogue for 32 consecutive columns of one output row: bias, activation and the
+// activation-derivative mask, from the raw accumulator words r into v.
 template <bool TF32>
-__device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row, int col0, const uint32_t (&r)[32],
-                                               const float *bias_s /* 32 staged bias values of these columns, or null */) {
+__device__ __forceinline__ void epilogue_values(const TcParams &p, long long row, int col0, const uint32_t (&r)[32],
+                                                const float *bias_s, float (&v)[32]) {
     constexpr bool t_bf16 = !TF32;
     const int valid = min(32, p.N - col0);
-    float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
     if (bias_s) {   // every lane reads the same shared-memory word: a broadcast, no bank conflict
@@ -252,19 +286,19 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
     } else if (p.act == ZN_ACT_SIGMOID) {
-#pragma unroll 4
+#pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = act_apply(ZN_ACT_SIGMOID, v[j]);
     } else if (p.act == ZN_ACT_TANH) {
-#pragma unroll 4
+#pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = act_apply(ZN_ACT_TANH, v[j]);
     } else if (p.act == ZN_ACT_GELU) {
-#pragma unroll 4
+#pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = zn_gelu_fwd(v[j]);
     } else if (p.act == ZN_ACT_LEAKY_RELU) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = zn_leaky_fwd(v[j]);
     } else if (p.act == ZN_ACT_ELU) {
-#pragma unroll 4
+#pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = zn_elu_fwd(v[j]);
     }
     if (p.mask) {
@@ -307,6 +341,17 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
                 if (j < valid && !(mrow[j] > 0.f)) v[j] = 0.f;
         }
     }
+}
+
+// Fused epilogue for 32 consecutive columns of one output row held by this thread:
+// bias, activation, activation-derivative mask, accumulate, stores (fp32 and/or operand type).
+template <bool TF32>
+__device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row, int col0, const uint32_t (&r)[32],
+                                               const float *bias_s /* 32 staged bias values of these columns, or null */) {
+    constexpr bool t_bf16 = !TF32;
+    const int valid = min(32, p.N - col0);
+    float v[32];
+    epilogue_values<TF32>(p, row, col0, r, bias_s, v);
     if (p.out_f32) {
         float *orow = p.out_f32 + row * p.ld_out_f32 + col0;
         const bool vec = valid == 32 && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
@@ -388,6 +433,33 @@ __device__ __forceinline__ const float *stage_bias(const TcParams &p, float *bia
     return dst;
 }
 
+// Staged output.  One epilogue warp owns two 4 KiB shared-memory buffers; a buffer holds the warp's 32 rows of one
+// 32-column block in the layout the tensor map's swizzle expects (fp32: 128-byte rows, 16-byte unit j of row r at
+// position j ^ (r & 7); 16-bit: 64-byte rows, unit j at j ^ ((r >> 1) & 3)), which also spreads the 16-byte stores
+// of a quarter warp over all 32 banks.  Lane 0 then issues one bulk tensor store per block and keeps at most one
+// store reading shared memory behind it, so the warp returns to the next accumulator words at once.
+constexpr int STG_BUF = 4096;
+constexpr int STAGING_BYTES = 4 * 2 * STG_BUF;
+
+__device__ __forceinline__ void stage_block_f32(uint32_t buf, int lane, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        st_shared_v4(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4), __float_as_uint(v[4 * j]),
+                     __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+}
+__device__ __forceinline__ void stage_block_bf16(uint32_t buf, int lane, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * j + 2 * h], v[8 * j + 2 * h + 1]);
+            w[h] = *reinterpret_cast<const uint32_t *>(&b2);
+        }
+        st_shared_v4(buf + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4), w[0], w[1], w[2], w[3]);
+    }
+}
+
 // ET: operand element type (__nv_bfloat16 or float-as-tf32).
 template <typename ET>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -464,7 +536,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (++q == TQ) { q = 0; qphase ^= 1u; }
                 if (t < 0) break;
                 int tm, tn;
-                tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+                tile_coords(t, p.num_m_tiles, p.num_n_tiles, p.band, tm, tn);
                 const int m0 = tm * BM, n0 = tn * BN;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
@@ -548,7 +620,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (++sq == TQ) { sq = 0; sqphase ^= 1u; }
             if (t < 0) break;
             int tm, tn;
-            tile_coords(t, p.num_m_tiles, p.num_n_tiles, tm, tn);
+            tile_coords(t, p.num_m_tiles, p.num_n_tiles, p.band, tm, tn);
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
@@ -597,12 +669,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // the leader's barrier); `empty` and `tmem_full` are signalled in both CTAs by one multicast
 // tcgen05.commit; the epilogue warps of both CTAs arrive on the leader's `tmem_empty`.
 
-constexpr int STAGES2 = 6;                        // default ring depth; 4 and 5 are built as well (see zn_gemm_tc)
+constexpr int STAGES2 = 5;                        // default ring depth; 4 is built as well (see zn_gemm_tc)
 constexpr int HALF = 128;                         // rows of A, and columns of B, staged per CTA
 constexpr int A2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int B2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int STAGE2_BYTES = A2_STAGE + B2_STAGE;
-constexpr int smem2_bytes(int stages) { return stages * STAGE2_BYTES + 1024 + 256 + BIAS_SMEM; }
+// after the operand ring: barriers (256 B), the bias strips, then (1024-aligned) the output staging buffers
+constexpr int PAIR_TAIL = ((256 + BIAS_SMEM + 1023) / 1024) * 1024;
+constexpr int smem2_bytes(int stages, bool staging) {
+    return 1024 /* alignment slack */ + stages * STAGE2_BYTES + PAIR_TAIL + (staging ? STAGING_BYTES : 0);
+}
+static_assert(smem2_bytes(STAGES2, true) <= 232448 && smem2_bytes(6, false) <= smem2_bytes(STAGES2, true),
+              "the two-CTA kernel must fit the 227 KB of shared memory a CTA may have");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -654,7 +732,8 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 
 template <typename ET, int NST>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const TcParams p) {
     constexpr bool TF32 = sizeof(ET) == 4;
     constexpr int ES = sizeof(ET);
     constexpr int BK = ROW_BYTES / ES;
@@ -677,6 +756,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *tile_ring = reinterpret_cast<volatile int *>(tmem_slot + 2);
     float *bias_smem = reinterpret_cast<float *>(gen + NST * STAGE2_BYTES + 256);
+    const uint32_t staging = base + NST * STAGE2_BYTES + PAIR_TAIL;      // 1024-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
@@ -684,6 +764,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        if (p.out_mode) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
         for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps x 2 CTAs
         // tile-index ring: the leader's producer publishes into both CTAs; its `empty` side counts every reader
@@ -716,16 +797,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            int q = 0, prev_t = 0;
+            int q = 0;
             uint32_t qphase = 0;
+            // The leader draws the index of the tile AFTER the one it is about to load while that one's loads are
+            // still being issued: the atomic's round trip to L2 is then hidden behind a whole tile of loads.
+            int t_next = cluster_id;
             for (bool first = true; ok; first = false) {
                 int t;
                 if (rank == 0) {
                     // the leader picks the pair's next tile and publishes it into both CTAs' rings
-                    t = first ? cluster_id
-                              : (p.dynamic_tiles ? (int)(num_clusters + atomicAdd(p.tile_counter, 1u)) : prev_t + num_clusters);
-                    prev_t = t;
+                    t = t_next;
                     if (t >= num_tiles) t = -1;
+                    if (t >= 0)
+                        t_next = p.dynamic_tiles ? (int)(num_clusters + atomicAdd(p.tile_counter, 1u)) : t + num_clusters;
                     if (!mbar_wait_cluster(sempty_bar(q), qphase ^ 1u, abort_flag, p.status, 15)) { ok = false; break; }
                     tile_ring[q] = t;
                     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(smem_u32((const void *)&tile_ring[q]), 1)), "r"(t)
@@ -740,7 +824,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (++q == TQ) { q = 0; qphase ^= 1u; }
                 if (t < 0) break;
                 int tm, tn;
-                tile_coords(t, num_m_pairs, p.num_n_tiles, tm, tn);
+                tile_coords(t, num_m_pairs, p.num_n_tiles, p.band, tm, tn);
                 const int m0 = tm * 2 * HALF + (int)rank * HALF;       // this CTA's rows of A
                 const int n0 = tn * BN + (int)rank * HALF;             // this CTA's columns of B
                 for (int kb = 0; kb < nkb; ++kb) {
@@ -811,6 +895,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // ================= epilogue (both CTAs): warps 2..5, this CTA's 128 rows =================
         const int q = warp & 3;
         int it = 0, sq = 0;
+        uint32_t stores = 0;                              // staged blocks this warp has handed to the TMA unit
         uint32_t sqphase = 0;
         bool ok = true;
         for (; ok; ++it) {
@@ -821,29 +906,64 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (++sq == TQ) { sq = 0; sqphase ^= 1u; }
             if (t < 0) break;
             int tm, tn;
-            tile_coords(t, num_m_pairs, p.num_n_tiles, tm, tn);
+            tile_coords(t, num_m_pairs, p.num_n_tiles, p.band, tm, tn);
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
             tc_fence_after();
-            const long long row = (long long)tm * 2 * HALF + (long long)rank * HALF + q * 32 + lane;
+            const int warp_row0 = tm * 2 * HALF + (int)rank * HALF + q * 32;
+            const long long row = (long long)warp_row0 + lane;
             const int n0 = tn * BN;
             const float *bias_s = stage_bias(p, bias_smem, n0);
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
+            // The accumulator words of block c + 1 are already on their way from tensor memory while block c goes
+            // through the epilogue arithmetic and its stores.
+            uint32_t next[32];
+            tc_ld32(taddr, next);
             for (int c = 0; c < nchunks; ++c) {
                 uint32_t r[32];
-                tc_ld32(taddr + (uint32_t)(c * 32), r);
-                tc_wait_ld();
-                if (c == nchunks - 1) {
+                tc_wait_ld_into(next);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = next[j];
+                if (c + 1 < nchunks) {
+                    tc_ld32(taddr + (uint32_t)((c + 1) * 32), next);
+                } else {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));   // to the leader's MMA thread
                 }
-                if (row >= p.M) continue;
-                epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+                if (p.out_mode == 0) {
+                    if (row >= p.M) continue;
+                    epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+                    continue;
+                }
+                if (warp_row0 >= p.M) continue;          // the warp's 32 rows all lie below C (uniform over the warp)
+                float v[32];
+                // rows below C inside a live block: computed from whatever the accumulator holds, without touching
+                // the mask, and clipped by the store
+                if (row < p.M) epilogue_values<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                }
+                const uint32_t sbuf = staging + (uint32_t)(q * 2 + (stores & 1)) * STG_BUF;
+                if (stores >= 2) {                       // the store that last used this buffer has read it
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+                }
+                if (p.out_mode == 1) stage_block_f32(sbuf, lane, v);
+                else stage_block_bf16(sbuf, lane, v);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tmC, n0 + c * 32, warp_row0, sbuf);
+                    bulk_commit();
+                }
+                ++stores;
             }
         }
+        if (lane == 0 && p.out_mode) bulk_wait_all();   // this thread's stores have left shared memory and landed
     }
 
     // ---- common exit: neither CTA may leave while its partner can still reach its shared or tensor memory
@@ -898,13 +1018,23 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// 2-D row-major tensor [outer][inner], row pitch ld elements; box {box_inner, box_outer}; 128B swizzle
-// (on 32-byte units when swizzle_32b_units, to match descriptor layout type 1); out-of-bounds reads zero.
+// 2-D row-major tensor [outer][inner], row pitch ld elements; box {box_inner, box_outer}.  Swizzle kinds:
+// 0 = 128 B on 16-byte units, 1 = 128 B on 32-byte units (to match descriptor layout type 1), 2 = 64 B (the
+// staged output blocks of 16-bit results); out-of-bounds reads give zero, out-of-bounds parts of a store are dropped.
+// Encoded maps are cached per context under the bytes of this key.
+struct TmapKey {
+    const void *ptr;
+    long long inner, outer, ld;
+    int es, box_inner, box_outer, swizzle;
+};
+
 zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int64_t inner, int64_t outer, int64_t ld,
-                    int box_inner, int box_outer, bool swizzle_32b_units) {
-    char key[160];
-    snprintf(key, sizeof key, "%p|%d|%lld|%lld|%lld|%d|%d|%d", ptr, es, (long long)inner, (long long)outer,
-             (long long)ld, box_inner, box_outer, (int)swizzle_32b_units);
+                    int box_inner, int box_outer, int swizzle_kind) {
+    TmapKey k;
+    memset(&k, 0, sizeof k);                      // padding bytes are part of the key
+    k.ptr = ptr; k.inner = inner; k.outer = outer; k.ld = ld;
+    k.es = es; k.box_inner = box_inner; k.box_outer = box_outer; k.swizzle = swizzle_kind;
+    const std::string key(reinterpret_cast<const char *>(&k), sizeof k);
     auto it = ctx->tmap_cache.find(key);
     if (it != ctx->tmap_cache.end()) {
         memcpy(out, it->second.data(), sizeof(CUtensorMap));
@@ -919,8 +1049,9 @@ zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int6
     cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-    CUresult r = enc(out, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+    const CUtensorMapSwizzle sw = swizzle_kind == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                  : swizzle_kind == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+    CUresult r = enc(out, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return zn_fail(ctx, ZN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
     if (ctx->tmap_cache.size() > 4096) ctx->tmap_cache.clear();
@@ -969,10 +1100,10 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
 
     CUtensorMap tmA, tmB;
     const bool tf32 = elem_type != 0;
-    if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM, false));     // [m][k]: inner k
-    else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk, tf32));            // [k][m]: inner m
-    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, BN, false));     // [n][k]: inner k
-    else ZN_TRY(make_tmap(ctx, &tmB, es, b, n, k, ldb, ch, bk, tf32));            // [k][n]: inner n
+    if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM, 0));         // [m][k]: inner k
+    else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk, tf32 ? 1 : 0));    // [k][m]: inner m
+    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, BN, 0));         // [n][k]: inner k
+    else ZN_TRY(make_tmap(ctx, &tmB, es, b, n, k, ldb, ch, bk, tf32 ? 1 : 0));    // [k][n]: inner n
 
     TcParams p;
     p.M = (int)m; p.N = (int)n; p.K = (int)k;
@@ -995,6 +1126,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.bias = e.bias; p.act = e.act; p.mask = e.mask; p.ld_mask = e.ld_mask;
     p.out_f32 = e.out_f32; p.ld_out_f32 = e.ld_out_f32; p.out_t = e.out_t; p.ld_out_t = e.ld_out_t;
     p.accumulate = e.accumulate;
+    p.out_mode = 0;
+    // Bands of 8 m-tiles: a wave of 74 tile pairs then shares 8 strips of A and about 9 of B, the fewest distinct
+    // strips (DRAM reads) a wave can have; measured against 16 on the 8192-wide training step: DRAM reads of an
+    // 8192 x 8192 x 8192 product fall from 1.25 GB towards 0.7 GB, the SM clock under the power cap rises from
+    // 1567 to 1634 MHz and the step from 57.2 to 56.5 ms.  ZN_TC_BAND overrides (diagnostic).
+    static const int band = [] { const char *e = getenv("ZN_TC_BAND"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 64 ? v : 8; }();
+    p.band = band;
     p.status = ctx->status_dev;
     if (!ctx->tile_counters) {
         ZN_CUDA(ctx, cudaMalloc((void **)&ctx->tile_counters, 2 * sizeof(unsigned int)));
@@ -1017,27 +1155,59 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
 
     zn_launch_scope scope(ctx, ZN_PROF_GEMM_TC, 2.0 * m * n * k,
                           (double)es * (m * k + k * n) + (e.out_f32 ? 4.0 : (double)es) * m * n);
-    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;   // ZN_TC_PAIR=0: one-CTA kernel only (diagnostic)
-    if (pair_mode && m > BM) {
+    // Which kernel.  The two-CTA kernel halves the operand traffic per SM and wins wherever the main loop is long.
+    // With a short main loop (K of at most 16 k-blocks: 1024 bf16 / 512 tf32 values) a tile is over before the
+    // pair's cluster-wide hand-shakes pay off and the one-CTA kernel is faster: measured in bf16, 65536 x 512 x 512
+    // 665 against 510-530 TFLOP/s, 1024^3 114-128 against 103, 256^3 12.8 against 16.8 us per launch.
+    // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
+    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
+    const bool use_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && p.num_k_blocks > 16));
+    if (use_pair) {
         // two-CTA kernel: 256 x 256 tiles, B staged in halves of 128 columns per CTA
-        if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, HALF, false));
+        if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, HALF, 0));
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | ((uint32_t)((2 * HALF) >> 4) << 24);   // M = 256 across the pair
+        // Output path.  Default: every thread stores its own row of the tile (32-byte pieces, straight from the
+        // registers the accumulator was read into).  ZN_TC_STAGED_STORE=1 selects the other path wherever it can
+        // run: the epilogue warps stage 32 x 32 blocks in shared memory and the TMA unit writes them as whole
+        // 128-byte lines.  Measured in bf16 with fp32 output, staged against per-thread: 65536 x 512 x 512 537
+        // against 518 TFLOP/s, 16384^3 TN 1188 against 1245, the 8192-wide training step 58.1 against 57.5 ms (the
+        // bulk stores share the TMA unit with the operand loads) -- no shape where it pays once short-K products go
+        // to the one-CTA kernel, so it stays an option.  It needs C to be ONE block the unit can address (16-byte
+        // aligned base and row pitch) that is only written; C += ..., two outputs at once and odd pitches always
+        // take the per-thread stores.
+        static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : 0;
+        const bool want_staged = staged_mode != 0;
+        CUtensorMap tmC;
+        memset(&tmC, 0, sizeof tmC);
+        if (want_staged && !e.accumulate && (e.out_f32 != nullptr) != (e.out_t != nullptr)) {
+            const bool wide = e.out_f32 != nullptr || tf32;                  // 4-byte results
+            const void *cptr = e.out_f32 ? (const void *)e.out_f32 : (const void *)e.out_t;
+            const int64_t ldc = e.out_f32 ? e.ld_out_f32 : e.ld_out_t;
+            const int ces = wide ? 4 : 2;
+            if ((reinterpret_cast<uintptr_t>(cptr) & 15) == 0 && (ldc * ces) % 16 == 0 && ldc >= n) {
+                ZN_TRY(make_tmap(ctx, &tmC, ces, cptr, n, m, ldc, 32, 32, wide ? 0 : 2));
+                p.out_mode = wide ? 1 : 2;
+            }
+        }
         const long long pair_tiles = (long long)((m + 2 * HALF - 1) / (2 * HALF)) * p.num_n_tiles;
         int max_clusters = ctx->sm_count / 2 - (e.reserve_sms + 1) / 2;
         if (max_clusters < 1) max_clusters = 1;
         const int clusters = (int)(pair_tiles < max_clusters ? pair_tiles : max_clusters);
-        // ZN_TC_PAIR_STAGES = 4 or 5 (diagnostic): a shallower operand ring leaves 62 / 94 KB of the SM's shared
-        // memory to kernels that share the SM with this one, instead of 30 KB
-        static const int nst = [] { const char *e = getenv("ZN_TC_PAIR_STAGES"); const int v = e ? atoi(e) : STAGES2; return (v == 4 || v == 5) ? v : STAGES2; }();
-        using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const TcParams);
+        // Ring depth: 5 stages beside the 32 KB of output staging; a launch that stores per thread has that room
+        // for a sixth stage.  ZN_TC_PAIR_STAGES = 4 / 5 / 6 overrides (diagnostic; 6 only without staging).
+        static const int nst_env = [] { const char *e = getenv("ZN_TC_PAIR_STAGES"); return e ? atoi(e) : 0; }();
+        int nst = STAGES2;
+        if (nst_env == 4 || nst_env == 5) nst = nst_env;
+        if (nst_env == 6 && p.out_mode == 0) nst = 6;
+        using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TcParams);
         PairFn fn;
-        if (elem_type == 0) fn = nst == 4 ? gemm_tc_pair_kernel<__nv_bfloat16, 4> : nst == 5 ? gemm_tc_pair_kernel<__nv_bfloat16, 5> : gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>;
-        else fn = nst == 4 ? gemm_tc_pair_kernel<float, 4> : nst == 5 ? gemm_tc_pair_kernel<float, 5> : gemm_tc_pair_kernel<float, STAGES2>;
+        if (elem_type == 0) fn = nst == 4 ? gemm_tc_pair_kernel<__nv_bfloat16, 4> : nst == 6 ? gemm_tc_pair_kernel<__nv_bfloat16, 6> : gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>;
+        else fn = nst == 4 ? gemm_tc_pair_kernel<float, 4> : nst == 6 ? gemm_tc_pair_kernel<float, 6> : gemm_tc_pair_kernel<float, STAGES2>;
         static std::atomic<uint64_t> pair_attr_mask{0};
         if (!(pair_attr_mask.load() & dev_bit)) {
-            for (PairFn f : {(PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 5>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>,
-                             (PairFn)gemm_tc_pair_kernel<float, 4>, (PairFn)gemm_tc_pair_kernel<float, 5>, (PairFn)gemm_tc_pair_kernel<float, STAGES2>}) {
-                ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2)));
+            for (PairFn f : {(PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 6>,
+                             (PairFn)gemm_tc_pair_kernel<float, 4>, (PairFn)gemm_tc_pair_kernel<float, STAGES2>, (PairFn)gemm_tc_pair_kernel<float, 6>}) {
+                ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2, true)));
                 cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             }
             cudaGetLastError();
@@ -1046,7 +1216,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(2 * clusters));
         cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = smem2_bytes(nst);
+        cfg.dynamicSmemBytes = smem2_bytes(nst, nst != 6);
         cfg.stream = ctx->stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1055,7 +1225,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        const cudaError_t le = cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p);
+        const cudaError_t le = cudaLaunchKernelEx(&cfg, fn, tmA, tmB, tmC, p);
         if (le != cudaSuccess) return launch_failed(le, "launch of the two-CTA tensor-core GEMM");
         return ZN_OK;
     }

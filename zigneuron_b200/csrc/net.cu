@@ -16,6 +16,7 @@
 // accepts) that the optimizer kernel refreshes.  Activations are [rows][ld] in
 // the operand type, ld = width rounded up to 8 elements in tensor-core modes.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "zn_internal.h"
@@ -56,6 +57,7 @@ struct Layer {
     // ordering between the lanes of a step (see step_dev)
     cudaEvent_t g_ready = nullptr, bias_done = nullptr, grads_ready = nullptr, reduced = nullptr, updated = nullptr;
     cudaEvent_t stepped = nullptr;        // sharded update: this rank's piece of the layer has been updated
+    cudaEvent_t half_ready = nullptr;     // data parallel: the first half of gW's rows exists (layer 0 only, see step_dev)
     bool update_pending = false;          // `updated` has been recorded and not yet waited for by the host
 };
 
@@ -230,9 +232,26 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     const bool exact = n->prec == ZN_FP32_EXACT;
     const bool dp = n->global_rows > 0 && zn_dp_active(ctx);
     const bool shard = dp && n->shard_update && !exact;
-    cudaStream_t s_main = ctx->lanes[ZN_LANE_MAIN].stream, s_comm = ctx->lanes[ZN_LANE_COMM].stream;
-    cudaStream_t s_opt = ctx->lanes[ZN_LANE_OPT].stream, s_aux = ctx->lanes[ZN_LANE_AUX].stream;
-    s_main = ctx->stream;   // lane 0 is active here; its slot in lanes[] is only refreshed on a switch
+    // Small networks (a few million parameters at most, one GPU) are bound by the number of launches and of
+    // stream-to-stream hand-overs, not by any kernel: they run the whole step on the main stream, take the norm of
+    // all gradients in one launch and update every tensor in one launch.  ZN_COMPACT_STEP=0 switches this off.
+    static const bool compact_allowed = !(getenv("ZN_COMPACT_STEP") && atoi(getenv("ZN_COMPACT_STEP")) == 0);
+    size_t total_params = 0;
+    for (const Layer &l : n->layers) total_params += l.len;
+    const bool compact = compact_allowed && !dp && !exact && total_params <= ((size_t)1 << 22) && 2 * L <= ZN_MULTI_UPDATE_MAX;
+    const int lane_comm = compact ? ZN_LANE_MAIN : ZN_LANE_COMM, lane_opt = compact ? ZN_LANE_MAIN : ZN_LANE_OPT;
+    const int lane_aux = compact ? ZN_LANE_MAIN : ZN_LANE_AUX;
+    cudaStream_t s_main = ctx->stream;   // lane 0 is active here; its slot in lanes[] is only refreshed on a switch
+    cudaStream_t s_comm = compact ? s_main : ctx->lanes[ZN_LANE_COMM].stream;
+    cudaStream_t s_opt = compact ? s_main : ctx->lanes[ZN_LANE_OPT].stream;
+    cudaStream_t s_aux = compact ? s_main : ctx->lanes[ZN_LANE_AUX].stream;
+    // ordering between two lanes; inside one stream the order of submission is the order of execution
+    auto hand_over = [&](cudaEvent_t ev, cudaStream_t from, cudaStream_t to) -> zn_status {
+        if (from == to) return ZN_OK;
+        ZN_CUDA(ctx, cudaEventRecord(ev, from));
+        ZN_CUDA(ctx, cudaStreamWaitEvent(to, ev, 0));
+        return ZN_OK;
+    };
     ZN_TRY(forward_dev(n, x_dev, rows));
 
     Layer &last = n->layers[L - 1];
@@ -252,27 +271,45 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         const int64_t ld_g = n->lds[idx + 1];
         const void *x_in = (idx == 0 && !n->tc) ? (const void *)x_dev : (const void *)n->acts[idx];
         // gb = column sums of G   (accumulateBias into a cleared gb, src/layer.zig:459), on the aux lane
-        ZN_CUDA(ctx, cudaEventRecord(l.g_ready, s_main));
-        ZN_CUDA(ctx, cudaStreamWaitEvent(s_aux, l.g_ready, 0));
+        ZN_TRY(hand_over(l.g_ready, s_main, s_aux));
         {
-            zn_lane_guard lane(ctx, ZN_LANE_AUX);
+            zn_lane_guard lane(ctx, lane_aux);
             ZN_TRY(zn_k_bias_reduce(ctx, g, n->bf16, ld_g, (int64_t)rows, (int64_t)l.out, l.grads + l.b_off, false, exact));
         }
-        ZN_CUDA(ctx, cudaEventRecord(l.bias_done, s_aux));
+        if (!compact) ZN_CUDA(ctx, cudaEventRecord(l.bias_done, s_aux));
         // gW = X^T . G           (matMulTransposeA, src/layer.zig:466)
-        {
+        // Layer 0 comes last, so the exchange of its gradients is the one with the least work left to hide under
+        // (only its own dX GEMM) and the next step's first GEMM waits for it.  Data parallel, its gW is therefore
+        // computed as two halves of its rows and the first half is already on the wire while the second is still
+        // being computed.  ZN_DP_SPLIT_LAST=0 switches this off (diagnostic).
+        static const bool split_last = !(getenv("ZN_DP_SPLIT_LAST") && atoi(getenv("ZN_DP_SPLIT_LAST")) == 0);
+        const size_t exchange_count = idx + 1 == L ? l.cap : l.blk;
+        size_t exchanged = 0;                       // floats of this layer's block already handed to the exchange
+        if (dp && !shard && idx == 0 && n->tc && split_last && l.in % 512 == 0 && l.in >= 1024) {
+            const size_t half = l.in / 2;
+            zn_epilogue ep;
+            ep.out_f32 = l.grads;
+            ep.ld_out_f32 = (int64_t)l.out;
+            ZN_TRY(net_gemm(n, 1, x_in, n->lds[idx], g, ld_g, (int64_t)half, (int64_t)l.out, (int64_t)rows, ep));
+            ZN_CUDA(ctx, cudaEventRecord(l.half_ready, s_main));
+            ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.half_ready, 0));
+            ZN_TRY(zn_dp_allreduce(ctx, l.grads, half * l.out, s_comm));
+            exchanged = half * l.out;
+            ep.out_f32 = l.grads + half * l.out;
+            const void *x_hi = (const char *)x_in + half * esize(n);      // columns [half, in) of the [rows][in] block
+            ZN_TRY(net_gemm(n, 1, x_hi, n->lds[idx], g, ld_g, (int64_t)(l.in - half), (int64_t)l.out, (int64_t)rows, ep));
+        } else {
             zn_epilogue ep;
             ep.out_f32 = l.grads;
             ep.ld_out_f32 = (int64_t)l.out;
             ZN_TRY(net_gemm(n, 1, x_in, n->lds[idx], g, ld_g, (int64_t)l.in, (int64_t)l.out, (int64_t)rows, ep));
         }
         // this layer's gradients are final: sum them over ranks and square-sum them while earlier layers run
-        ZN_CUDA(ctx, cudaEventRecord(l.grads_ready, s_main));
-        ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.grads_ready, 0));
-        ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.bias_done, 0));
+        ZN_TRY(hand_over(l.grads_ready, s_main, s_comm));
+        if (!compact) ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.bias_done, 0));
         // the last layer's block carries the loss sum in its tail; the other three tail floats stay zero and
         // ride along so that every exchanged count is a multiple of four floats
-        if (dp && !shard) ZN_TRY(zn_dp_allreduce(ctx, l.grads, idx + 1 == L ? l.cap : l.blk, s_comm));
+        if (dp && !shard) ZN_TRY(zn_dp_allreduce(ctx, l.grads + exchanged, exchange_count - exchanged, s_comm));
         if (shard) {
             // sharded update: this rank ends with the summed gradients of its own piece of the block only, and
             // squares just that piece (the padding inside a block is zero and adds nothing)
@@ -285,14 +322,14 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
             } else {
                 ZN_CUDA(ctx, cudaMemsetAsync(n->sumsq + idx, 0, sizeof(double), s_comm));
             }
-        } else if (!exact) {
+        } else if (!exact && !compact) {
             zn_lane_guard lane(ctx, ZN_LANE_COMM);
             const zn_seg segs[2] = {{l.grads, l.in * l.out}, {l.grads + l.b_off, l.out}};
             ZN_TRY(zn_k_sumsq(ctx, segs, 2, n->sumsq + idx));
         }
-        ZN_CUDA(ctx, cudaEventRecord(l.reduced, s_comm));
+        if (!compact) ZN_CUDA(ctx, cudaEventRecord(l.reduced, s_comm));
         // G of the layer above lives in the block the next dX overwrites: its column sums must be done
-        if (idx + 1 < L) ZN_CUDA(ctx, cudaStreamWaitEvent(s_main, n->layers[idx + 1].bias_done, 0));
+        if (idx + 1 < L && !compact) ZN_CUDA(ctx, cudaStreamWaitEvent(s_main, n->layers[idx + 1].bias_done, 0));
         // dX = G . W^T, masked by the previous layer's activation derivative (src/layer.zig:440-448)
         {
             zn_epilogue ep;
@@ -333,17 +370,19 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     n->last_rows = rows;
 
     // ---- optimizer lane: everything below waits for all layers' reductions, not for the main stream
-    for (size_t i = 0; i < L; ++i) ZN_CUDA(ctx, cudaStreamWaitEvent(s_opt, n->layers[i].reduced, 0));
-    zn_lane_guard opt_lane(ctx, ZN_LANE_OPT);
+    if (!compact)
+        for (size_t i = 0; i < L; ++i) ZN_CUDA(ctx, cudaStreamWaitEvent(s_opt, n->layers[i].reduced, 0));
+    zn_lane_guard opt_lane(ctx, lane_opt);
+    (void)lane_comm;
 
     // global norm over every gradient tensor, weights then bias, layer by layer (src/network.zig:513-521)
-    if (exact) {
+    if (exact || compact) {
         std::vector<zn_seg> segs;
         for (size_t i = 0; i < L; ++i) {
             segs.push_back({n->layers[i].grads, n->layers[i].in * n->layers[i].out});
             segs.push_back({n->layers[i].grads + n->layers[i].b_off, n->layers[i].out});
         }
-        ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars, true));
+        ZN_TRY(zn_k_grad_norm(ctx, segs.data(), (int)segs.size(), n->scalars, exact));
     } else {
         if (shard) {
             // one exchange of L + 1 doubles: every layer's sum of squares and the loss sum; the communication lane
@@ -365,6 +404,8 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
     if (done) ZN_CUDA(ctx, cudaEventRecord(done, s_opt));
 
     // optimizer per layer (src/network.zig:541-549)
+    zn_opt_args multi_args[ZN_MULTI_UPDATE_MAX];
+    int multi_kind[ZN_MULTI_UPDATE_MAX], multi_bias[ZN_MULTI_UPDATE_MAX], multi_n = 0;
     for (size_t i = 0; i < L; ++i) {
         Layer &l = n->layers[i];
         zn_opt_args a{};
@@ -383,6 +424,14 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
             a.decay_mul = 1.0f - wdlr;
         }
         auto update = [&](bool is_bias) -> zn_status {
+            if (compact) {      // queued: one launch for all tensors after the loop
+                a.w_clamp = (l.opt == OPT_SGD && is_bias) ? 50.0f : 100.0f;
+                multi_args[multi_n] = a;
+                multi_kind[multi_n] = l.opt == OPT_ADAMW ? (int)OPT_ADAM : l.opt;
+                multi_bias[multi_n] = is_bias ? 1 : 0;
+                ++multi_n;
+                return ZN_OK;
+            }
             switch (l.opt) {
             case OPT_ADAM: case OPT_ADAMW: a.w_clamp = 100.0f; return zn_k_adam(ctx, a);
             case OPT_MOMENTUM: return zn_k_sgd_momentum(ctx, a);
@@ -425,9 +474,11 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         if (l.m) a.m = l.m + l.b_off;
         if (l.v) a.v = l.v + l.b_off;
         ZN_TRY(update(true));
+        if (compact) continue;        // everything runs on the main stream: the next step is ordered after it anyway
         ZN_CUDA(ctx, cudaEventRecord(l.updated, s_opt));
         l.update_pending = true;
     }
+    if (compact && multi_n > 0) ZN_TRY(zn_k_multi_update(ctx, multi_args, multi_kind, multi_bias, multi_n));
     return ZN_OK;
 }
 
@@ -522,7 +573,7 @@ extern "C" void zn_net_destroy(zn_net *n) {
         if (l.params_nccl) zn_dp_free_registered(n->ctx, l.params, l.params_reg);
         else cudaFree(l.params);
         cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
-        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated, l.stepped})
+        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated, l.stepped, l.half_ready})
             if (ev) cudaEventDestroy(ev);
     }
     cudaFree(n->sumsq);
@@ -560,7 +611,7 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     ZN_CUDA(ctx, cudaMalloc((void **)&l.grads, alloc));
     ZN_CUDA(ctx, cudaMemsetAsync(l.params, 0, alloc, ctx->stream));
     ZN_CUDA(ctx, cudaMemsetAsync(l.grads, 0, alloc, ctx->stream));
-    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated, &l.stepped})
+    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated, &l.stepped, &l.half_ready})
         ZN_CUDA(ctx, cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
     if (n->tc) {
         const bool direct = !n->bf16 && output_size % 4 == 0;   // tf32 can read W itself when its pitch is TMA-legal

@@ -32,8 +32,27 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-__global__ void sq_partial_kernel(const __grid_constant__ SegTable tab, float *__restrict__ partial) {
+// Sum of the block partials in double, by one block: thread i adds partial[i], partial[i + TPB], ...; then a tree.
+__device__ __forceinline__ double sum_partials_double(const float *partial, int n, double *sm) {
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)__ldcg(partial + i);
+    sm[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = TPB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+        __syncthreads();
+    }
+    return sm[0];
+}
+
+// finish: 0 = partials only (a second kernel adds them up); 1 = the block that arrives last adds all partials and
+// writes the sum of squares as a double; 2 = ... and writes norm and clip factor (src/network.zig:513-524).  The
+// adding order is that of the two-kernel form, so the results are the same to the bit.
+__global__ void sq_partial_kernel(const __grid_constant__ SegTable tab, float *__restrict__ partial,
+                                  unsigned int *counter, int finish, void *out) {
     __shared__ float part[TPB / 32];
+    __shared__ double fin[TPB];
+    __shared__ bool last;
     int seg = 0;
     while (seg + 1 < tab.nseg && (int)blockIdx.x >= tab.first_block[seg + 1]) ++seg;
     const float *p = tab.ptr[seg];
@@ -61,25 +80,26 @@ __global__ void sq_partial_kernel(const __grid_constant__ SegTable tab, float *_
 #pragma unroll
         for (int i = 0; i < TPB / 32; ++i) t += part[i];
         partial[blockIdx.x] = t;
+        if (finish) {
+            __threadfence();                                       // the partial is visible before the arrival is
+            last = atomicAdd(counter, 1u) == gridDim.x - 1;
+        }
     }
-}
-
-// norm = sqrt(sum); factor = norm > 1 ? 1 / (norm + 1e-6) : 1   (src/network.zig:513-524)
-__global__ void norm_final_kernel(const float *__restrict__ partial, int n, float *__restrict__ out) {
-    __shared__ double sm[TPB];
-    double s = 0.0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partial[i];
-    sm[threadIdx.x] = s;
+    if (!finish) return;
     __syncthreads();
-    for (int o = TPB / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
-        __syncthreads();
-    }
+    if (!last) return;
+    __threadfence();
+    const double total_sq = sum_partials_double(partial, (int)gridDim.x, fin);
     if (threadIdx.x == 0) {
-        const float total = sqrtf((float)sm[0]);
-        const float max_norm = 1.0f;
-        out[0] = total;
-        out[1] = total > max_norm ? __fdiv_rn(max_norm, __fadd_rn(total, 1e-6f)) : 1.0f;
+        if (finish == 1) {
+            *static_cast<double *>(out) = total_sq;
+        } else {
+            float *o = static_cast<float *>(out);
+            const float total = sqrtf((float)total_sq);
+            o[0] = total;
+            o[1] = total > 1.0f ? __fdiv_rn(1.0f, __fadd_rn(total, 1e-6f)) : 1.0f;
+        }
+        *counter = 0u;                                             // ready for the next launch on this lane
     }
 }
 
@@ -330,7 +350,6 @@ void prefer_gemm_compatible_carveout(zn_ctx *ctx) {
     const int c = cudaSharedmemCarveoutMaxShared;
     const cudaFuncAttribute at = cudaFuncAttributePreferredSharedMemoryCarveout;
     cudaFuncSetAttribute(sq_partial_kernel, at, c);
-    cudaFuncSetAttribute(norm_final_kernel, at, c);
     cudaFuncSetAttribute(norm_exact_kernel, at, c);
     cudaFuncSetAttribute(scale_kernel, at, c);
     cudaFuncSetAttribute(sgd_kernel<float>, at, c);
@@ -390,27 +409,15 @@ zn_status zn_k_grad_norm(zn_ctx *ctx, const zn_seg *segs, int nseg, float *norm_
         return ZN_OK;
     }
     ZN_TRY(zn_scratch_reserve(ctx, (size_t)blocks));
-    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 2);
-    sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch);
-    norm_final_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, blocks, norm_factor_dev);
+    unsigned int *counters = nullptr;
+    ZN_TRY(zn_lane_counters(ctx, &counters));
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 1);
+    sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch, counters + ZN_COUNTER_SUMSQ, 2, norm_factor_dev);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }
 
 namespace {
-
-__global__ void sumsq_final_kernel(const float *__restrict__ partial, int n, double *__restrict__ out) {
-    __shared__ double sm[TPB];
-    double s = 0.0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partial[i];
-    sm[threadIdx.x] = s;
-    __syncthreads();
-    for (int o = TPB / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *out = sm[0];
-}
 
 __global__ void norm_combine_kernel(const double *__restrict__ sums, int count, float *__restrict__ out) {
     double s = 0.0;
@@ -443,15 +450,16 @@ zn_status zn_k_sumsq(zn_ctx *ctx, const zn_seg *segs, int nseg, double *sumsq_de
         const uint64_t bit = 1ull << (ctx->device & 63);
         if (!(done_mask.load() & bit)) {
             done_mask.fetch_or(bit);
-            cudaFuncSetAttribute(sumsq_final_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(sq_partial_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaFuncSetAttribute(norm_combine_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaGetLastError();
         }
     }
     ZN_TRY(zn_scratch_reserve(ctx, (size_t)blocks));
-    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 2);
-    sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch);
-    sumsq_final_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, blocks, sumsq_dev);
+    unsigned int *counters = nullptr;
+    ZN_TRY(zn_lane_counters(ctx, &counters));
+    zn_launch_scope scope(ctx, ZN_PROF_GRAD_NORM, 0, bytes, 1);
+    sq_partial_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab, ctx->scratch, counters + ZN_COUNTER_SUMSQ, 1, sumsq_dev);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }
@@ -529,6 +537,83 @@ zn_status launch_state1(zn_ctx *ctx, const zn_opt_args &a) {
 }
 
 }   // namespace
+
+namespace {
+
+struct MultiUpdateTable {
+    zn_opt_args a[ZN_MULTI_UPDATE_MAX];
+    int kind[ZN_MULTI_UPDATE_MAX], is_bias[ZN_MULTI_UPDATE_MAX];
+    int first_block[ZN_MULTI_UPDATE_MAX + 1];
+    int n;
+};
+constexpr int MULTI_ELEMS_PER_BLOCK = TPB * 8;
+
+// One launch for every parameter tensor of a small network (where a launch costs more than the update itself).
+// Each block belongs to one tensor and walks its own 2048 elements with that tensor's rule.
+__global__ void multi_update_kernel(const __grid_constant__ MultiUpdateTable tab) {
+    int t = 0;
+    while (t + 1 < tab.n && (int)blockIdx.x >= tab.first_block[t + 1]) ++t;
+    const zn_opt_args &a = tab.a[t];
+    const int kind = tab.kind[t], is_bias = tab.is_bias[t];
+    const float f = a.factor_dev ? *a.factor_dev : 1.0f;
+    const size_t base = (size_t)((int)blockIdx.x - tab.first_block[t]) * MULTI_ELEMS_PER_BLOCK;
+    const size_t end = min(a.count, base + MULTI_ELEMS_PER_BLOCK);
+    const float omb1 = 1.0f - a.beta1, omb2 = 1.0f - a.beta2, omr = 1.0f - a.rho;
+    for (size_t i = base + threadIdx.x; i < end; i += TPB) {
+        float g = a.g[i], w = a.w[i];
+        bool write_g = f != 1.0f;
+        if (kind == 1) {
+            float m = a.m[i], v = a.v[i];
+            write_g = write_g || a.wd > 0.0f;
+            adam_one(a, f, omb1, omb2, g, w, m, v);
+            a.m[i] = m;
+            a.v[i] = v;
+        } else if (kind == 2) {
+            float st = a.m[i];
+            state1_one<STATE1_MOMENTUM>(a, f, omr, g, w, st);
+            a.m[i] = st;
+        } else if (kind == 4) {
+            float st = a.m[i];
+            write_g = write_g || a.wd > 0.0f;
+            state1_one<STATE1_RMSPROP>(a, f, omr, g, w, st);
+            a.m[i] = st;
+        } else {
+            sgd_one(a, f, is_bias, g, w);
+        }
+        if (write_g) a.g[i] = g;
+        a.w[i] = w;
+        if (a.shadow) {
+            if (a.shadow_bf16) store_shadow<__nv_bfloat16>(static_cast<__nv_bfloat16 *>(a.shadow), i, a.cols, a.ld_shadow, w);
+            else store_shadow<float>(static_cast<float *>(a.shadow), i, a.cols, a.ld_shadow, w);
+        }
+    }
+}
+
+}   // namespace
+
+zn_status zn_k_multi_update(zn_ctx *ctx, const zn_opt_args *args, const int *kinds, const int *is_bias, int count) {
+    if (count <= 0 || count > ZN_MULTI_UPDATE_MAX)
+        return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "multi update: 1..%d tensors supported", (int)ZN_MULTI_UPDATE_MAX);
+    MultiUpdateTable tab;
+    int blocks = 0;
+    double bytes = 0;
+    for (int i = 0; i < count; ++i) {
+        tab.a[i] = args[i];
+        tab.kind[i] = kinds[i];
+        tab.is_bias[i] = is_bias[i];
+        tab.first_block[i] = blocks;
+        blocks += (int)((args[i].count + MULTI_ELEMS_PER_BLOCK - 1) / MULTI_ELEMS_PER_BLOCK);
+        bytes += (kinds[i] == 1 ? 28.0 : kinds[i] == 0 ? 12.0 : 20.0) * (double)args[i].count;
+    }
+    tab.first_block[count] = blocks;
+    tab.n = count;
+    if (blocks == 0) return ZN_OK;
+    prefer_gemm_compatible_carveout(ctx);
+    zn_launch_scope scope(ctx, ZN_PROF_OPTIMIZER, 0, bytes);
+    multi_update_kernel<<<blocks, TPB, 0, ctx->stream>>>(tab);
+    ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
 
 zn_status zn_k_sgd_momentum(zn_ctx *ctx, const zn_opt_args &a) { return launch_state1<STATE1_MOMENTUM>(ctx, a); }
 zn_status zn_k_rmsprop(zn_ctx *ctx, const zn_opt_args &a) { return launch_state1<STATE1_RMSPROP>(ctx, a); }

@@ -134,6 +134,13 @@ __global__ void act_backward_t_kernel(int act, const T *__restrict__ y, int64_t 
     }
 }
 
+// exp and log of the exact mode.  The reference's CPU path calls its math library, whose float routines return the
+// correctly rounded result in all but isolated cases; the device's expf / logf are allowed 1-2 ulp.  One ulp in a
+// softmax is enough to send an Adam run down another path after a few dozen steps, so the exact mode evaluates in
+// double precision and rounds once, which gives the correctly rounded float in all but about one case in 10^8.
+__device__ __forceinline__ float exp_rounded_once(float x) { return (float)exp((double)x); }
+__device__ __forceinline__ float log_rounded_once(float x) { return (float)log((double)x); }
+
 // ---- row-wise softmax -------------------------------------------------------------------
 // Activation.softmaxForward (src/activation.zig:51-78) on every row of a block, the way Dense.forward
 // applies it sample by sample (src/layer.zig:398-406).  One warp per row.  `exact`: lane 0 takes the
@@ -150,7 +157,7 @@ __global__ void softmax_rows_kernel(const TIN *in, int64_t ld_in, TOUT *out_t, i
         if (exact) {
             if (lane == 0) {
                 for (int64_t c = 0; c < cols; ++c) { const float v = to_f32(x[c]); if (v > mx) mx = v; }
-                for (int64_t c = 0; c < cols; ++c) sum = __fadd_rn(sum, expf(__fsub_rn(to_f32(x[c]), mx)));
+                for (int64_t c = 0; c < cols; ++c) sum = __fadd_rn(sum, exp_rounded_once(__fsub_rn(to_f32(x[c]), mx)));
             }
             mx = __shfl_sync(0xffffffffu, mx, 0);
             sum = __shfl_sync(0xffffffffu, sum, 0);
@@ -163,7 +170,8 @@ __global__ void softmax_rows_kernel(const TIN *in, int64_t ld_in, TOUT *out_t, i
         const bool ok = sum > 0.f;                       // false also for NaN: uniform, as the reference
         const float uniform = __fdiv_rn(1.0f, (float)cols);
         for (int64_t c = lane; c < cols; c += 32) {
-            const float v = ok ? __fdiv_rn(expf(__fsub_rn(to_f32(x[c]), mx)), sum) : uniform;
+            const float ex = exact ? exp_rounded_once(__fsub_rn(to_f32(x[c]), mx)) : expf(__fsub_rn(to_f32(x[c]), mx));
+            const float v = ok ? __fdiv_rn(ex, sum) : uniform;
             if (out_t) out_t[r * ld_t + c] = from_f32<TOUT>(v);
             if (out_f32) out_f32[r * ld_f + c] = v;
         }
@@ -207,11 +215,16 @@ __global__ void bias_reduce_exact_kernel(const T *__restrict__ g, int64_t ld, in
 
 // Stage 1: block (strip, split) sums rows [split*rows_per, ...) of a 32*VEC-column strip.
 // Each warp walks rows warp, warp+8, ...; a lane owns VEC adjacent columns (16 bytes).
+// With `counters` (one per strip, zero between launches) the block of a strip that finishes last also adds the
+// strip's partial sums up, in split order, and writes gb: the whole reduction in one launch.  Without, stage 2 is
+// the kernel below.  Either way the additions are the same ones in the same order.
 template <typename T, int VEC>
 __global__ void bias_reduce_partial_kernel(const T *__restrict__ g, int64_t ld, int64_t rows, int64_t cols,
-                                           int64_t rows_per, float *__restrict__ partial) {
+                                           int64_t rows_per, float *__restrict__ partial, float *__restrict__ gb,
+                                           int accumulate, unsigned int *counters) {
     constexpr int STRIP = 32 * VEC;
     __shared__ float sm[TPB / 32][STRIP];
+    __shared__ bool last;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int64_t c0 = (int64_t)blockIdx.x * STRIP + lane * VEC;
     const int64_t r_begin = (int64_t)blockIdx.y * rows_per;
@@ -251,6 +264,21 @@ __global__ void bias_reduce_partial_kernel(const T *__restrict__ g, int64_t ld, 
         const int64_t gc = (int64_t)blockIdx.x * STRIP + c;
         if (gc < cols) partial[(int64_t)blockIdx.y * cols + gc] = s;
     }
+    if (!counters) return;
+    __threadfence();                                   // this block's partial sums are visible before its arrival is
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&counters[blockIdx.x], 1u) == gridDim.y - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int c = threadIdx.x; c < STRIP; c += TPB) {
+        const int64_t gc = (int64_t)blockIdx.x * STRIP + c;
+        if (gc >= cols) continue;
+        float s = 0.f;
+        for (unsigned int i = 0; i < gridDim.y; ++i) s += __ldcg(partial + (int64_t)i * cols + gc);
+        gb[gc] = accumulate ? gb[gc] + s : s;
+    }
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0u;   // ready for the next launch on this lane
 }
 
 // Stage 2: gb[c] (+)= sum over splits, in split order.
@@ -265,11 +293,42 @@ __global__ void bias_reduce_final_kernel(const float *__restrict__ partial, int6
 
 // ---- losses ---------------------------------------------------------------------------------
 
+// End of a loss kernel: the block's partial sum is stored; with an arrival counter the block that arrives last also
+// adds all partial sums up (double, fixed order: thread i takes partial[i], partial[i + TPB], ..., then a tree) and
+// writes the loss sum, so the loss needs no second launch.  Called by every thread of the block.
+__device__ __forceinline__ void finish_loss_sum(float block_total, float *partial, float *loss_sum, unsigned int *counter) {
+    __shared__ double fin[TPB];
+    __shared__ bool last;
+    if (threadIdx.x == 0) {
+        partial[blockIdx.x] = block_total;
+        if (counter) {
+            __threadfence();
+            last = atomicAdd(counter, 1u) == gridDim.x - 1;
+        }
+    }
+    if (!counter) return;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    double s = 0.0;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) s += (double)__ldcg(partial + i);
+    fin[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = TPB / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) fin[threadIdx.x] += fin[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        *loss_sum = (float)fin[0];
+        *counter = 0u;
+    }
+}
+
 // MSE (src/loss.zig:93-109): grad = 2*(o-t)/n, partial[block] = sum (o-t)^2 over the block's elements.
 template <typename T>
 __global__ void mse_kernel(const float *__restrict__ out, int64_t ld_o, const float *__restrict__ target,
                            T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float n_div,
-                           float *__restrict__ partial) {
+                           float *__restrict__ partial, float *loss_sum, unsigned int *counter) {
     const int64_t total = rows * cols;
     float s = 0.f;
     const bool flat = (ld_o == cols) && (!grad || ld_g == cols);
@@ -303,7 +362,7 @@ __global__ void mse_kernel(const float *__restrict__ out, int64_t ld_o, const fl
         }
     }
     s = block_sum(s);
-    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+    finish_loss_sum(s, partial, loss_sum, counter);
 }
 
 // Binary cross-entropy on probabilities (src/loss.zig:255-302): p clamped to [1e-7, 1 - 1e-7], so is 1 - p;
@@ -322,7 +381,7 @@ __device__ __forceinline__ float bce_term(float o, float t, float &p) {
 template <typename T>
 __global__ void bce_kernel(const float *__restrict__ out, int64_t ld_o, const float *__restrict__ target,
                            T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float n_div,
-                           float *__restrict__ partial) {
+                           float *__restrict__ partial, float *loss_sum, unsigned int *counter) {
     const int64_t total = rows * cols;
     float s = 0.f;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -333,7 +392,7 @@ __global__ void bce_kernel(const float *__restrict__ out, int64_t ld_o, const fl
         if (grad) grad[r * ld_g + c] = from_f32<T>(__fdiv_rn(__fsub_rn(p, t), n_div));
     }
     s = block_sum(s);
-    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+    finish_loss_sum(s, partial, loss_sum, counter);
 }
 
 // Row loss of Loss.crossEntropyForward (src/loss.zig:110-169), the variant WITHOUT "_logits" in its name,
@@ -350,7 +409,7 @@ __device__ __forceinline__ float ce_plain_row_loss(float mx, float sum_clamped, 
 template <typename T>
 __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const float *__restrict__ target,
                           T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float *__restrict__ partial,
-                          int exact, int plain) {
+                          int exact, int plain, float *loss_sum, unsigned int *counter) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     float loss_acc = 0.f;
     for (int64_t r = (int64_t)blockIdx.x * wpb + w; r < rows; r += (int64_t)gridDim.x * wpb) {
@@ -368,14 +427,16 @@ __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const 
         se = warp_sum(se);
         if (exact) {   // the reference's order: one running sum over the columns (src/loss.zig:243-247)
             se = 0.f;
-            for (int64_t c = 0; c < cols; ++c) se = __fadd_rn(se, expf(__fsub_rn(l[c], mx)));
+            for (int64_t c = 0; c < cols; ++c) se = __fadd_rn(se, exp_rounded_once(__fsub_rn(l[c], mx)));
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
         if (grad) {
             T *g = grad + r * ld_g;
-            for (int64_t c = lane; c < cols; c += 32)
-                g[c] = from_f32<T>(__fsub_rn(__fdiv_rn(expf(l[c] - mx), se), t[c]));
+            for (int64_t c = lane; c < cols; c += 32) {
+                const float e = exact ? exp_rounded_once(__fsub_rn(l[c], mx)) : expf(l[c] - mx);
+                g[c] = from_f32<T>(__fsub_rn(__fdiv_rn(e, se), t[c]));
+            }
         }
         if (!plain) {
             if (lane == 0 && first != INT64_MAX) loss_acc += -(l[first] - (logf(se) + mx));
@@ -393,7 +454,7 @@ __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const 
         }
     }
     loss_acc = block_sum(loss_acc);
-    if (threadIdx.x == 0) partial[blockIdx.x] = loss_acc;
+    finish_loss_sum(loss_acc, partial, loss_sum, counter);
 }
 
 // FP32_EXACT mode: the loss SUM in the reference's order.  MSE: one running f32 sum of (o-t)^2 over all
@@ -417,8 +478,8 @@ __global__ void loss_sum_exact_kernel(int loss, const float *__restrict__ out, i
             float mx = -INFINITY;
             for (int64_t c = 0; c < cols; ++c) if (o[c] > mx) mx = o[c];
             float sec = 0.f;
-            for (int64_t c = 0; c < cols; ++c) sec = __fadd_rn(sec, expf(fminf(50.f, fmaxf(-50.f, __fsub_rn(o[c], mx)))));
-            const float lse = __fadd_rn(logf(sec), mx);
+            for (int64_t c = 0; c < cols; ++c) sec = __fadd_rn(sec, exp_rounded_once(fminf(50.f, fmaxf(-50.f, __fsub_rn(o[c], mx)))));
+            const float lse = __fadd_rn(log_rounded_once(sec), mx);
             float ls = 0.f, cnt = 0.f;
             for (int64_t c = 0; c < cols; ++c)
                 if (t[c] > 0.5f) { ls = __fadd_rn(ls, __fsub_rn(lse, o[c])); cnt += 1.f; }
@@ -427,28 +488,14 @@ __global__ void loss_sum_exact_kernel(int loss, const float *__restrict__ out, i
             float mx = o[0];
             for (int64_t c = 1; c < cols; ++c) if (o[c] > mx) mx = o[c];
             float se = 0.f;
-            for (int64_t c = 0; c < cols; ++c) se = __fadd_rn(se, expf(__fsub_rn(o[c], mx)));
-            const float lse = __fadd_rn(logf(se), mx);
+            for (int64_t c = 0; c < cols; ++c) se = __fadd_rn(se, exp_rounded_once(__fsub_rn(o[c], mx)));
+            const float lse = __fadd_rn(log_rounded_once(se), mx);
             float l = 0.f;
             for (int64_t c = 0; c < cols; ++c) if (t[c] > 0.5f) { l = -(__fsub_rn(o[c], lse)); break; }
             total = __fadd_rn(total, l);
         }
     }
     *result = total;
-}
-
-__global__ void sum_partials_kernel(const float *__restrict__ partial, int n, float *__restrict__ out) {
-    // one block; double accumulation in a fixed order
-    __shared__ double sm[TPB];
-    double s = 0.0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partial[i];
-    sm[threadIdx.x] = s;
-    __syncthreads();
-    for (int o = TPB / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *out = (float)sm[0];
 }
 
 // The column reduction runs on a side lane underneath the persistent GEMM, whose CTAs need the SM set up
@@ -590,13 +637,17 @@ zn_status zn_k_bias_reduce(zn_ctx *ctx, const void *g, bool g_bf16, int64_t ld, 
     const int64_t rows_per = (rows + splits - 1) / splits;
     splits = (rows + rows_per - 1) / rows_per;
     ZN_TRY(zn_scratch_reserve(ctx, (size_t)(splits * cols)));
-    zn_launch_scope scope(ctx, ZN_PROF_BIAS_REDUCE, 0, bytes, 2);
+    // one launch when every strip has an arrival counter of its own, else the two-kernel form
+    unsigned int *counters = nullptr;
+    if (strips <= ZN_COUNTER_SUMSQ) ZN_TRY(zn_lane_counters(ctx, &counters));
+    zn_launch_scope scope(ctx, ZN_PROF_BIAS_REDUCE, 0, bytes, counters ? 1 : 2);
     dim3 grid((unsigned)strips, (unsigned)splits);
     if (g_bf16)
-        bias_reduce_partial_kernel<__nv_bfloat16, 8><<<grid, TPB, 0, ctx->stream>>>((const __nv_bfloat16 *)g, ld, rows, cols, rows_per, ctx->scratch);
+        bias_reduce_partial_kernel<__nv_bfloat16, 8><<<grid, TPB, 0, ctx->stream>>>((const __nv_bfloat16 *)g, ld, rows, cols, rows_per, ctx->scratch, gb, accumulate ? 1 : 0, counters);
     else
-        bias_reduce_partial_kernel<float, 4><<<grid, TPB, 0, ctx->stream>>>((const float *)g, ld, rows, cols, rows_per, ctx->scratch);
-    bias_reduce_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(ctx->scratch, cols, (int)splits, gb, accumulate);
+        bias_reduce_partial_kernel<float, 4><<<grid, TPB, 0, ctx->stream>>>((const float *)g, ld, rows, cols, rows_per, ctx->scratch, gb, accumulate ? 1 : 0, counters);
+    if (!counters)
+        bias_reduce_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(ctx->scratch, cols, (int)splits, gb, accumulate);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }
@@ -683,7 +734,8 @@ extern "C" zn_status zn_accumulate_bias_noalloc(zn_ctx *ctx, float *grad_bias, s
     if (!scratch) return st;
     ctx->launches += 2;
     dim3 grid((unsigned)strips, (unsigned)splits);
-    bias_reduce_partial_kernel<float, 4><<<grid, TPB, 0, ctx->stream>>>(g, cols, rows, cols, rows_per, scratch);
+    // two kernels and no arrival counters: the counters of the one-launch form live in memory the context allocates
+    bias_reduce_partial_kernel<float, 4><<<grid, TPB, 0, ctx->stream>>>(g, cols, rows, cols, rows_per, scratch, nullptr, 0, nullptr);
     bias_reduce_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(scratch, cols, (int)splits, grad_bias, 1);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
@@ -700,26 +752,32 @@ zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const
     else if (flat) grid = grid_for(ctx, total, 4);
     else grid = grid_for(ctx, rows * 32, 8);
     ZN_TRY(zn_scratch_reserve(ctx, (size_t)grid));
-    zn_launch_scope scope(ctx, ZN_PROF_LOSS, 0, (double)total * (8 + (grad ? (grad_bf16 ? 2 : 4) : 0)), 2);
+    // the loss sum is formed by the last block of the loss kernel itself; the exact mode forms it in the
+    // reference's order with a kernel of its own
+    unsigned int *counter = nullptr;
+    if (!exact) {
+        ZN_TRY(zn_lane_counters(ctx, &counter));
+        counter += ZN_COUNTER_LOSS;
+    }
+    zn_launch_scope scope(ctx, ZN_PROF_LOSS, 0, (double)total * (8 + (grad ? (grad_bf16 ? 2 : 4) : 0)), exact ? 2 : 1);
     if (loss == ZN_LOSS_MSE) {
         if (grad_bf16)
-            mse_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+            mse_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch, loss_sum_dev, counter);
         else
-            mse_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+            mse_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch, loss_sum_dev, counter);
     } else if (loss == ZN_LOSS_BINARY_CROSS_ENTROPY) {
         if (grad_bf16)
-            bce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+            bce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch, loss_sum_dev, counter);
         else
-            bce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch);
+            bce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, mse_divisor, ctx->scratch, loss_sum_dev, counter);
     } else {
         const int plain = loss == ZN_LOSS_CROSS_ENTROPY ? 1 : 0;
         if (grad_bf16)
-            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain);
+            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain, loss_sum_dev, counter);
         else
-            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain);
+            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain, loss_sum_dev, counter);
     }
     if (exact) loss_sum_exact_kernel<<<1, 1, 0, ctx->stream>>>(loss, out, ld_o, target, rows, cols, loss_sum_dev);
-    else sum_partials_kernel<<<1, TPB, 0, ctx->stream>>>(ctx->scratch, grid, loss_sum_dev);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }

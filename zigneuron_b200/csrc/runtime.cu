@@ -118,6 +118,7 @@ extern "C" void zn_ctx_destroy(zn_ctx *ctx) {
     for (int i = 0; i < 6; ++i) cudaFree(ctx->stage[i]);
     cudaFree(ctx->scratch);
     cudaFree(ctx->tile_counters);
+    cudaFree(ctx->block_counters);
     for (int i = 1; i < 4; ++i) cudaFree(ctx->lanes[i].scratch);
     for (int i = 0; i < 4; ++i)
         if (ctx->lane_join[i]) cudaEventDestroy(ctx->lane_join[i]);
@@ -212,6 +213,16 @@ bool zn_is_device_ptr(const void *p) {
         return false;
     }
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+zn_status zn_lane_counters(zn_ctx *ctx, unsigned int **out) {
+    if (!ctx->block_counters) {
+        const size_t bytes = 4 * ZN_COUNTERS_PER_LANE * sizeof(unsigned int);
+        ZN_CUDA(ctx, cudaMalloc((void **)&ctx->block_counters, bytes));
+        ZN_CUDA(ctx, cudaMemset(ctx->block_counters, 0, bytes));      // synchronous: cleared before any lane uses it
+    }
+    *out = ctx->block_counters + ctx->lane * ZN_COUNTERS_PER_LANE;
+    return ZN_OK;
 }
 
 // Device that owns a device pointer, or -1 for host memory and unknown addresses.

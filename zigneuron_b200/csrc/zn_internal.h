@@ -72,6 +72,9 @@ struct zn_ctx {
     // on the main stream (each launch clears the one the next launch will use).
     unsigned int *tile_counters = nullptr;
     unsigned int tile_counter_turn = 0;
+    // Arrival counters of the reductions that finish in their own last block (column sums, sums of squares, loss
+    // sums): 1024 per lane, all zero between launches (the block that finishes a reduction clears what it used).
+    unsigned int *block_counters = nullptr;
 
     zn_dp_state *dp = nullptr;
 };
@@ -114,6 +117,9 @@ zn_status zn_sync_all_lanes(zn_ctx *ctx);         // host waits for every lane
 zn_status zn_join_lanes_into_main(zn_ctx *ctx);   // the main stream waits (on the device) for the other lanes
 
 zn_status zn_scratch_reserve(zn_ctx *ctx, size_t floats);
+// The active lane's 1024 arrival counters (allocated and cleared on first use); see zn_ctx::block_counters.
+enum { ZN_COUNTERS_PER_LANE = 1024, ZN_COUNTER_SUMSQ = 1000, ZN_COUNTER_LOSS = 1001 };   // [0, 1000): column strips
+zn_status zn_lane_counters(zn_ctx *ctx, unsigned int **out);
 zn_status zn_check_device_status(zn_ctx *ctx);   // reads the pinned status word after a sync
 bool zn_is_device_ptr(const void *p);
 int zn_ptr_device(const void *p);                 // owning device of a device pointer, -1 for host memory
@@ -199,6 +205,11 @@ struct zn_opt_args {
     bool shadow_bf16;
     int64_t cols, ld_shadow;        // shadow[(i / cols) * ld_shadow + i % cols]
 };
+// Every parameter tensor of a small network in ONE launch: `kinds[i]` says which update tensor i gets
+// (0 sgd, 1 adam / adamw, 2 momentum sgd, 4 rmsprop; the OPT_* values of net.cu), is_bias[i] selects the plain
+// SGD bias rule.  At most ZN_MULTI_UPDATE_MAX tensors.  Same arithmetic per element as the kernels below.
+enum { ZN_MULTI_UPDATE_MAX = 16 };
+zn_status zn_k_multi_update(zn_ctx *ctx, const zn_opt_args *args, const int *kinds, const int *is_bias, int count);
 zn_status zn_k_sgd(zn_ctx *ctx, const zn_opt_args &a, bool is_bias);
 zn_status zn_k_adam(zn_ctx *ctx, const zn_opt_args &a);
 zn_status zn_k_sgd_momentum(zn_ctx *ctx, const zn_opt_args &a);
