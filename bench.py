@@ -37,7 +37,35 @@ BLOCK_ROWS = 1024                     # data is generated in blocks of rows keye
 SUM_IO = sum(a * b for a, b in DIMS)  # 201,326,592
 PARAMS = SUM_IO + sum(b for _, b in DIMS)
 FLOP_PER_SAMPLE = 6.0 * SUM_IO        # forward + dX + dW GEMMs, the reference's dX of layer 0 included
-NCU_DRAM_BYTES_PER_FLOP = 465.4e6 / (2.0 * 8192 * 8192 * 4096)   # dram read+write of one captured GEMM launch / its flops
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, ncu, --clock-control none) of the step's twelve GEMM
+# launches, captured on this network with 8192 rows per launch, in launch order: forward of layers 0-3, then per
+# layer from the last to the first the weight-gradient product (TN) and the input-gradient product (NT).  Rows are
+# M of the NN / NT products and K of the TN products, and both the tiles a launch walks and the strips it streams
+# grow in proportion to them, so a launch with R rows moves R / 8192 times these bytes.
+NCU_ROWS = 8192
+NCU_GEMM_DRAM_BYTES = {   # (orientation, m, n, k at 8192 rows): measured DRAM bytes
+    ("NN", "rows", 8192, 4096): 334.9e6, ("NN", "rows", 8192, 8192): 1370.5e6, ("NN", "rows", 4096, 8192): 806.4e6,
+    ("TN", 8192, 4096, "rows"): 798.3e6, ("TN", 8192, 8192, "rows"): 1499.4e6, ("TN", 4096, 8192, "rows"): 737.3e6,
+    ("NT", "rows", 8192, 4096): 522.8e6, ("NT", "rows", 8192, 8192): 1518.8e6, ("NT", "rows", 4096, 8192): 744.8e6,
+}
+
+
+def step_gemms(rows, bf16_out=2, f32=4):
+    """The twelve GEMM launches of one step on `rows` rows: (orientation, key into NCU_GEMM_DRAM_BYTES, flops,
+    algorithmic bytes = every operand read once + the output written once, bf16 operands, the relu mask of the
+    input-gradient products included)."""
+    out = []
+    L = len(DIMS)
+    for i, (a, b) in enumerate(DIMS):                      # forward: rows x b x a
+        last = i + 1 == L
+        alg = 2 * (rows * a + a * b) + (f32 if last else bf16_out) * rows * b
+        out.append(("NN", ("NN", "rows", b, a), 2.0 * rows * a * b, alg))
+    for i in range(L - 1, -1, -1):
+        a, b = DIMS[i]
+        out.append(("TN", ("TN", a, b, "rows"), 2.0 * rows * a * b, 2 * (rows * a + rows * b) + f32 * a * b))
+        mask = 2 * rows * a if i > 0 else 0
+        out.append(("NT", ("NT", "rows", a, b), 2.0 * rows * a * b, 2 * (rows * b + a * b) + mask + 2 * rows * a))
+    return out
 
 
 def layer_weights(layer):
@@ -476,10 +504,7 @@ def run_ours(args):
                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak if peak else None, "peak_source": f"{peaks['source']}, sustained bf16",
                      "launches": g["launches"], "avg_launch_ms": g["ms"] / max(1, g["launches"]),
-                     # DRAM bytes of one launch: ncu capture of the 8192x8192x4096 case (465 MB for 0.55 TFLOP,
-                     # profiles/gemm_tc_pair_bf16_8192x8192x4096_full.md) scaled by the flops of an average launch here
-                     "traffic": NCU_DRAM_BYTES_PER_FLOP * g["flops"] / max(1, g["launches"]),
-                     "traffic_unit": "bytes per launch (scaled from a smaller ncu capture)"},
+                     **gemm_traffic(rows)},
         "kernel_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
         "kernel_ms_note": "gemm, loss and convert run on the main stream and add up to the step; optimizer, bias_reduce and "
                           "grad_norm run on side streams underneath the GEMMs, so their durations (and GB/s) are stretched "
@@ -520,6 +545,27 @@ def run_ours(args):
         dist.destroy_process_group()
     if failed:
         raise SystemExit("dp_check failed: " + json.dumps(check))
+
+
+def gemm_traffic(rows):
+    """roofline.traffic: measured DRAM bytes per launch (average over the step's twelve GEMMs) beside the algorithmic
+    bytes, and the same per orientation."""
+    gemms = step_gemms(rows)
+    scale = rows / NCU_ROWS
+    per = {}
+    for orient, key, _, alg in gemms:
+        d = per.setdefault(orient, {"launches": 0, "traffic": 0.0, "algorithmic": 0.0})
+        d["launches"] += 1
+        d["traffic"] += NCU_GEMM_DRAM_BYTES[key] * scale
+        d["algorithmic"] += alg
+    total = sum(d["traffic"] for d in per.values())
+    total_alg = sum(d["algorithmic"] for d in per.values())
+    for d in per.values():
+        d["ratio"] = d["traffic"] / d["algorithmic"]
+    return {"traffic": total / len(gemms), "algorithmic_bytes": total_alg / len(gemms), "traffic_over_algorithmic": total / total_alg,
+            "traffic_unit": f"DRAM bytes per launch, average of the 12 GEMMs of a step; ncu capture at {NCU_ROWS} rows per launch "
+                            f"scaled by rows / {NCU_ROWS} (bytes are linear in the rows at fixed layer widths)",
+            "traffic_by_orientation": per}
 
 
 def run_gemm_sweep(args):

@@ -473,3 +473,58 @@ def test_add_dense_initial_distribution(be, act, scale_of):
     assert abs(W.var() - scale ** 2 / 3) <= 0.03 * scale ** 2 / 3          # U(-s, s) has variance s^2 / 3
     assert abs(np.corrcoef(W.ravel(), W2.T.ravel()[:W.size])[0, 1]) < 0.02
     net.deinit()
+
+
+_COMPACT_SNIPPET = r"""
+import sys
+import numpy as np
+sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+import zigneuron_b200 as zn
+from oracle import zn_oracle as zo
+from util import assert_close, reference_init
+P = zn.Precision
+be = zn.Backend(0)
+dims, acts = [(20, 48), (48, 24), (24, 6)], ["relu", "relu", "linear"]
+rng = np.random.default_rng(9)
+x = rng.standard_normal((64, 20)).astype(np.float32)
+t = np.eye(6, dtype=np.float32)[rng.integers(0, 6, 64)]
+OPT = {{"sgd": (zn.Sgd(), lambda o, i: None), "adam": (zn.Adam(), lambda o, i: o.set_adam(i)),
+       "momentum": (zn.Sgd(momentum=0.9), lambda o, i: o.set_sgd_momentum(i, 0.9)),
+       "adamw": (zn.AdamW(weight_decay=0.05), lambda o, i: o.set_adamw(i, 0.9, 0.999, 1e-8, 0.05)),
+       "rmsprop": (zn.Rmsprop(rho=0.8, weight_decay=0.01), lambda o, i: o.set_rmsprop(i, 0.8, 1e-8, 0.01))}}
+for name, (gopt, oset) in OPT.items():
+    for prec, tol in ((P.FP32_SIMT, 2e-5), (P.BF16_TC, 2e-2)):
+        wr = np.random.default_rng(3)
+        gnet, onet = zn.Network(be, prec), zo.Net()
+        for i, ((a, b), act) in enumerate(zip(dims, acts)):
+            gnet.addDense(a, b, act)
+            onet.add_dense(a, b, zo.RELU if act == "relu" else zo.LINEAR)
+            W, bias = reference_init(wr, a, b, act), wr.uniform(-0.1, 0.1, b).astype(np.float32)
+            gnet.setWeights(i, W, bias)
+            onet.set_params(i, W, bias)
+            oset(onet, i)
+        gnet.setOptimizer(gopt)
+        n0 = be.launch_count()
+        for step in range(3):
+            lg = gnet.trainStep(x, t, 0.01, zn.Loss.cross_entropy_logits)
+            lo = onet.train_step(x, t, 64, 0.01, zo.CE_LOGITS)
+            assert abs(lg - lo) <= tol * max(1.0, abs(lo)), (name, prec.name, step, lg, lo)
+        launches = (be.launch_count() - n0) / 3
+        assert launches <= 16 + (1 if prec == P.BF16_TC else 0), (name, launches)   # 3 layers: 3 + 1 + 9 + 1 + 1 (+ input conversion)
+        for i in range(3):
+            assert_close(gnet.getWeights(i)[0], onet.get_params(i)[0], tol * (25 if name != "sgd" else 1), f"{{name}} {{prec.name}} W{{i}}")
+        gnet.deinit()
+print("compact step ok")
+"""
+
+
+def test_compact_single_stream_step_in_a_subprocess():
+    """ZN_COMPACT_STEP=1 (read once per process): the step of a small network on one stream, one norm launch, one
+    update launch for all tensors.  Every optimizer against the oracle, and the launch count it exists for."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = _COMPACT_SNIPPET.format(root=root, tests=os.path.join(root, "tests"))
+    r = subprocess.run([sys.executable, "-c", code], env={**os.environ, "ZN_COMPACT_STEP": "1"}, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "compact step ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]

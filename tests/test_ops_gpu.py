@@ -117,7 +117,10 @@ def test_gemm_tensor_core(be, prec, orient, shape):
     rnd = round_bf16 if prec == P.BF16_TC else trunc_tf32
     sa, sb = _store(orient, rnd(a), rnd(b))
     want = _oracle(orient, sa, sb, m, n, k)
-    assert_close(_gpu(be, orient, sa, sb, m, n, k), want, 1e-5, f"{prec.name} {orient} {shape} pre-rounded")
+    # The tensor cores add their products into fp32 without rounding every partial sum to nearest, so what is left
+    # grows with the length of the sum: measured 1.08e-5 (tf32) at K = 4100, below 5e-6 up to K = 2304.
+    tol = 1e-5 * max(1.0, (k / 1024.0) ** 0.5)
+    assert_close(_gpu(be, orient, sa, sb, m, n, k), want, tol, f"{prec.name} {orient} {shape} pre-rounded")
 
 
 @pytest.mark.parametrize("prec", [P.FP32_EXACT, P.FP32_SIMT, P.TF32_TC, P.BF16_TC])

@@ -1,12 +1,15 @@
 // tcgen05 / TMEM GEMM for the three Dense products on sm_100a.
 //
 // One persistent CTA per SM walks 128 x 256 output tiles.  Warp 0 feeds a
-// 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
+// 3-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
 // every CTA loads its own tiles); one thread of warp 1 issues tcgen05.mma (cta_group::1, M=128,
 // N=256) into one of two 256-column fp32 accumulators in tensor memory; warps
 // 2..5 drain the other accumulator with tcgen05.ld and apply the fused epilogue
 // (bias, activation, activation-derivative mask, accumulate, down-convert), so
-// the epilogue of tile i overlaps the main loop of tile i+1.
+// the epilogue of tile i overlaps the main loop of tile i+1.  Results leave through
+// shared memory and bulk tensor stores (whole 128-byte lines) or, where that is not
+// possible, as per-thread stores.  A two-CTA variant of the same kernel (further
+// down) takes every product with a long main loop.
 //
 // The three orientations of the reference (Backend.matMul, matMulTransposeB,
 // matMulTransposeA; src/backend.zig:169-195, :298-325) differ only in which
@@ -33,7 +36,7 @@
 namespace {
 
 constexpr int BM = 128, BN = 256;
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;                           // one-CTA kernel: 3 x 48 KiB of operands beside 32 KiB of output staging
 constexpr int TQ = 4;                               // depth of the tile-index ring inside a CTA
 constexpr int ROW_BYTES = 128;                    // one swizzle row
 constexpr int A_STAGE = BM * ROW_BYTES;           // 16 KiB
@@ -42,7 +45,12 @@ constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int BIAS_SMEM = 4 * BN * 4;                 // one tile's bias values, a private copy per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + BIAS_SMEM;
+constexpr int STG_BUF = 4096;                         // one staged 32 x 32 output block (fp32; 16-bit blocks use half)
+constexpr int STAGING_BYTES = 4 * 2 * STG_BUF;        // two blocks per epilogue warp
+// after the operand ring: barriers (256 B), the bias strips, then (1024-aligned) the output staging buffers
+constexpr int RING_TAIL = ((256 + BIAS_SMEM + 1023) / 1024) * 1024;
+constexpr int SMEM_BYTES = 1024 /* alignment slack */ + STAGES * STAGE_BYTES + RING_TAIL + STAGING_BYTES;
+static_assert(SMEM_BYTES <= 232448, "the one-CTA kernel must fit the 227 KB of shared memory a CTA may have");
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
 struct TcParams {
@@ -71,11 +79,35 @@ struct TcParams {
     // TMA unit (tensor map tmC), which writes whole 128-byte lines and clips at the edges of C.
     int out_mode;
     int band;                // m-tiles per band of the tile order (see tile_coords)
+#ifdef ZN_DIAG
+    unsigned long long *phase_ts;   // diagnostic builds: CTA 0 of the one-CTA kernel writes %globaltimer per phase here
+#endif
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+#ifdef ZN_DIAG
+// diagnostic builds: nanosecond time stamp of one phase of CTA 0 (first visit only)
+#define ZN_PHASE(p, i)                                                                                 \
+    do {                                                                                               \
+        if ((p).phase_ts && blockIdx.x == 0 && (p).phase_ts[i] == 0ull) {                              \
+            unsigned long long t__;                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                    \
+            (p).phase_ts[i] = t__;                                                                     \
+        }                                                                                              \
+    } while (0)
+// diagnostic builds: SM clock of one point of the epilogue of block `c` (warp 2, lane 0 of CTA 0), posted to device memory
+__device__ long long zn_diag_clk[128];
+#define ZN_CLK(c, point)                                                                               \
+    do {                                                                                               \
+        if (blockIdx.x == 0 && threadIdx.x == 64 && (c) < 8) zn_diag_clk[(c) * 8 + (point)] = clock64(); \
+    } while (0)
+#else
+#define ZN_PHASE(p, i) do { } while (0)
+#define ZN_CLK(c, point) do { } while (0)
+#endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -163,7 +195,6 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // at most N of this thread's bulk groups may still be READING their shared-memory source
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // orders this thread's ordinary shared-memory writes before later reads of them by the TMA unit
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -207,19 +238,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// The same wait, written so that the compiler treats the 32 registers of an earlier tc_ld32 as produced HERE: no
-// read of them can be scheduled above the wait when other work sits between the load and the wait.
-__device__ __forceinline__ void tc_wait_ld_into(uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.wait::ld.sync.aligned;"
-        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-        :
-        : "memory");
-}
-
 // Shared-memory matrix descriptor, descriptor version 1.  layout_type 2 = 128-byte swizzle on 16-byte
 // units; 1 = 128-byte swizzle on 32-byte units, the only swizzled layout the tensor cores accept for an
 // MN-major operand of a 32-bit type (tf32).  lbo / sbo in bytes.
@@ -438,9 +456,6 @@ __device__ __forceinline__ const float *stage_bias(const TcParams &p, float *bia
 // position j ^ (r & 7); 16-bit: 64-byte rows, unit j at j ^ ((r >> 1) & 3)), which also spreads the 16-byte stores
 // of a quarter warp over all 32 banks.  Lane 0 then issues one bulk tensor store per block and keeps at most one
 // store reading shared memory behind it, so the warp returns to the next accumulator words at once.
-constexpr int STG_BUF = 4096;
-constexpr int STAGING_BYTES = 4 * 2 * STG_BUF;
-
 __device__ __forceinline__ void stage_block_f32(uint32_t buf, int lane, const float (&v)[32]) {
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -460,10 +475,47 @@ __device__ __forceinline__ void stage_block_bf16(uint32_t buf, int lane, const f
     }
 }
 
+// One 32 x 32 block of results of one epilogue warp through shared memory and the TMA unit.  `stores` counts the
+// blocks this warp has handed over so far (it picks the buffer and tells when a buffer's previous store must have
+// finished reading it).  Rows at or below M inside the block are written as zeros and dropped by the store.
+template <bool TF32>
+__device__ __forceinline__ void staged_block(const TcParams &p, const CUtensorMap *tmC, uint32_t warp_staging, int lane,
+                                             int warp_row0, int col0, const uint32_t (&r)[32], const float *bias_s,
+                                             uint32_t &stores, int c = 0 /* block number, diagnostic builds only */) {
+    float v[32];
+    const long long row = (long long)warp_row0 + lane;
+    ZN_CLK(c, 1);
+    if (row < p.M) epilogue_values<TF32>(p, row, col0, r, bias_s, v);
+    else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    }
+    ZN_CLK(c, 2);
+    const uint32_t sbuf = warp_staging + (stores & 1u) * STG_BUF;
+    if (stores >= 2) {                       // the store that last used this buffer has read it
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+    }
+    ZN_CLK(c, 3);
+    if (p.out_mode == 1) stage_block_f32(sbuf, lane, v);
+    else stage_block_bf16(sbuf, lane, v);
+    ZN_CLK(c, 4);
+    fence_proxy_async_smem();
+    ZN_CLK(c, 5);
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(tmC, col0, warp_row0, sbuf);
+        bulk_commit();
+    }
+    ZN_CLK(c, 6);
+    ++stores;
+}
+
 // ET: operand element type (__nv_bfloat16 or float-as-tf32).
 template <typename ET>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const TcParams p) {
     constexpr bool TF32 = sizeof(ET) == 4;
     constexpr int ES = sizeof(ET);
     constexpr int BK = ROW_BYTES / ES;            // k elements per stage: 64 bf16 / 32 tf32
@@ -488,12 +540,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *tile_ring = reinterpret_cast<volatile int *>(tmem_slot + 2);
     float *bias_smem = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256);
+    const uint32_t staging = base + STAGES * STAGE_BYTES + RING_TAIL;      // 1024-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    if (threadIdx.x == 0) ZN_PHASE(p, 0);
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        if (p.out_mode) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
         for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }   // MMA thread + 4 epilogue warps
@@ -511,6 +566,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) ZN_PHASE(p, 1);
 
     const int num_tiles = p.num_m_tiles * p.num_n_tiles;
     const int nkb = p.num_k_blocks;
@@ -542,6 +598,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    ZN_PHASE(p, 2);
                     const int k0 = kb * BK;
                     if (!p.a_mn) {
                         tma_load_2d(sa, &tmA, k0, m0, full_bar(s));                       // box {BK, 128}
@@ -592,6 +649,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 3)) { ok = false; break; }
+                    ZN_PHASE(p, 3);
                     tc_fence_after();
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
 #pragma unroll
@@ -604,13 +662,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(tfull_bar(buf));    // accumulator complete
+                ZN_PHASE(p, 4);
             }
         }
     } else {
         // ================= epilogue: warps 2..5, TMEM lanes 32*(warp%4).. =================
         const int q = warp & 3;
         int it = 0, sq = 0;
-        uint32_t sqphase = 0;
+        uint32_t sqphase = 0, stores = 0;
         bool ok = true;
         for (; ok; ++it) {
             if (!mbar_wait(sfull_bar(sq), sqphase, abort_flag, p.status, 7)) { ok = false; break; }
@@ -624,14 +683,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            if (q == 2 && lane == 0) ZN_PHASE(p, 5);
             tc_fence_after();
-            const long long row = (long long)tm * BM + q * 32 + lane;
+            const int warp_row0 = tm * BM + q * 32;
+            const long long row = (long long)warp_row0 + lane;
             const int n0 = tn * BN;
             const float *bias_s = stage_bias(p, bias_smem, n0);
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
             for (int c = 0; c < nchunks; ++c) {
                 uint32_t r[32];
+                ZN_CLK(c, 0);
                 tc_ld32(taddr + (uint32_t)(c * 32), r);
                 tc_wait_ld();
                 if (c == nchunks - 1) {
@@ -640,11 +702,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
-                if (row >= p.M) continue;
-                epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+                if (p.out_mode == 0) {
+                    ZN_CLK(c, 1);
+                    if (row < p.M) epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+                    ZN_CLK(c, 6);
+                } else if (warp_row0 < p.M) {            // uniform over the warp
+                    staged_block<TF32>(p, &tmC, staging + (uint32_t)(q * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r,
+                                       bias_s ? bias_s + c * 32 : nullptr, stores, c);
+                }
             }
+            if (q == 2 && lane == 0) ZN_PHASE(p, 6);
         }
+        if (lane == 0 && p.out_mode) bulk_wait_read<0>();   // the TMA unit has read every staged block; the writes complete with the kernel
     }
+    if (threadIdx.x == 0) ZN_PHASE(p, 7);
 
     // ---- common exit
     if (*abort_flag) {
@@ -656,6 +727,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (lane == 0) ZN_PHASE(p, 8);
     }
 }
 
@@ -674,8 +746,7 @@ constexpr int HALF = 128;                         // rows of A, and columns of B
 constexpr int A2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int B2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int STAGE2_BYTES = A2_STAGE + B2_STAGE;
-// after the operand ring: barriers (256 B), the bias strips, then (1024-aligned) the output staging buffers
-constexpr int PAIR_TAIL = ((256 + BIAS_SMEM + 1023) / 1024) * 1024;
+constexpr int PAIR_TAIL = RING_TAIL;
 constexpr int smem2_bytes(int stages, bool staging) {
     return 1024 /* alignment slack */ + stages * STAGE2_BYTES + PAIR_TAIL + (staging ? STAGING_BYTES : 0);
 }
@@ -917,18 +988,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const float *bias_s = stage_bias(p, bias_smem, n0);
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
-            // The accumulator words of block c + 1 are already on their way from tensor memory while block c goes
-            // through the epilogue arithmetic and its stores.
-            uint32_t next[32];
-            tc_ld32(taddr, next);
             for (int c = 0; c < nchunks; ++c) {
                 uint32_t r[32];
-                tc_wait_ld_into(next);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = next[j];
-                if (c + 1 < nchunks) {
-                    tc_ld32(taddr + (uint32_t)((c + 1) * 32), next);
-                } else {
+                tc_ld32(taddr + (uint32_t)(c * 32), r);
+                tc_wait_ld();
+                if (c == nchunks - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));   // to the leader's MMA thread
@@ -939,31 +1003,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     continue;
                 }
                 if (warp_row0 >= p.M) continue;          // the warp's 32 rows all lie below C (uniform over the warp)
-                float v[32];
-                // rows below C inside a live block: computed from whatever the accumulator holds, without touching
-                // the mask, and clipped by the store
-                if (row < p.M) epilogue_values<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr, v);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
-                }
-                const uint32_t sbuf = staging + (uint32_t)(q * 2 + (stores & 1)) * STG_BUF;
-                if (stores >= 2) {                       // the store that last used this buffer has read it
-                    if (lane == 0) bulk_wait_read<1>();
-                    __syncwarp();
-                }
-                if (p.out_mode == 1) stage_block_f32(sbuf, lane, v);
-                else stage_block_bf16(sbuf, lane, v);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    tma_store_2d(&tmC, n0 + c * 32, warp_row0, sbuf);
-                    bulk_commit();
-                }
-                ++stores;
+                staged_block<TF32>(p, &tmC, staging + (uint32_t)(q * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r,
+                                   bias_s ? bias_s + c * 32 : nullptr, stores);
             }
         }
-        if (lane == 0 && p.out_mode) bulk_wait_all();   // this thread's stores have left shared memory and landed
+        if (lane == 0 && p.out_mode) bulk_wait_read<0>();   // the TMA unit has read every staged block; the writes complete with the kernel
     }
 
     // ---- common exit: neither CTA may leave while its partner can still reach its shared or tensor memory
@@ -1127,12 +1171,33 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.out_f32 = e.out_f32; p.ld_out_f32 = e.ld_out_f32; p.out_t = e.out_t; p.ld_out_t = e.ld_out_t;
     p.accumulate = e.accumulate;
     p.out_mode = 0;
-    // Bands of 8 m-tiles: a wave of 74 tile pairs then shares 8 strips of A and about 9 of B, the fewest distinct
-    // strips (DRAM reads) a wave can have; measured against 16 on the 8192-wide training step: DRAM reads of an
-    // 8192 x 8192 x 8192 product fall from 1.25 GB towards 0.7 GB, the SM clock under the power cap rises from
-    // 1567 to 1634 MHz and the step from 57.2 to 56.5 ms.  ZN_TC_BAND overrides (diagnostic).
-    static const int band = [] { const char *e = getenv("ZN_TC_BAND"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 64 ? v : 8; }();
+    // Rows of tiles per band.  A wave of 74 tile pairs shares `band` strips of A and about 74 / band strips of B;
+    // 8 gives the fewest distinct strips (8 + 9.25), i.e. the fewest DRAM reads per wave, and 16 keeps a band's A
+    // strips (band x 256 rows x K) in L2 across the waves of the band as long as they are small enough.  So: 16
+    // while the A strips of such a band stay within 34 MB (K up to 4096 bf16), else 8.  Measured on the 8192-wide
+    // training step (ncu, 8192 rows): an 8192 x 8192 x 8192 product reads 0.99 GB from DRAM with bands of 8 and
+    // 1.25 GB with 16, an 8192 x 8192 x 4096 product 0.34 GB against 0.22 GB; under the 1 kW cap the DRAM power
+    // saved raises the SM clock (median 1567 -> 1634 MHz) and the step went from 57.2 to 56.5 ms.
+    // ZN_TC_BAND overrides (diagnostic).
+    static const int band_env = [] { const char *e = getenv("ZN_TC_BAND"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 64 ? v : 0; }();
+    const int band = band_env ? band_env : ((long long)16 * 256 * k * es <= (34ll << 20) ? 16 : 8);
     p.band = band;
+#ifdef ZN_DIAG
+    // ZN_TC_PHASES=1 (diagnostic builds): CTA 0 of every one-CTA launch stamps its phases; the host waits for the launch
+    // and prints them relative to the kernel's first stamp
+    static unsigned long long *phase_host = nullptr, *phase_dev = nullptr;
+    static const bool phases = getenv("ZN_TC_PHASES") != nullptr;
+    p.phase_ts = nullptr;
+    if (phases) {
+        if (!phase_host) {
+            cudaHostAlloc((void **)&phase_host, 16 * sizeof(unsigned long long), cudaHostAllocMapped);
+            cudaHostGetDevicePointer((void **)&phase_dev, phase_host, 0);
+        }
+        cudaStreamSynchronize(ctx->stream);
+        for (int i = 0; i < 16; ++i) phase_host[i] = 0ull;
+        p.phase_ts = phase_dev;
+    }
+#endif
     p.status = ctx->status_dev;
     if (!ctx->tile_counters) {
         ZN_CUDA(ctx, cudaMalloc((void **)&ctx->tile_counters, 2 * sizeof(unsigned int)));
@@ -1143,6 +1208,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     // fixed round-robin order and touches neither counter.
     static const int dyn = getenv("ZN_TC_STATIC_TILES") ? 0 : 1;
     p.dynamic_tiles = (dyn && ctx->lane == ZN_LANE_MAIN) ? 1 : 0;
+    {
+        // a launch in which every CTA (or CTA pair) has at most one tile has nothing to hand out
+        const bool would_pair = m > BM && p.num_k_blocks > 16;
+        const long long units = would_pair ? (long long)((m + 2 * BM - 1) / (2 * BM)) * p.num_n_tiles : (long long)p.num_m_tiles * p.num_n_tiles;
+        const long long workers = would_pair ? ctx->sm_count / 2 - (e.reserve_sms + 1) / 2 : ctx->sm_count - e.reserve_sms;
+        if (units <= workers) p.dynamic_tiles = 0;
+    }
     p.tile_counter = ctx->tile_counters + (ctx->tile_counter_turn & 1);
     p.next_counter = ctx->tile_counters + ((ctx->tile_counter_turn + 1) & 1);
     if (p.dynamic_tiles) ctx->tile_counter_turn += 1;
@@ -1162,33 +1234,34 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
     static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
     const bool use_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && p.num_k_blocks > 16));
+    // Output path.  Either every thread stores its own row of the tile straight from the registers the accumulator
+    // was read into (32-byte pieces, one row per lane: an instruction touches 32 different lines, and the L1 store
+    // path takes about two cycles per line, 5 us for a 128 x 256 fp32 tile), or the epilogue warps stage 32 x 32
+    // blocks in shared memory and the TMA unit writes them as whole 128-byte lines.  The one-CTA kernel, whose tiles
+    // have a short main loop and so wait for their epilogue, stages; the two-CTA kernel, whose epilogue hides under
+    // the next tile's long main loop and whose TMA unit is busy with operand loads, stores per thread (measured
+    // there, staged against per-thread: 16384^3 TN 1188 against 1245 TFLOP/s, the 8192-wide training step 58.1
+    // against 57.5 ms).  ZN_TC_STAGED_STORE=0 / 1 forces one path in both kernels (diagnostic).  Staging needs C to
+    // be ONE block the unit can address (16-byte aligned base and row pitch) that is only written; C += ..., two
+    // outputs at once and odd pitches always take the per-thread stores.
+    static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : -1;
+    const bool want_staged = staged_mode < 0 ? !use_pair : staged_mode != 0;
+    CUtensorMap tmC;
+    memset(&tmC, 0, sizeof tmC);
+    if (want_staged && !e.accumulate && (e.out_f32 != nullptr) != (e.out_t != nullptr)) {
+        const bool wide = e.out_f32 != nullptr || tf32;                  // 4-byte results
+        const void *cptr = e.out_f32 ? (const void *)e.out_f32 : (const void *)e.out_t;
+        const int64_t ldc = e.out_f32 ? e.ld_out_f32 : e.ld_out_t;
+        const int ces = wide ? 4 : 2;
+        if ((reinterpret_cast<uintptr_t>(cptr) & 15) == 0 && (ldc * ces) % 16 == 0 && ldc >= n) {
+            ZN_TRY(make_tmap(ctx, &tmC, ces, cptr, n, m, ldc, 32, 32, wide ? 0 : 2));
+            p.out_mode = wide ? 1 : 2;
+        }
+    }
     if (use_pair) {
         // two-CTA kernel: 256 x 256 tiles, B staged in halves of 128 columns per CTA
         if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, HALF, 0));
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | ((uint32_t)((2 * HALF) >> 4) << 24);   // M = 256 across the pair
-        // Output path.  Default: every thread stores its own row of the tile (32-byte pieces, straight from the
-        // registers the accumulator was read into).  ZN_TC_STAGED_STORE=1 selects the other path wherever it can
-        // run: the epilogue warps stage 32 x 32 blocks in shared memory and the TMA unit writes them as whole
-        // 128-byte lines.  Measured in bf16 with fp32 output, staged against per-thread: 65536 x 512 x 512 537
-        // against 518 TFLOP/s, 16384^3 TN 1188 against 1245, the 8192-wide training step 58.1 against 57.5 ms (the
-        // bulk stores share the TMA unit with the operand loads) -- no shape where it pays once short-K products go
-        // to the one-CTA kernel, so it stays an option.  It needs C to be ONE block the unit can address (16-byte
-        // aligned base and row pitch) that is only written; C += ..., two outputs at once and odd pitches always
-        // take the per-thread stores.
-        static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : 0;
-        const bool want_staged = staged_mode != 0;
-        CUtensorMap tmC;
-        memset(&tmC, 0, sizeof tmC);
-        if (want_staged && !e.accumulate && (e.out_f32 != nullptr) != (e.out_t != nullptr)) {
-            const bool wide = e.out_f32 != nullptr || tf32;                  // 4-byte results
-            const void *cptr = e.out_f32 ? (const void *)e.out_f32 : (const void *)e.out_t;
-            const int64_t ldc = e.out_f32 ? e.ld_out_f32 : e.ld_out_t;
-            const int ces = wide ? 4 : 2;
-            if ((reinterpret_cast<uintptr_t>(cptr) & 15) == 0 && (ldc * ces) % 16 == 0 && ldc >= n) {
-                ZN_TRY(make_tmap(ctx, &tmC, ces, cptr, n, m, ldc, 32, 32, wide ? 0 : 2));
-                p.out_mode = wide ? 1 : 2;
-            }
-        }
         const long long pair_tiles = (long long)((m + 2 * HALF - 1) / (2 * HALF)) * p.num_n_tiles;
         int max_clusters = ctx->sm_count / 2 - (e.reserve_sms + 1) / 2;
         if (max_clusters < 1) max_clusters = 1;
@@ -1232,9 +1305,27 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     const int sms = ctx->sm_count - e.reserve_sms > 0 ? ctx->sm_count - e.reserve_sms : 1;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
-    else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
+    if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmC, p);
+    else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmC, p);
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return launch_failed(le, "launch of the tensor-core GEMM");
+#ifdef ZN_DIAG
+    if (phases) {
+        cudaStreamSynchronize(ctx->stream);
+        fprintf(stderr, "phases m=%lld n=%lld k=%lld grid=%d:", (long long)m, (long long)n, (long long)k, grid);
+        for (int i = 1; i <= 8; ++i)
+            fprintf(stderr, " %d:%+.2fus", i, phase_host[i] ? (double)((long long)phase_host[i] - (long long)phase_host[0]) / 1e3 : -1.0);
+        fprintf(stderr, "\n");
+        long long clk[128];
+        cudaMemcpyFromSymbol(clk, zn_diag_clk, sizeof clk);
+        fprintf(stderr, "  epilogue clocks of warp 2 (cycles from the block's start: wait_ld, values, buffer free, staged, fence, issued):");
+        for (int c = 0; c < 8; ++c) {
+            fprintf(stderr, " [b%d @%lld:", c, c ? clk[c * 8] - clk[0] : 0ll);
+            for (int k2 = 1; k2 <= 6; ++k2) fprintf(stderr, " %lld", clk[c * 8 + k2] ? clk[c * 8 + k2] - clk[c * 8] : -1ll);
+            fprintf(stderr, "]");
+        }
+        fprintf(stderr, "\n");
+    }
+#endif
     return ZN_OK;
 }
