@@ -104,9 +104,16 @@ __device__ long long zn_diag_clk[128];
     do {                                                                                               \
         if (blockIdx.x == 0 && threadIdx.x == 64 && (c) < 8) zn_diag_clk[(c) * 8 + (point)] = clock64(); \
     } while (0)
+// diagnostic builds: SM clock of one point of tile number `it` (as counted by the role) in the leader CTA of cluster 0
+__device__ long long zn_diag_tile[8 * 16];
+#define ZN_TILE_CLK(it, point)                                                                         \
+    do {                                                                                               \
+        if (blockIdx.x == 0 && (it) < 8) zn_diag_tile[(it) * 16 + (point)] = clock64();               \
+    } while (0)
 #else
 #define ZN_PHASE(p, i) do { } while (0)
 #define ZN_CLK(c, point) do { } while (0)
+#define ZN_TILE_CLK(it, point) do { } while (0)
 #endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -872,8 +879,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t qphase = 0;
             // The leader draws the index of the tile AFTER the one it is about to load while that one's loads are
             // still being issued: the atomic's round trip to L2 is then hidden behind a whole tile of loads.
+            // Publishing an index (remote store + release at cluster scope) still costs this thread about 3,300
+            // cycles between two tiles, which the clock stamps of diagnostic builds show as 3,660 cycles without
+            // operands at the MMA thread per 8192-deep tile.  Handing the next index over in the MIDDLE of a tile
+            // removes that gap (600 cycles) and was measured: the k-blocks then take 647 instead of 611 cycles
+            // each and the training step 57.69 against 57.42 ms (three alternating runs on one box).  The main
+            // loop runs at the rate L2 delivers operands to the SMs, not at the rate the producer asks for them.
             int t_next = cluster_id;
-            for (bool first = true; ok; first = false) {
+            int ptile = 0;                                    // tiles this producer has started (diagnostic builds)
+            for (bool first = true; ok; first = false, ++ptile) {
                 int t;
                 if (rank == 0) {
                     // the leader picks the pair's next tile and publishes it into both CTAs' rings
@@ -882,6 +896,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (t >= 0)
                         t_next = p.dynamic_tiles ? (int)(num_clusters + atomicAdd(p.tile_counter, 1u)) : t + num_clusters;
                     if (!mbar_wait_cluster(sempty_bar(q), qphase ^ 1u, abort_flag, p.status, 15)) { ok = false; break; }
+                    ZN_TILE_CLK(ptile, 7);
                     tile_ring[q] = t;
                     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(smem_u32((const void *)&tile_ring[q]), 1)), "r"(t)
                                  : "memory");
@@ -900,6 +915,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const int n0 = tn * BN + (int)rank * HALF;             // this CTA's columns of B
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                    if (rank == 0) { if (kb == 0) ZN_TILE_CLK(ptile, 8); if (kb == nkb - 1) ZN_TILE_CLK(ptile, 9); }
                     const uint32_t sa = base + s * STAGE2_BYTES, sb = sa + A2_STAGE;
                     const uint32_t lead_full = map_to_cta(full_bar(s), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE2_BYTES);
@@ -941,13 +957,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 mbar_arrive(sempty_bar(q));
                 if (++q == TQ) { q = 0; qphase ^= 1u; }
                 if (t < 0) break;
+                ZN_TILE_CLK(it, 0);
                 const int buf = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
+                ZN_TILE_CLK(it, 1);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 13)) { ok = false; break; }
+                    if (kb == 0) ZN_TILE_CLK(it, 2);
                     tc_fence_after();
                     const uint32_t sa = base + s * STAGE2_BYTES, sb = sa + A2_STAGE;
 #pragma unroll
@@ -960,6 +979,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (++s == NST) { s = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit_pair(tfull_bar(buf));   // accumulator complete, in both CTAs
+                ZN_TILE_CLK(it, 3);
             }
         }
     } else {
@@ -976,11 +996,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (lane == 0) mbar_arrive_cluster(map_to_cta(sempty_bar(sq), 0));
             if (++sq == TQ) { sq = 0; sqphase ^= 1u; }
             if (t < 0) break;
+            if (threadIdx.x == 64) ZN_TILE_CLK(it, 4);
             int tm, tn;
             tile_coords(t, num_m_pairs, p.num_n_tiles, p.band, tm, tn);
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
+            if (threadIdx.x == 64) ZN_TILE_CLK(it, 5);
             tc_fence_after();
             const int warp_row0 = tm * 2 * HALF + (int)rank * HALF + q * 32;
             const long long row = (long long)warp_row0 + lane;
@@ -1006,6 +1028,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 staged_block<TF32>(p, &tmC, staging + (uint32_t)(q * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r,
                                    bias_s ? bias_s + c * 32 : nullptr, stores);
             }
+            if (threadIdx.x == 64) ZN_TILE_CLK(it, 6);
         }
         if (lane == 0 && p.out_mode) bulk_wait_read<0>();   // the TMA unit has read every staged block; the writes complete with the kernel
     }
@@ -1300,6 +1323,25 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         cfg.numAttrs = 1;
         const cudaError_t le = cudaLaunchKernelEx(&cfg, fn, tmA, tmB, tmC, p);
         if (le != cudaSuccess) return launch_failed(le, "launch of the two-CTA tensor-core GEMM");
+#ifdef ZN_DIAG
+        if (phases) {
+            cudaStreamSynchronize(ctx->stream);
+            long long tc[8 * 16];
+            cudaMemcpyFromSymbol(tc, zn_diag_tile, sizeof tc);
+            fprintf(stderr, "pair tiles m=%lld n=%lld k=%lld clusters=%d; leader CTA of cluster 0, cycles from its first stamp\n"
+                            "  per tile: producer publish / first load / last load | MMA index / accumulator free / first operands / last issue | "
+                            "epilogue index / accumulator full / done\n", (long long)m, (long long)n, (long long)k, clusters);
+            long long t0 = tc[7] ? tc[7] : tc[0];
+            for (int i = 0; i < 8; ++i) {
+                if (!tc[i * 16 + 0]) break;
+                fprintf(stderr, "  tile %d: P %lld %lld %lld | M %lld %lld %lld %lld | E %lld %lld %lld\n", i, tc[i * 16 + 7] - t0, tc[i * 16 + 8] - t0,
+                        tc[i * 16 + 9] - t0, tc[i * 16 + 0] - t0, tc[i * 16 + 1] - t0, tc[i * 16 + 2] - t0, tc[i * 16 + 3] - t0,
+                        tc[i * 16 + 4] - t0, tc[i * 16 + 5] - t0, tc[i * 16 + 6] - t0);
+            }
+            static const long long zeros[8 * 16] = {0};
+            cudaMemcpyToSymbol(zn_diag_tile, zeros, sizeof zeros);
+        }
+#endif
         return ZN_OK;
     }
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;

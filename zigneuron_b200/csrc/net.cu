@@ -57,7 +57,6 @@ struct Layer {
     // ordering between the lanes of a step (see step_dev)
     cudaEvent_t g_ready = nullptr, bias_done = nullptr, grads_ready = nullptr, reduced = nullptr, updated = nullptr;
     cudaEvent_t stepped = nullptr;        // sharded update: this rank's piece of the layer has been updated
-    cudaEvent_t half_ready = nullptr;     // data parallel: the first half of gW's rows exists (layer 0 only, see step_dev)
     bool update_pending = false;          // `updated` has been recorded and not yet waited for by the host
 };
 
@@ -280,27 +279,10 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         }
         if (!compact) ZN_CUDA(ctx, cudaEventRecord(l.bias_done, s_aux));
         // gW = X^T . G           (matMulTransposeA, src/layer.zig:466)
-        // Layer 0 comes last, so the exchange of its gradients is the one with the least work left to hide under
-        // (only its own dX GEMM) and the next step's first GEMM waits for it.  Data parallel, its gW is therefore
-        // computed as two halves of its rows and the first half is already on the wire while the second is still
-        // being computed.  ZN_DP_SPLIT_LAST=0 switches this off (diagnostic).
-        static const bool split_last = !(getenv("ZN_DP_SPLIT_LAST") && atoi(getenv("ZN_DP_SPLIT_LAST")) == 0);
-        const size_t exchange_count = idx + 1 == L ? l.cap : l.blk;
-        size_t exchanged = 0;                       // floats of this layer's block already handed to the exchange
-        if (dp && !shard && idx == 0 && n->tc && split_last && l.in % 512 == 0 && l.in >= 1024) {
-            const size_t half = l.in / 2;
-            zn_epilogue ep;
-            ep.out_f32 = l.grads;
-            ep.ld_out_f32 = (int64_t)l.out;
-            ZN_TRY(net_gemm(n, 1, x_in, n->lds[idx], g, ld_g, (int64_t)half, (int64_t)l.out, (int64_t)rows, ep));
-            ZN_CUDA(ctx, cudaEventRecord(l.half_ready, s_main));
-            ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.half_ready, 0));
-            ZN_TRY(zn_dp_allreduce(ctx, l.grads, half * l.out, s_comm));
-            exchanged = half * l.out;
-            ep.out_f32 = l.grads + half * l.out;
-            const void *x_hi = (const char *)x_in + half * esize(n);      // columns [half, in) of the [rows][in] block
-            ZN_TRY(net_gemm(n, 1, x_hi, n->lds[idx], g, ld_g, (int64_t)(l.in - half), (int64_t)l.out, (int64_t)rows, ep));
-        } else {
+        // (Computing layer 0's gW as two halves and putting the first half on the wire while the second is computed
+        // was measured on 8 GPUs: 8.464 against 8.390 ms per step.  Two launches of half the tiles lose more to
+        // their partial last waves than the earlier start of the exchange gains.  Not kept.)
+        {
             zn_epilogue ep;
             ep.out_f32 = l.grads;
             ep.ld_out_f32 = (int64_t)l.out;
@@ -311,7 +293,7 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         if (!compact) ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.bias_done, 0));
         // the last layer's block carries the loss sum in its tail; the other three tail floats stay zero and
         // ride along so that every exchanged count is a multiple of four floats
-        if (dp && !shard) ZN_TRY(zn_dp_allreduce(ctx, l.grads + exchanged, exchange_count - exchanged, s_comm));
+        if (dp && !shard) ZN_TRY(zn_dp_allreduce(ctx, l.grads, idx + 1 == L ? l.cap : l.blk, s_comm));
         if (shard) {
             // sharded update: this rank ends with the summed gradients of its own piece of the block only, and
             // squares just that piece (the padding inside a block is zero and adds nothing)
@@ -590,7 +572,7 @@ extern "C" void zn_net_destroy(zn_net *n) {
         if (l.params_nccl) zn_dp_free_registered(n->ctx, l.params, l.params_reg);
         else cudaFree(l.params);
         cudaFree(l.m); cudaFree(l.v); cudaFree(l.w_op);
-        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated, l.stepped, l.half_ready})
+        for (cudaEvent_t ev : {l.g_ready, l.bias_done, l.grads_ready, l.reduced, l.updated, l.stepped})
             if (ev) cudaEventDestroy(ev);
     }
     cudaFree(n->sumsq);
@@ -628,7 +610,7 @@ extern "C" zn_status zn_net_add_dense(zn_net *n, size_t input_size, size_t outpu
     ZN_CUDA(ctx, cudaMalloc((void **)&l.grads, alloc));
     ZN_CUDA(ctx, cudaMemsetAsync(l.params, 0, alloc, ctx->stream));
     ZN_CUDA(ctx, cudaMemsetAsync(l.grads, 0, alloc, ctx->stream));
-    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated, &l.stepped, &l.half_ready})
+    for (cudaEvent_t *ev : {&l.g_ready, &l.bias_done, &l.grads_ready, &l.reduced, &l.updated, &l.stepped})
         ZN_CUDA(ctx, cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
     if (n->tc) {
         const bool direct = !n->bf16 && output_size % 4 == 0;   // tf32 can read W itself when its pitch is TMA-legal
