@@ -31,9 +31,9 @@ DIMS = [(4096, 8192), (8192, 8192), (8192, 8192), (8192, 4096)]
 ACTS = ["relu", "relu", "relu", "linear"]
 GLOBAL_BATCH = 65536
 # Data parallel: from this many ranks on, the parameter update is split over the ranks (reduce-scatter, update of the
-# own piece, all-gather) unless --shard-update says otherwise.  Measured on one 8-GPU box in one call: 8.242 ms per
-# step sharded against 8.390 replicated at 8 ranks; 28.99 against 28.69 ms at 2 ranks.
-SHARD_UPDATE_FROM_RANKS = 8
+# own piece, all-gather) unless --shard-update says otherwise.  Measured, sharded against replicated, each pair in one
+# call on one box: 8 ranks 8.242 against 8.390 ms per step, 4 ranks 15.137 against 15.876, 2 ranks 28.99 against 28.69.
+SHARD_UPDATE_FROM_RANKS = 4
 SEED = 3
 LR = 1e-3
 BLOCK_ROWS = 1024                     # data is generated in blocks of rows keyed by (seed, stream, block)
@@ -47,9 +47,9 @@ FLOP_PER_SAMPLE = 6.0 * SUM_IO        # forward + dX + dW GEMMs, the reference's
 # grow in proportion to them, so a launch with R rows moves R / 8192 times these bytes.
 NCU_ROWS = 8192
 NCU_GEMM_DRAM_BYTES = {   # (orientation, m, n, k at 8192 rows): measured DRAM bytes
-    ("NN", "rows", 8192, 4096): 334.9e6, ("NN", "rows", 8192, 8192): 1370.5e6, ("NN", "rows", 4096, 8192): 806.4e6,
-    ("TN", 8192, 4096, "rows"): 798.3e6, ("TN", 8192, 8192, "rows"): 1499.4e6, ("TN", 4096, 8192, "rows"): 737.3e6,
-    ("NT", "rows", 8192, 4096): 522.8e6, ("NT", "rows", 8192, 8192): 1518.8e6, ("NT", "rows", 4096, 8192): 744.8e6,
+    ("NN", "rows", 8192, 4096): 333.6e6, ("NN", "rows", 8192, 8192): 1080.4e6, ("NN", "rows", 4096, 8192): 715.0e6,
+    ("TN", 8192, 4096, "rows"): 715.2e6, ("TN", 8192, 8192, "rows"): 1339.4e6, ("TN", 4096, 8192, "rows"): 634.3e6,
+    ("NT", "rows", 8192, 4096): 534.6e6, ("NT", "rows", 8192, 8192): 1285.8e6, ("NT", "rows", 4096, 8192): 640.2e6,
 }
 
 
