@@ -28,6 +28,7 @@ struct NcclApi {
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     // optional (NCCL >= 2.19): memory the collectives can work on in place
@@ -57,6 +58,7 @@ NcclApi &api() {
     ZN_SYM(AllReduce, "ncclAllReduce");
     ZN_SYM(ReduceScatter, "ncclReduceScatter");
     ZN_SYM(AllGather, "ncclAllGather");
+    ZN_SYM(Broadcast, "ncclBroadcast");
     ZN_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     ZN_SYM(GetErrorString, "ncclGetErrorString");
     ZN_SYM(MemAlloc, "ncclMemAlloc");
@@ -228,6 +230,27 @@ zn_status zn_dp_all_gather(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t s
     if (!ctx->dp->comm) return comm_gone(ctx);
     ncclResult_t r = api().AllGather(buf + (size_t)ctx->dp->rank * shard, buf, shard, ncclFloat32, ctx->dp->comm, stream);
     if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllGather: %s", api().GetErrorString(r));
+    return ZN_OK;
+}
+
+bool zn_dp_can_gather_bf16(const zn_ctx *ctx) { return zn_dp_can_shard(ctx) && api().Broadcast; }
+
+// In place on world * shard bf16 values: every rank contributes its own piece and ends with all of them.
+zn_status zn_dp_all_gather_bf16(zn_ctx *ctx, void *buf, size_t shard, cudaStream_t stream) {
+    if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "all-gather needs an initialised communicator");
+    if (!ctx->dp->comm) return comm_gone(ctx);
+    __nv_bfloat16 *b = static_cast<__nv_bfloat16 *>(buf);
+    ncclResult_t r = api().AllGather(b + (size_t)ctx->dp->rank * shard, b, shard, ncclBfloat16, ctx->dp->comm, stream);
+    if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclAllGather(bf16): %s", api().GetErrorString(r));
+    return ZN_OK;
+}
+
+// In place: `count` floats at buf go from rank `root` to every rank.
+zn_status zn_dp_broadcast(zn_ctx *ctx, float *buf, size_t count, int root, cudaStream_t stream) {
+    if (!zn_dp_can_gather_bf16(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "broadcast needs an initialised communicator");
+    if (!ctx->dp->comm) return comm_gone(ctx);
+    ncclResult_t r = api().Broadcast(buf, buf, count, ncclFloat32, root, ctx->dp->comm, stream);
+    if (r != ncclSuccess) return zn_fail(ctx, ZN_ERR_NCCL, "ncclBroadcast: %s", api().GetErrorString(r));
     return ZN_OK;
 }
 

@@ -32,6 +32,9 @@ bool zn_dp_can_shard(const zn_ctx *ctx);
 zn_status zn_dp_allreduce_f64(zn_ctx *ctx, double *buf, size_t count, cudaStream_t stream);
 zn_status zn_dp_reduce_scatter(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream);
 zn_status zn_dp_all_gather(zn_ctx *ctx, float *buf, size_t shard, cudaStream_t stream);
+bool zn_dp_can_gather_bf16(const zn_ctx *ctx);
+zn_status zn_dp_all_gather_bf16(zn_ctx *ctx, void *buf, size_t shard, cudaStream_t stream);
+zn_status zn_dp_broadcast(zn_ctx *ctx, float *buf, size_t count, int root, cudaStream_t stream);
 
 namespace {
 
@@ -45,6 +48,7 @@ struct Layer {
     size_t b_off = 0, len = 0, blk = 0;   // bias offset, used length, used length rounded up to a multiple of 4
     size_t cap = 0;                       // floats allocated per block: >= blk + 4; the last four are the tail
     size_t shard = 0;                     // sharded update: floats per rank, world * shard >= blk
+    bool gather_bf16 = false;             // sharded update: the ranks exchange the bf16 operand copy, not the fp32 weights
     float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
     void *grads_reg = nullptr, *params_reg = nullptr;   // registration handles of blocks that come from NCCL
     bool grads_nccl = false, params_nccl = false;       // the block was allocated by NCCL and is registered
@@ -89,6 +93,7 @@ struct zn_net {
     int head = 0, inflight = 0;
     size_t global_rows = 0;               // > 0: data parallel
     bool shard_update = false;            // data parallel with the update split over the ranks (see step_dev)
+    bool params_stale = false;            // sharded update with bf16 hand-over: fp32 W of the other ranks' pieces is out of date
     cudaEvent_t norm_ready = nullptr;     // sharded update: the global sums of squares and the loss sum are in
     float last_norm = 0.f, last_factor = 1.f;
     const void *last_input_grad = nullptr;
@@ -438,12 +443,32 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
                 a.w = l.params + a0; a.g = l.grads + a0; a.count = a1 - a0; a.shadow = nullptr;
                 a.m = l.m ? l.m + a0 : nullptr;
                 a.v = l.v ? l.v + a0 : nullptr;
+                if (part == 0 && l.gather_bf16) {
+                    // the update writes this piece of the bf16 operand copy as well: W and its copy have the same
+                    // flat layout (pitch = width), so the piece sits at the same offset
+                    a.shadow = static_cast<__nv_bfloat16 *>(l.w_op) + a0;
+                    a.shadow_bf16 = true;
+                    a.cols = a.ld_shadow = (int64_t)l.out;
+                }
                 ZN_TRY(update(part == 1));
             }
             ZN_CUDA(ctx, cudaEventRecord(l.stepped, s_opt));
             ZN_CUDA(ctx, cudaStreamWaitEvent(s_comm, l.stepped, 0));
-            ZN_TRY(zn_dp_all_gather(ctx, l.params, l.shard, s_comm));
-            {
+            if (l.gather_bf16) {
+                // What the next forward pass needs is the bf16 operand copy and the fp32 bias: gather the first (half
+                // the bytes of the fp32 weights, and no conversion pass afterwards), broadcast the second from the
+                // rank(s) that own it.  The fp32 weights of the other ranks' pieces are brought up to date only when
+                // somebody asks for them (zn_net_get_weights, zn_net_save).
+                ZN_TRY(zn_dp_all_gather_bf16(ctx, l.w_op, l.shard, s_comm));
+                const size_t b0 = l.b_off, b1 = l.b_off + l.out;
+                for (size_t r = b0 / l.shard; r <= (b1 - 1) / l.shard; ++r) {
+                    const size_t c0 = b0 > r * l.shard ? b0 : r * l.shard;
+                    const size_t c1 = b1 < (r + 1) * l.shard ? b1 : (r + 1) * l.shard;
+                    if (c0 < c1) ZN_TRY(zn_dp_broadcast(ctx, l.params + c0, c1 - c0, (int)r, s_comm));
+                }
+                n->params_stale = true;
+            } else {
+                ZN_TRY(zn_dp_all_gather(ctx, l.params, l.shard, s_comm));
                 zn_lane_guard lane(ctx, ZN_LANE_COMM);
                 ZN_TRY(refresh_operand_copy(n, l));
             }
@@ -469,6 +494,19 @@ zn_status step_dev(zn_net *n, const float *x_dev, const float *t_dev, size_t row
         l.update_pending = true;
     }
     if (compact && multi_n > 0) ZN_TRY(zn_k_multi_update(ctx, multi_args, multi_kind, multi_bias, multi_n));
+    return ZN_OK;
+}
+
+// Sharded update with the bf16 hand-over: every rank gathers the fp32 weights of the other ranks' pieces.  Collective:
+// every rank has to come here (zn_net_get_weights, zn_net_save and switching the sharding off do).
+zn_status gather_stale_params(zn_net *n) {
+    if (!n->params_stale) return ZN_OK;
+    zn_ctx *ctx = n->ctx;
+    ZN_TRY(zn_sync_all_lanes(ctx));
+    for (Layer &l : n->layers)
+        if (l.gather_bf16) ZN_TRY(zn_dp_all_gather(ctx, l.params, l.shard, ctx->lanes[ZN_LANE_COMM].stream));
+    ZN_TRY(zn_sync_all_lanes(ctx));
+    n->params_stale = false;
     return ZN_OK;
 }
 
@@ -664,6 +702,7 @@ extern "C" zn_status zn_net_set_weights(zn_net *n, size_t layer, const float *we
 extern "C" zn_status zn_net_get_weights(zn_net *n, size_t layer, float *weights, float *bias) {
     ZN_TRY(check_net(n, true));
     zn_ctx *ctx = n->ctx;
+    ZN_TRY(gather_stale_params(n));
     if (layer >= n->layers.size()) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "layer %zu out of range", layer);
     Layer &l = n->layers[layer];
     if (weights) ZN_CUDA(ctx, cudaMemcpyAsync(weights, l.params, l.in * l.out * sizeof(float), cudaMemcpyDefault, ctx->stream));
@@ -955,6 +994,7 @@ bool get_u32(FILE *f, uint32_t *v) { return fread(v, 4, 1, f) == 1; }
 extern "C" zn_status zn_net_save(zn_net *n, const char *path) {
     ZN_TRY(check_net(n, true));
     zn_ctx *ctx = n->ctx;
+    ZN_TRY(gather_stale_params(n));
     if (!path) return zn_fail(ctx, ZN_ERR_INVALID_VALUE, "save: null path");
     FILE *f = fopen(path, "wb");
     if (!f) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "save: cannot create %s", path);
@@ -1042,7 +1082,11 @@ zn_status regrow_block(zn_net *n, float **blk, bool *is_nccl, void **reg, size_t
 extern "C" zn_status zn_net_set_update_sharding(zn_net *n, int32_t on) {
     ZN_TRY(check_net(n, true));
     zn_ctx *ctx = n->ctx;
-    if (!on) { n->shard_update = false; return ZN_OK; }
+    if (!on) {
+        ZN_TRY(gather_stale_params(n));
+        n->shard_update = false;
+        return ZN_OK;
+    }
     if (n->global_rows == 0 || !zn_dp_active(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "call zn_net_set_data_parallel first");
     if (!zn_dp_can_shard(ctx)) return zn_fail(ctx, ZN_ERR_NOT_AVAILABLE, "this NCCL has no reduce-scatter / all-gather");
     if (n->prec == ZN_FP32_EXACT) return zn_fail(ctx, ZN_ERR_UNSUPPORTED, "FP32_EXACT sums every gradient in the reference's order on one rank; it cannot be sharded");
@@ -1060,6 +1104,23 @@ extern "C" zn_status zn_net_set_update_sharding(zn_net *n, int32_t on) {
         if (l.v) ZN_TRY(regrow_block(n, &l.v, nullptr, nullptr, l.cap, cap, false, true));
         l.cap = cap;
     }
+    // bf16 networks whose operand copy of W has W's own flat layout hand that copy over between the ranks instead
+    // of the fp32 weights; the copy then needs room for world * shard values.  ZN_DP_GATHER_FP32=1 keeps the fp32 form.
+    static const bool fp32_gather = getenv("ZN_DP_GATHER_FP32") != nullptr;
+    for (Layer &l : n->layers) {
+        l.gather_bf16 = false;
+        if (fp32_gather || !n->bf16 || !l.w_op || l.ld_w != (int64_t)l.out || !zn_dp_can_gather_bf16(ctx)) continue;
+        const size_t elems = world * l.shard > l.in * l.out ? world * l.shard : l.in * l.out;
+        void *grown = nullptr;
+        ZN_CUDA(ctx, cudaMalloc(&grown, elems * sizeof(__nv_bfloat16)));
+        ZN_CUDA(ctx, cudaMemsetAsync(grown, 0, elems * sizeof(__nv_bfloat16), ctx->stream));
+        ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(l.w_op);
+        l.w_op = grown;
+        ZN_TRY(refresh_operand_copy(n, l));
+        l.gather_bf16 = true;
+    }
+    ZN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     n->shard_update = true;
     return ZN_OK;
 }
