@@ -278,14 +278,14 @@ ZN_API zn_status zn_dp_init(zn_ctx *ctx, int32_t rank, int32_t world, const uint
 ZN_API zn_status zn_dp_destroy(zn_ctx *ctx);
 ZN_API zn_status zn_net_set_data_parallel(zn_net *net, size_t global_rows);
 /* Optional, after zn_net_set_data_parallel: split the parameter update over the ranks.  Per layer a
- * reduce-scatter of the gradients, each rank clips and updates its own 1/world piece, then the ranks exchange what
- * the next forward pass needs: the bf16 operand copy of the weights (an all-gather of half the bytes; bf16 networks
- * whose layer widths are multiples of 8) or else the updated fp32 weights; results as before up to the order NCCL
- * adds in.  While it is on, zn_net_get_grads and zn_net_save_optimizer fail with ZN_ERR_NOT_AVAILABLE (a rank
- * holds its own piece only), FP32_EXACT is refused, and zn_net_get_weights / zn_net_save are COLLECTIVE: with the
- * bf16 exchange a rank's fp32 copy of the other ranks' pieces is brought up to date only then, by an all-gather
- * every rank has to take part in (call them on all ranks, in the same order).  No counterpart in the reference,
- * whose multi-GPU layer has no collective at all (src/cuda_multi_gpu.zig). */
+ * reduce-scatter of the gradients, each rank clips and updates its own 1/world piece, then an all-gather of the
+ * updated fp32 weights; results as before up to the order NCCL adds in.  While it is on, zn_net_get_grads and
+ * zn_net_save_optimizer fail with ZN_ERR_NOT_AVAILABLE (a rank holds its own piece only) and FP32_EXACT is
+ * refused.  Option, ZN_DP_GATHER_BF16=1 in the environment of this call: bf16 networks whose layer widths are
+ * multiples of 8 exchange the bf16 operand copy of the weights instead (half the bytes); a rank's fp32 copy of the
+ * other ranks' pieces is then brought up to date only by zn_net_get_weights / zn_net_save, which become
+ * COLLECTIVE (an all-gather every rank has to take part in: call them on all ranks, in the same order).  No
+ * counterpart in the reference, whose multi-GPU layer has no collective at all (src/cuda_multi_gpu.zig). */
 ZN_API zn_status zn_net_set_update_sharding(zn_net *net, int32_t on);
 
 /* ---- failure detection ------------------------------------------------------------ */

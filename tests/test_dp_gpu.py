@@ -45,6 +45,8 @@ def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value, shard=Fal
     # the last GEMM of a data-parallel step runs its first rows on fewer SMs: 64 of each rank's 100 rows here,
     # so that both of its launches are exercised
     os.environ.setdefault("ZN_DP_RESERVE_ROWS", "64")
+    if shard == "bf16":
+        os.environ["ZN_DP_GATHER_BF16"] = "1"      # the sharded update's optional exchange of the bf16 operand copy
     import zigneuron_b200 as zn
     prec = zn.Precision(prec_value)
     loss = zn.Loss.mse if loss_name == "mse" else zn.Loss.cross_entropy_logits
@@ -78,7 +80,7 @@ def _rank(rank, world, uid_path, out_dir, loss_name, adam, prec_value, shard=Fal
     be.deinit()
 
 
-@pytest.mark.parametrize("shard", [False, True], ids=["replicated", "sharded"])
+@pytest.mark.parametrize("shard", [False, True, "bf16"], ids=["replicated", "sharded", "sharded-bf16-exchange"])
 @pytest.mark.parametrize("loss_name,adam,prec_name,tol", [("mse", False, "FP32_SIMT", 1e-5), ("ce", True, "FP32_SIMT", 2e-3),
                                                            ("mse", False, "BF16_TC", 2e-2), ("mse", True, "BF16_TC", 2e-2)])
 def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name, tol, shard):
@@ -89,6 +91,8 @@ def test_two_gpus_match_one_gpu_and_oracle(tmp_path, loss_name, adam, prec_name,
     from oracle import zn_oracle as zo
     from util import rel_l2
     prec = zn.Precision[prec_name]
+    if shard == "bf16" and prec_name != "BF16_TC":
+        pytest.skip("the bf16 exchange exists for bf16 networks only")
     mp.spawn(_rank, args=(2, str(tmp_path / "uid"), str(tmp_path), loss_name, adam, int(prec), shard), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "r0.npz"), np.load(tmp_path / "r1.npz")
     # both ranks end with identical parameters and report the same (global) loss

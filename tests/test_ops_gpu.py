@@ -96,9 +96,13 @@ def test_gemm_accumulate(be, orient):
 
 
 # Short main loops (K up to 1024 bf16 / 512 tf32 values) and single row tiles run the one-CTA kernel, the rest the
-# two-CTA kernel: the last three shapes have more than one row tile AND a long K in both precisions.
+# two-CTA kernel: the last three shapes of the first two rows have more than one row tile AND a long K in both
+# precisions.  The one-CTA kernel takes 128-column tiles where N fits one or the 256-column tiles would fill at
+# most half the SMs (every shape of the first row, and the third row), 256-column tiles otherwise (the fourth row).
 TC_SHAPES = [(128, 256, 64), (256, 512, 256), (300, 200, 100), (130, 10, 256), (1024, 512, 784), (64, 2048, 1500),
-             (2048, 1024, 512), (384, 320, 2304), (300, 520, 1100), (513, 260, 4100)]
+             (2048, 1024, 512), (384, 320, 2304), (300, 520, 1100), (513, 260, 4100),
+             (1024, 1024, 1024), (200, 136, 96), (256, 384, 512),
+             (4096, 1200, 256), (2500, 2304, 200)]
 
 
 @pytest.mark.parametrize("prec", [P.BF16_TC, P.TF32_TC])
@@ -499,11 +503,15 @@ print("forced-kernel checks ok")
 """
 
 
-@pytest.mark.parametrize("env", [{"ZN_TC_PAIR": "2"}, {"ZN_TC_PAIR": "2", "ZN_TC_STAGED_STORE": "1"}, {"ZN_TC_PAIR": "0"}],
-                         ids=["two-CTA everywhere", "two-CTA with staged TMA stores", "one-CTA everywhere"])
+@pytest.mark.parametrize("env", [{"ZN_TC_PAIR": "2"}, {"ZN_TC_PAIR": "2", "ZN_TC_STAGED_STORE": "1"}, {"ZN_TC_PAIR": "0"},
+                                 {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "0"}, {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "2"},
+                                 {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "2", "ZN_TC_STAGED_STORE": "0"}],
+                         ids=["two-CTA everywhere", "two-CTA with staged TMA stores", "one-CTA everywhere",
+                              "one-CTA, 256-column tiles only", "one-CTA, 128-column tiles only",
+                              "one-CTA, 128-column tiles, per-thread stores"])
 def test_each_tensor_core_kernel_on_shapes_the_default_routes_elsewhere(env):
-    """The library picks the one-CTA or the two-CTA kernel by shape, and the two-CTA kernel's shared-memory-staged
-    bulk-store epilogue is an option.  The choices are read once per process, so each forced combination runs in a
+    """The library picks the one-CTA or the two-CTA kernel and the one-CTA kernel's tile width by shape, and the
+    two-CTA kernel's shared-memory-staged bulk-store epilogue is an option.  The choices are read once per process, so each forced combination runs in a
     process of its own, over shapes (ragged edges included) that the default routing would send to the other kernel."""
     import os
     import subprocess

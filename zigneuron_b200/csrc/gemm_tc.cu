@@ -36,12 +36,11 @@
 namespace {
 
 constexpr int BM = 128, BN = 256;
-constexpr int STAGES = 3;                           // one-CTA kernel: 3 x 48 KiB of operands beside 32 KiB of output staging
+// one-CTA kernel, beside 32 KiB of output staging: 3 x 48 KiB of operands for 256-column tiles, 5 x 32 KiB for 128-column ones
+__host__ __device__ constexpr int onecta_stages(int bn) { return bn == 256 ? 3 : 5; }
 constexpr int TQ = 4;                               // depth of the tile-index ring inside a CTA
 constexpr int ROW_BYTES = 128;                    // one swizzle row
 constexpr int A_STAGE = BM * ROW_BYTES;           // 16 KiB
-constexpr int B_STAGE = BN * ROW_BYTES;           // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int BIAS_SMEM = 4 * BN * 4;                 // one tile's bias values, a private copy per epilogue warp
@@ -49,8 +48,11 @@ constexpr int STG_BUF = 4096;                         // one staged 32 x 32 outp
 constexpr int STAGING_BYTES = 4 * 2 * STG_BUF;        // two blocks per epilogue warp
 // after the operand ring: barriers (256 B), the bias strips, then (1024-aligned) the output staging buffers
 constexpr int RING_TAIL = ((256 + BIAS_SMEM + 1023) / 1024) * 1024;
-constexpr int SMEM_BYTES = 1024 /* alignment slack */ + STAGES * STAGE_BYTES + RING_TAIL + STAGING_BYTES;
-static_assert(SMEM_BYTES <= 232448, "the one-CTA kernel must fit the 227 KB of shared memory a CTA may have");
+constexpr int onecta_smem(int bn) {
+    return 1024 /* alignment slack */ + onecta_stages(bn) * (A_STAGE + bn * ROW_BYTES) + RING_TAIL + STAGING_BYTES;
+}
+static_assert(onecta_smem(256) <= 232448 && onecta_smem(128) <= 232448,
+              "the one-CTA kernel must fit the 227 KB of shared memory a CTA may have");
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
 struct TcParams {
@@ -448,12 +450,12 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
 // Each epilogue warp copies the tile's BN bias values into its own strip of shared memory once, instead of
 // every thread fetching all of them from global memory through an L1 that the shared-memory split leaves
 // tiny.  A private strip per warp needs no barrier between warps, only __syncwarp around the reuse.
-__device__ __forceinline__ const float *stage_bias(const TcParams &p, float *bias_smem, int n0) {
+__device__ __forceinline__ const float *stage_bias(const TcParams &p, float *bias_smem, int n0, int bn = BN) {
     if (!p.bias) return nullptr;
     const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & 3;
     float *dst = bias_smem + w * BN;
     __syncwarp();                                   // the previous tile's reads of the strip are done
-    for (int j = lane; j < BN; j += 32) dst[j] = (n0 + j < p.N) ? __ldg(p.bias + n0 + j) : 0.f;
+    for (int j = lane; j < bn; j += 32) dst[j] = (n0 + j < p.N) ? __ldg(p.bias + n0 + j) : 0.f;
     __syncwarp();
     return dst;
 }
@@ -518,8 +520,10 @@ __device__ __forceinline__ void staged_block(const TcParams &p, const CUtensorMa
     ++stores;
 }
 
-// ET: operand element type (__nv_bfloat16 or float-as-tf32).
-template <typename ET>
+// ET: operand element type (__nv_bfloat16 or float-as-tf32).  BN_: columns of one output tile, 256 or 128; the
+// narrow tile is for problems whose 128 x 256 tiles would leave most SMs idle (it doubles the tile count and
+// halves the padding a narrow N pays for).
+template <typename ET, int BN_>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const TcParams p) {
@@ -529,6 +533,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int CH = ROW_BYTES / ES;            // MN elements per 128-byte chunk of an MN-major tile
     constexpr int UMMA_K_BYTES = 32;              // 16 bf16 / 8 tf32 per instruction
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;   // 4 instructions per stage
+    constexpr int STAGES = onecta_stages(BN_);
+    constexpr int STAGE_BYTES = A_STAGE + BN_ * ROW_BYTES;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -600,7 +606,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (t < 0) break;
                 int tm, tn;
                 tile_coords(t, p.num_m_tiles, p.num_n_tiles, p.band, tm, tn);
-                const int m0 = tm * BM, n0 = tn * BN;
+                const int m0 = tm * BM, n0 = tn * BN_;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
@@ -615,10 +621,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             tma_load_2d(sa + c * (BK * ROW_BYTES), &tmA, m0 + c * CH, k0, full_bar(s));
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(sb, &tmB, k0, n0, full_bar(s));                       // box {BK, 256}
+                        tma_load_2d(sb, &tmB, k0, n0, full_bar(s));                       // box {BK, BN_}
                     } else {
 #pragma unroll
-                        for (int c = 0; c < BN / CH; ++c)
+                        for (int c = 0; c < BN_ / CH; ++c)
                             tma_load_2d(sb + c * (BK * ROW_BYTES), &tmB, n0 + c * CH, k0, full_bar(s));
                     }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
@@ -653,7 +659,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN_);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 3)) { ok = false; break; }
                     ZN_PHASE(p, 3);
@@ -694,10 +700,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_after();
             const int warp_row0 = tm * BM + q * 32;
             const long long row = (long long)warp_row0 + lane;
-            const int n0 = tn * BN;
-            const float *bias_s = stage_bias(p, bias_smem, n0);
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
+            const int n0 = tn * BN_;
+            const float *bias_s = stage_bias(p, bias_smem, n0, BN_);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN_);
+            const int nchunks = min(BN_ / 32, (p.N - n0 + 31) / 32);
             for (int c = 0; c < nchunks; ++c) {
                 uint32_t r[32];
                 ZN_CLK(c, 0);
@@ -1149,39 +1155,57 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const int es = elem_type == 0 ? 2 : 4;
     const int bk = ROW_BYTES / es, ch = ROW_BYTES / es;
 
+    using OneFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TcParams);
     static std::atomic<uint64_t> attr_set_mask{0};   // cudaFuncSetAttribute is per device
     const uint64_t dev_bit = 1ull << (ctx->device & 63);
     if (!(attr_set_mask.load() & dev_bit)) {
-        ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          SMEM_BYTES));
-        ZN_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         // Ask for the full 228 KB shared-memory split rather than the smallest one that fits this kernel:
         // the ~30 KB left over let the small reduction and update kernels of the other lanes share the SM.
-        cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
-        cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
+        for (OneFn f : {(OneFn)gemm_tc_kernel<__nv_bfloat16, 256>, (OneFn)gemm_tc_kernel<float, 256>}) {
+            ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, onecta_smem(256)));
+            cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        }
+        for (OneFn f : {(OneFn)gemm_tc_kernel<__nv_bfloat16, 128>, (OneFn)gemm_tc_kernel<float, 128>}) {
+            ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, onecta_smem(128)));
+            cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        }
         cudaGetLastError();
         attr_set_mask.fetch_or(dev_bit);
     }
+
+    // Which kernel.  The two-CTA kernel halves the operand traffic per SM and wins wherever the main loop is long.
+    // With a short main loop (K of at most 16 k-blocks: 1024 bf16 / 512 tf32 values) a tile is over before the
+    // pair's cluster-wide hand-shakes pay off and the one-CTA kernel is faster: measured in bf16, 65536 x 512 x 512
+    // 665 against 510-530 TFLOP/s, 1024^3 114-128 against 103, 256^3 12.8 against 16.8 us per launch.
+    // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
+    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
+    const int num_k_blocks = (int)((k + bk - 1) / bk);
+    const bool use_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && num_k_blocks > 16));
+    // Tile width of the one-CTA kernel: 128 columns instead of 256 where N fits one narrow tile, or where the wide
+    // tiles would occupy at most half the SMs (twice the tiles, each half the work).
+    // ZN_TC_NARROW=0 / 2: never / always in the one-CTA kernel (diagnostic).
+    static const int narrow_mode = getenv("ZN_TC_NARROW") ? atoi(getenv("ZN_TC_NARROW")) : 1;
+    const long long wide_tiles = (long long)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const bool narrow = !use_pair && (narrow_mode == 2 || (narrow_mode == 1 && (n <= 128 || 2 * wide_tiles <= ctx->sm_count - e.reserve_sms)));
+    const int bn = narrow ? 128 : BN;
 
     CUtensorMap tmA, tmB;
     const bool tf32 = elem_type != 0;
     if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM, 0));         // [m][k]: inner k
     else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk, tf32 ? 1 : 0));    // [k][m]: inner m
-    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, BN, 0));         // [n][k]: inner k
+    if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, use_pair ? HALF : bn, 0));   // [n][k]: inner k; the pair stages B in halves of 128 columns per CTA
     else ZN_TRY(make_tmap(ctx, &tmB, es, b, n, k, ldb, ch, bk, tf32 ? 1 : 0));    // [k][n]: inner n
 
     TcParams p;
     p.M = (int)m; p.N = (int)n; p.K = (int)k;
     p.num_m_tiles = (int)((m + BM - 1) / BM);
-    p.num_n_tiles = (int)((n + BN - 1) / BN);
-    p.num_k_blocks = (int)((k + bk - 1) / bk);
+    p.num_n_tiles = (int)((n + bn - 1) / bn);
+    p.num_k_blocks = num_k_blocks;
     p.a_mn = a_mn ? 1 : 0;
     p.b_mn = b_mn ? 1 : 0;
     const uint32_t fmt = elem_type == 0 ? 1u /* bf16 */ : 2u /* tf32 */;
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
-              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+              ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     p.mn_lbo = (uint32_t)(bk * ROW_BYTES);
     p.mn_sbo = tf32 ? 512 : 1024;
 #ifdef ZN_DIAG
@@ -1233,7 +1257,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.dynamic_tiles = (dyn && ctx->lane == ZN_LANE_MAIN) ? 1 : 0;
     {
         // a launch in which every CTA (or CTA pair) has at most one tile has nothing to hand out
-        const bool would_pair = m > BM && p.num_k_blocks > 16;
+        const bool would_pair = use_pair;
         const long long units = would_pair ? (long long)((m + 2 * BM - 1) / (2 * BM)) * p.num_n_tiles : (long long)p.num_m_tiles * p.num_n_tiles;
         const long long workers = would_pair ? ctx->sm_count / 2 - (e.reserve_sms + 1) / 2 : ctx->sm_count - e.reserve_sms;
         if (units <= workers) p.dynamic_tiles = 0;
@@ -1250,13 +1274,6 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
 
     zn_launch_scope scope(ctx, ZN_PROF_GEMM_TC, 2.0 * m * n * k,
                           (double)es * (m * k + k * n) + (e.out_f32 ? 4.0 : (double)es) * m * n);
-    // Which kernel.  The two-CTA kernel halves the operand traffic per SM and wins wherever the main loop is long.
-    // With a short main loop (K of at most 16 k-blocks: 1024 bf16 / 512 tf32 values) a tile is over before the
-    // pair's cluster-wide hand-shakes pay off and the one-CTA kernel is faster: measured in bf16, 65536 x 512 x 512
-    // 665 against 510-530 TFLOP/s, 1024^3 114-128 against 103, 256^3 12.8 against 16.8 us per launch.
-    // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
-    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
-    const bool use_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && p.num_k_blocks > 16));
     // Output path.  Either every thread stores its own row of the tile straight from the registers the accumulator
     // was read into (32-byte pieces, one row per lane: an instruction touches 32 different lines, and the L1 store
     // path takes about two cycles per line, 5 us for a 128 x 256 fp32 tile), or the epilogue warps stage 32 x 32
@@ -1282,8 +1299,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         }
     }
     if (use_pair) {
-        // two-CTA kernel: 256 x 256 tiles, B staged in halves of 128 columns per CTA
-        if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, HALF, 0));
+        // two-CTA kernel: 256 x 256 tiles
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | ((uint32_t)((2 * HALF) >> 4) << 24);   // M = 256 across the pair
         const long long pair_tiles = (long long)((m + 2 * HALF - 1) / (2 * HALF)) * p.num_n_tiles;
         int max_clusters = ctx->sm_count / 2 - (e.reserve_sms + 1) / 2;
@@ -1347,8 +1363,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     const int sms = ctx->sm_count - e.reserve_sms > 0 ? ctx->sm_count - e.reserve_sms : 1;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmC, p);
-    else gemm_tc_kernel<float><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmC, p);
+    if (narrow) {
+        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 128><<<grid, THREADS, onecta_smem(128), ctx->stream>>>(tmA, tmB, tmC, p);
+        else gemm_tc_kernel<float, 128><<<grid, THREADS, onecta_smem(128), ctx->stream>>>(tmA, tmB, tmC, p);
+    } else {
+        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 256><<<grid, THREADS, onecta_smem(256), ctx->stream>>>(tmA, tmB, tmC, p);
+        else gemm_tc_kernel<float, 256><<<grid, THREADS, onecta_smem(256), ctx->stream>>>(tmA, tmB, tmC, p);
+    }
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return launch_failed(le, "launch of the tensor-core GEMM");
 #ifdef ZN_DIAG
