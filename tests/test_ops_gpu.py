@@ -42,6 +42,17 @@ def _oracle(orient, sa, sb, m, n, k, c=None, acc=False):
     return f(sa, sb, m, n, k, c=c, accumulate=acc)
 
 
+def _reference(orient, sa, sb, m, n, k):
+    """The oracle's product; for the few shapes of more than 10^9 multiply-adds, which its plain loops would take
+    minutes over, the same product in float64 (the tensor-core tolerances below are far wider than the 1e-6 by
+    which the oracle's fp32 sums and float64 differ)."""
+    if m * n * k <= 1_000_000_000:
+        return _oracle(orient, sa, sb, m, n, k)
+    a = sa.astype(np.float64).reshape((k, m) if orient == "TN" else (m, k))
+    b = sb.astype(np.float64).reshape((n, k) if orient == "NT" else (k, n))
+    return ((a.T if orient == "TN" else a) @ (b.T if orient == "NT" else b)).astype(np.float32)
+
+
 def _gpu(be, orient, sa, sb, m, n, k, c=None, acc=False):
     out = np.zeros((m, n), np.float32) if c is None else c.copy()
     f = {"NN": be.matMul, "TN": be.matMulTransposeA, "NT": be.matMulTransposeB}[orient]
@@ -95,14 +106,15 @@ def test_gemm_accumulate(be, orient):
     assert_close(_gpu(be, orient, sa, sb, m, n, k, c=c0, acc=True), want, 2e-2)
 
 
-# Short main loops (K up to 1024 bf16 / 512 tf32 values) and single row tiles run the one-CTA kernel, the rest the
-# two-CTA kernel: the last three shapes of the first two rows have more than one row tile AND a long K in both
-# precisions.  The one-CTA kernel takes 128-column tiles where N fits one or the 256-column tiles would fill at
-# most half the SMs (every shape of the first row, and the third row), 256-column tiles otherwise (the fourth row).
+# Routing.  The two-CTA kernel takes products with more than one row tile, a long K (more than 1024 bf16 / 512 tf32
+# values) AND more 256 x 256 tiles than the GPU has SM pairs (74): the last row.  Everything else runs the one-CTA
+# kernel, with 128-column tiles where N fits one or the 256-column tiles would fill at most half the SMs (rows one
+# to three), with 256-column tiles otherwise (row four).
 TC_SHAPES = [(128, 256, 64), (256, 512, 256), (300, 200, 100), (130, 10, 256), (1024, 512, 784), (64, 2048, 1500),
              (2048, 1024, 512), (384, 320, 2304), (300, 520, 1100), (513, 260, 4100),
              (1024, 1024, 1024), (200, 136, 96), (256, 384, 512),
-             (4096, 1200, 256), (2500, 2304, 200)]
+             (4096, 1200, 256), (2500, 2304, 200),
+             (2048, 2560, 1100), (1300, 3900, 2304)]
 
 
 @pytest.mark.parametrize("prec", [P.BF16_TC, P.TF32_TC])
@@ -115,12 +127,12 @@ def test_gemm_tensor_core(be, prec, orient, shape):
     be.set_precision(prec)
     # (1) raw fp32 inputs: the bar for the tensor-core path is 2e-2
     sa, sb = _store(orient, a, b)
-    want = _oracle(orient, sa, sb, m, n, k)
+    want = _reference(orient, sa, sb, m, n, k)
     assert_close(_gpu(be, orient, sa, sb, m, n, k), want, 2e-2, f"{prec.name} {orient} {shape}")
     # (2) inputs already representable in the operand type: only accumulation order differs
     rnd = round_bf16 if prec == P.BF16_TC else trunc_tf32
     sa, sb = _store(orient, rnd(a), rnd(b))
-    want = _oracle(orient, sa, sb, m, n, k)
+    want = _reference(orient, sa, sb, m, n, k)
     # The tensor cores add their products into fp32 without rounding every partial sum to nearest, so what is left
     # grows with the length of the sum: measured 1.08e-5 (tf32) at K = 4100, below 5e-6 up to K = 2304.
     tol = 1e-5 * max(1.0, (k / 1024.0) ** 0.5)
@@ -505,10 +517,11 @@ print("forced-kernel checks ok")
 
 @pytest.mark.parametrize("env", [{"ZN_TC_PAIR": "2"}, {"ZN_TC_PAIR": "2", "ZN_TC_STAGED_STORE": "1"}, {"ZN_TC_PAIR": "0"},
                                  {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "0"}, {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "2"},
-                                 {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "2", "ZN_TC_STAGED_STORE": "0"}],
+                                 {"ZN_TC_PAIR": "0", "ZN_TC_NARROW": "2", "ZN_TC_STAGED_STORE": "0"},
+                                 {"ZN_TC_PAIR": "2", "ZN_TC_PAIR8": "2"}],
                          ids=["two-CTA everywhere", "two-CTA with staged TMA stores", "one-CTA everywhere",
                               "one-CTA, 256-column tiles only", "one-CTA, 128-column tiles only",
-                              "one-CTA, 128-column tiles, per-thread stores"])
+                              "one-CTA, 128-column tiles, per-thread stores", "two-CTA with 8 epilogue warps"])
 def test_each_tensor_core_kernel_on_shapes_the_default_routes_elsewhere(env):
     """The library picks the one-CTA or the two-CTA kernel and the one-CTA kernel's tile width by shape, and the
     two-CTA kernel's shared-memory-staged bulk-store epilogue is an option.  The choices are read once per process, so each forced combination runs in a

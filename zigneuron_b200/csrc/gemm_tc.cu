@@ -1,15 +1,15 @@
 // tcgen05 / TMEM GEMM for the three Dense products on sm_100a.
 //
-// One persistent CTA per SM walks 128 x 256 output tiles.  Warp 0 feeds a
-// 3-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
-// every CTA loads its own tiles); one thread of warp 1 issues tcgen05.mma (cta_group::1, M=128,
-// N=256) into one of two 256-column fp32 accumulators in tensor memory; warps
-// 2..5 drain the other accumulator with tcgen05.ld and apply the fused epilogue
-// (bias, activation, activation-derivative mask, accumulate, down-convert), so
-// the epilogue of tile i overlaps the main loop of tile i+1.  Results leave through
-// shared memory and bulk tensor stores (whole 128-byte lines) or, where that is not
-// possible, as per-thread stores.  A two-CTA variant of the same kernel (further
-// down) takes every product with a long main loop.
+// One persistent CTA per SM walks 128 x 256 output tiles (128 x 128 where the wide tiles would leave
+// most SMs idle).  Warp 0 feeds a 3-stage (narrow tiles: 4-stage) shared-memory ring with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, every CTA loads its own tiles); one thread of warp 1 issues
+// tcgen05.mma (cta_group::1, M=128, N=256 or 128) into one of two fp32 accumulators in tensor memory; warps
+// 2..9 drain the other accumulator with tcgen05.ld (two warps per quarter of the rows, half the columns
+// each) and apply the fused epilogue (bias, activation, activation-derivative mask, accumulate,
+// down-convert), so the epilogue of tile i overlaps the main loop of tile i+1.  Results leave through
+// shared memory and bulk tensor stores (whole 128-byte lines) or, where that is not possible, as
+// per-thread stores.  A two-CTA variant of the same kernel (further down) takes every product with a
+// long main loop.
 //
 // The three orientations of the reference (Backend.matMul, matMulTransposeB,
 // matMulTransposeA; src/backend.zig:169-195, :298-325) differ only in which
@@ -36,22 +36,26 @@
 namespace {
 
 constexpr int BM = 128, BN = 256;
-// one-CTA kernel, beside 32 KiB of output staging: 3 x 48 KiB of operands for 256-column tiles, 5 x 32 KiB for 128-column ones
-__host__ __device__ constexpr int onecta_stages(int bn) { return bn == 256 ? 3 : 5; }
+// one-CTA kernel, beside 64 KiB of output staging: 3 x 48 KiB of operands for 256-column tiles, 4 x 32 KiB for
+// 128-column ones; a launch that stores per thread has the room for a fourth stage of 48 KiB
+__host__ __device__ constexpr int onecta_stages(int bn, bool staging) { return bn == 256 ? (staging ? 3 : 4) : 4; }
 constexpr int TQ = 4;                               // depth of the tile-index ring inside a CTA
 constexpr int ROW_BYTES = 128;                    // one swizzle row
 constexpr int A_STAGE = BM * ROW_BYTES;           // 16 KiB
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;                        // two-CTA kernel: producer warp, MMA warp, 4 epilogue warps
+constexpr int EPI1 = 8;                             // one-CTA kernel: 8 epilogue warps, two per quarter of the accumulator's rows
+constexpr int THREADS1 = 64 + 32 * EPI1;
 constexpr int TMEM_COLS = 512;
 constexpr int BIAS_SMEM = 4 * BN * 4;                 // one tile's bias values, a private copy per epilogue warp
 constexpr int STG_BUF = 4096;                         // one staged 32 x 32 output block (fp32; 16-bit blocks use half)
-constexpr int STAGING_BYTES = 4 * 2 * STG_BUF;        // two blocks per epilogue warp
+constexpr int STAGING1_BYTES = EPI1 * 2 * STG_BUF;    // two blocks per epilogue warp of the one-CTA kernel
 // after the operand ring: barriers (256 B), the bias strips, then (1024-aligned) the output staging buffers
 constexpr int RING_TAIL = ((256 + BIAS_SMEM + 1023) / 1024) * 1024;
-constexpr int onecta_smem(int bn) {
-    return 1024 /* alignment slack */ + onecta_stages(bn) * (A_STAGE + bn * ROW_BYTES) + RING_TAIL + STAGING_BYTES;
+constexpr int onecta_smem(int bn, bool staging) {
+    return 1024 /* alignment slack */ + onecta_stages(bn, staging) * (A_STAGE + bn * ROW_BYTES) + RING_TAIL +
+           (staging ? STAGING1_BYTES : 0);
 }
-static_assert(onecta_smem(256) <= 232448 && onecta_smem(128) <= 232448,
+static_assert(onecta_smem(256, true) <= 232448 && onecta_smem(256, false) <= 232448 && onecta_smem(128, true) <= 232448,
               "the one-CTA kernel must fit the 227 KB of shared memory a CTA may have");
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
@@ -108,6 +112,12 @@ __device__ long long zn_diag_clk[128];
     } while (0)
 // diagnostic builds: SM clock of one point of tile number `it` (as counted by the role) in the leader CTA of cluster 0
 __device__ long long zn_diag_tile[8 * 16];
+// diagnostic builds, one-CTA kernel, CTA 0: cycles its MMA thread spent waiting for a free accumulator [0] and for
+// operands [1], its cycles from first to last tile [2], its tiles [3]; cycles epilogue warp 2 spent waiting for a
+// full accumulator [4] and working on one [5]
+__device__ long long zn_diag_wait[8];
+#define ZN_WAIT_BEGIN() const long long w0__ = clock64()
+#define ZN_WAIT_END(slot) do { if (blockIdx.x == 0) zn_diag_wait[slot] += clock64() - w0__; } while (0)
 #define ZN_TILE_CLK(it, point)                                                                         \
     do {                                                                                               \
         if (blockIdx.x == 0 && (it) < 8) zn_diag_tile[(it) * 16 + (point)] = clock64();               \
@@ -116,6 +126,8 @@ __device__ long long zn_diag_tile[8 * 16];
 #define ZN_PHASE(p, i) do { } while (0)
 #define ZN_CLK(c, point) do { } while (0)
 #define ZN_TILE_CLK(it, point) do { } while (0)
+#define ZN_WAIT_BEGIN() do { } while (0)
+#define ZN_WAIT_END(slot) do { } while (0)
 #endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -447,19 +459,6 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams &p, long long row,
     }
 }
 
-// Each epilogue warp copies the tile's BN bias values into its own strip of shared memory once, instead of
-// every thread fetching all of them from global memory through an L1 that the shared-memory split leaves
-// tiny.  A private strip per warp needs no barrier between warps, only __syncwarp around the reuse.
-__device__ __forceinline__ const float *stage_bias(const TcParams &p, float *bias_smem, int n0, int bn = BN) {
-    if (!p.bias) return nullptr;
-    const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & 3;
-    float *dst = bias_smem + w * BN;
-    __syncwarp();                                   // the previous tile's reads of the strip are done
-    for (int j = lane; j < bn; j += 32) dst[j] = (n0 + j < p.N) ? __ldg(p.bias + n0 + j) : 0.f;
-    __syncwarp();
-    return dst;
-}
-
 // Staged output.  One epilogue warp owns two 4 KiB shared-memory buffers; a buffer holds the warp's 32 rows of one
 // 32-column block in the layout the tensor map's swizzle expects (fp32: 128-byte rows, 16-byte unit j of row r at
 // position j ^ (r & 7); 16-bit: 64-byte rows, unit j at j ^ ((r >> 1) & 3)), which also spreads the 16-byte stores
@@ -522,9 +521,10 @@ __device__ __forceinline__ void staged_block(const TcParams &p, const CUtensorMa
 
 // ET: operand element type (__nv_bfloat16 or float-as-tf32).  BN_: columns of one output tile, 256 or 128; the
 // narrow tile is for problems whose 128 x 256 tiles would leave most SMs idle (it doubles the tile count and
-// halves the padding a narrow N pays for).
-template <typename ET, int BN_>
-__global__ void __launch_bounds__(THREADS, 1)
+// halves the padding a narrow N pays for).  STAGED_: room for the output staging buffers; without them (launches
+// that store per thread) the operand ring of the wide tile gets a fourth stage.
+template <typename ET, int BN_, bool STAGED_>
+__global__ void __launch_bounds__(THREADS1, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const TcParams p) {
     constexpr bool TF32 = sizeof(ET) == 4;
@@ -533,7 +533,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int CH = ROW_BYTES / ES;            // MN elements per 128-byte chunk of an MN-major tile
     constexpr int UMMA_K_BYTES = 32;              // 16 bf16 / 8 tf32 per instruction
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;   // 4 instructions per stage
-    constexpr int STAGES = onecta_stages(BN_);
+    constexpr int STAGES = onecta_stages(BN_, STAGED_);
     constexpr int STAGE_BYTES = A_STAGE + BN_ * ROW_BYTES;
 
     extern __shared__ uint8_t smem_raw[];
@@ -563,8 +563,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
         if (p.out_mode) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
-        for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }   // MMA thread + 4 epilogue warps
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EPI1); }
+        for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 1 + EPI1); }   // MMA thread + the epilogue warps
         if (blockIdx.x == 0 && p.dynamic_tiles) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -592,13 +592,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             int q = 0;
             uint32_t qphase = 0;
-            int prev_t = 0;
-            for (bool first = true; ok; first = false) {
-                // next tile: the CTA's own first, then whatever the grid has not started yet
-                int t = first ? (int)blockIdx.x
-                              : (p.dynamic_tiles ? (int)(gridDim.x + atomicAdd(p.tile_counter, 1u)) : prev_t + (int)gridDim.x);
-                prev_t = t;
+            // Tiles: the CTA's own first, then whatever the grid has not started yet.  The index of the tile AFTER the
+            // one about to be loaded is drawn now, so that the atomic's round trip to L2 hides behind a tile of loads.
+            int t_next = (int)blockIdx.x;
+            while (ok) {
+                int t = t_next;
                 if (t >= num_tiles) t = -1;
+                if (t >= 0) t_next = p.dynamic_tiles ? (int)(gridDim.x + atomicAdd(p.tile_counter, 1u)) : t + (int)gridDim.x;
                 if (!mbar_wait(sempty_bar(q), qphase ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
                 tile_ring[q] = t;
                 mbar_arrive(sfull_bar(q));            // release: the MMA and epilogue warps read the slot after this
@@ -657,11 +657,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (t < 0) break;
                 const int buf = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                {
+                    ZN_WAIT_BEGIN();
+                    if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                    ZN_WAIT_END(0);
+                }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN_);
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 3)) { ok = false; break; }
+                    {
+                        ZN_WAIT_BEGIN();
+                        if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, 3)) { ok = false; break; }
+                        ZN_WAIT_END(1);
+                    }
                     ZN_PHASE(p, 3);
                     tc_fence_after();
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_STAGE;
@@ -676,11 +684,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 if (ok) tc_commit(tfull_bar(buf));    // accumulator complete
                 ZN_PHASE(p, 4);
+#ifdef ZN_DIAG
+                if (blockIdx.x == 0) {
+                    if (it == 0) zn_diag_wait[6] = clock64();
+                    zn_diag_wait[2] = clock64() - zn_diag_wait[6];
+                    zn_diag_wait[3] = it + 1;
+                }
+#endif
             }
         }
     } else {
-        // ================= epilogue: warps 2..5, TMEM lanes 32*(warp%4).. =================
+        // ================= epilogue: warps 2..9 =================
+        // A warp reads the TMEM lanes 32 * (warp % 4) .., i.e. that quarter of the tile's rows; the two warps of a
+        // quarter take one half of the tile's columns each.
+        const int ew = warp - 2;                       // 0..7: staging buffers and bias strip of this warp
         const int q = warp & 3;
+        const int h = ew >> 2;                         // which half of the columns
+        constexpr int HALF_CHUNKS = BN_ / 64;          // 32-column blocks per half
+        float *bias_strip = bias_smem + ew * (BN_ / 2);
         int it = 0, sq = 0;
         uint32_t sqphase = 0, stores = 0;
         bool ok = true;
@@ -695,38 +716,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tile_coords(t, p.num_m_tiles, p.num_n_tiles, p.band, tm, tn);
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-            if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
-            if (q == 2 && lane == 0) ZN_PHASE(p, 5);
-            tc_fence_after();
             const int warp_row0 = tm * BM + q * 32;
             const long long row = (long long)warp_row0 + lane;
             const int n0 = tn * BN_;
-            const float *bias_s = stage_bias(p, bias_smem, n0, BN_);
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN_);
             const int nchunks = min(BN_ / 32, (p.N - n0 + 31) / 32);
-            for (int c = 0; c < nchunks; ++c) {
+            const int c_begin = h * HALF_CHUNKS, c_end = min(nchunks, c_begin + HALF_CHUNKS);
+            if (p.bias) {
+                // The warp copies its half of the tile's bias values into its own strip of shared memory once, instead
+                // of every thread fetching all of them from global memory through an L1 that the shared-memory split
+                // leaves tiny.  A private strip per warp needs no barrier between warps.
+                __syncwarp();                          // the previous tile's reads of the strip are done
+                for (int j = lane; j < BN_ / 2; j += 32) {
+                    const int col = n0 + c_begin * 32 + j;
+                    bias_strip[j] = col < p.N ? __ldg(p.bias + col) : 0.f;
+                }
+                __syncwarp();
+            }
+            {
+                ZN_WAIT_BEGIN();
+                if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+                if (threadIdx.x == 64) ZN_WAIT_END(4);
+            }
+            if (warp == 2 && lane == 0) ZN_PHASE(p, 5);
+#ifdef ZN_DIAG
+            const long long e0__ = clock64();
+#endif
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN_);
+            if (c_begin >= c_end) {                    // a ragged last tile may leave this warp's half empty
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));
+            }
+            for (int c = c_begin; c < c_end; ++c) {
                 uint32_t r[32];
                 ZN_CLK(c, 0);
                 tc_ld32(taddr + (uint32_t)(c * 32), r);
                 tc_wait_ld();
-                if (c == nchunks - 1) {
-                    // all reads of this accumulator are done: hand it back to the MMA warp
+                if (c == c_end - 1) {
+                    // all of this warp's reads of the accumulator are done: hand it back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
-                if (p.out_mode == 0) {
+                const float *bias_s = p.bias ? bias_strip + (c - c_begin) * 32 : nullptr;
+                if (!STAGED_ || p.out_mode == 0) {
                     ZN_CLK(c, 1);
-                    if (row < p.M) epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+                    if (row < p.M) epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s);
                     ZN_CLK(c, 6);
                 } else if (warp_row0 < p.M) {            // uniform over the warp
-                    staged_block<TF32>(p, &tmC, staging + (uint32_t)(q * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r,
-                                       bias_s ? bias_s + c * 32 : nullptr, stores, c);
+                    staged_block<TF32>(p, &tmC, staging + (uint32_t)(ew * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r, bias_s,
+                                       stores, c);
                 }
             }
-            if (q == 2 && lane == 0) ZN_PHASE(p, 6);
+            if (warp == 2 && lane == 0) ZN_PHASE(p, 6);
+#ifdef ZN_DIAG
+            if (blockIdx.x == 0 && threadIdx.x == 64) zn_diag_wait[5] += clock64() - e0__;
+#endif
         }
-        if (lane == 0 && p.out_mode) bulk_wait_read<0>();   // the TMA unit has read every staged block; the writes complete with the kernel
+        if (STAGED_ && lane == 0 && p.out_mode) bulk_wait_read<0>();   // the TMA unit has read every staged block; the writes complete with the kernel
     }
     if (threadIdx.x == 0) ZN_PHASE(p, 7);
 
@@ -760,9 +808,10 @@ constexpr int A2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int B2_STAGE = HALF * ROW_BYTES;        // 16 KiB
 constexpr int STAGE2_BYTES = A2_STAGE + B2_STAGE;
 constexpr int PAIR_TAIL = RING_TAIL;
-constexpr int smem2_bytes(int stages, bool staging) {
-    return 1024 /* alignment slack */ + stages * STAGE2_BYTES + PAIR_TAIL + (staging ? STAGING_BYTES : 0);
+constexpr int smem2_bytes(int stages, bool staging, int epi_warps = 4) {
+    return 1024 /* alignment slack */ + stages * STAGE2_BYTES + PAIR_TAIL + (staging ? epi_warps * 2 * STG_BUF : 0);
 }
+static_assert(smem2_bytes(4, true, 8) <= 232448, "the two-CTA kernel with 8 epilogue warps keeps 4 stages");
 static_assert(smem2_bytes(STAGES2, true) <= 232448 && smem2_bytes(6, false) <= smem2_bytes(STAGES2, true),
               "the two-CTA kernel must fit the 227 KB of shared memory a CTA may have");
 
@@ -814,8 +863,11 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
     }
 }
 
-template <typename ET, int NST>
-__global__ void __launch_bounds__(THREADS, 1)
+// EPI_: epilogue warps per CTA.  4 (one per quarter of the CTA's rows), the form every default route uses: a long
+// main loop hides the epilogue.  8 (two per quarter, half the columns each, always with staged stores) is an
+// option for short main loops (see zn_gemm_tc).
+template <typename ET, int NST, int EPI_>
+__global__ void __launch_bounds__(64 + 32 * EPI_, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const TcParams p) {
     constexpr bool TF32 = sizeof(ET) == 4;
@@ -850,10 +902,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
         if (p.out_mode) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
         for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps x 2 CTAs
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 2 * EPI_); }   // the epilogue warps of both CTAs
         // tile-index ring: the leader's producer publishes into both CTAs; its `empty` side counts every reader
-        // of the pair: leader MMA thread + 4 leader epilogue warps + peer producer + 4 peer epilogue warps
-        for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 10); }
+        // of the pair: leader MMA thread + leader epilogue warps + peer producer + peer epilogue warps
+        for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 2 + 2 * EPI_); }
         if (blockIdx.x == 0 && p.dynamic_tiles) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -989,8 +1041,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
         }
     } else {
-        // ================= epilogue (both CTAs): warps 2..5, this CTA's 128 rows =================
+        // ================= epilogue (both CTAs): warps 2.., this CTA's 128 rows =================
+        // A warp reads the TMEM lanes 32 * (warp % 4) ..; with 8 warps the two warps of a quarter take half the
+        // columns each.
+        const int ew = warp - 2;
         const int q = warp & 3;
+        constexpr int PARTS = EPI_ / 4;                    // column parts of a tile: 1 or 2
+        constexpr int PART_CHUNKS = (BN / 32) / PARTS;     // 32-column blocks per part
+        const int c_first = (ew >> 2) * PART_CHUNKS;
+        float *bias_strip = bias_smem + ew * (BN / PARTS);
         int it = 0, sq = 0;
         uint32_t stores = 0;                              // staged blocks this warp has handed to the TMA unit
         uint32_t sqphase = 0;
@@ -1007,32 +1066,46 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tile_coords(t, num_m_pairs, p.num_n_tiles, p.band, tm, tn);
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-            if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
-            if (threadIdx.x == 64) ZN_TILE_CLK(it, 5);
-            tc_fence_after();
             const int warp_row0 = tm * 2 * HALF + (int)rank * HALF + q * 32;
             const long long row = (long long)warp_row0 + lane;
             const int n0 = tn * BN;
-            const float *bias_s = stage_bias(p, bias_smem, n0);
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
-            for (int c = 0; c < nchunks; ++c) {
+            const int c_end = min(nchunks, c_first + PART_CHUNKS);
+            if (p.bias) {
+                // the warp's own copy of its part of the tile's bias values (no barrier between warps needed)
+                __syncwarp();                              // the previous tile's reads of the strip are done
+                for (int j = lane; j < BN / PARTS; j += 32) {
+                    const int col = n0 + c_first * 32 + j;
+                    bias_strip[j] = col < p.N ? __ldg(p.bias + col) : 0.f;
+                }
+                __syncwarp();
+            }
+            if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
+            if (threadIdx.x == 64) ZN_TILE_CLK(it, 5);
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            if (c_first >= c_end) {                        // a ragged last tile may leave this warp's part empty
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+            }
+            for (int c = c_first; c < c_end; ++c) {
                 uint32_t r[32];
                 tc_ld32(taddr + (uint32_t)(c * 32), r);
                 tc_wait_ld();
-                if (c == nchunks - 1) {
+                if (c == c_end - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));   // to the leader's MMA thread
                 }
+                const float *bias_s = p.bias ? bias_strip + (c - c_first) * 32 : nullptr;
                 if (p.out_mode == 0) {
                     if (row >= p.M) continue;
-                    epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s ? bias_s + c * 32 : nullptr);
+                    epilogue_chunk<TF32>(p, row, n0 + c * 32, r, bias_s);
                     continue;
                 }
                 if (warp_row0 >= p.M) continue;          // the warp's 32 rows all lie below C (uniform over the warp)
-                staged_block<TF32>(p, &tmC, staging + (uint32_t)(q * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r,
-                                   bias_s ? bias_s + c * 32 : nullptr, stores);
+                staged_block<TF32>(p, &tmC, staging + (uint32_t)(ew * 2) * STG_BUF, lane, warp_row0, n0 + c * 32, r, bias_s, stores);
             }
             if (threadIdx.x == 64) ZN_TILE_CLK(it, 6);
         }
@@ -1161,13 +1234,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     if (!(attr_set_mask.load() & dev_bit)) {
         // Ask for the full 228 KB shared-memory split rather than the smallest one that fits this kernel:
         // the ~30 KB left over let the small reduction and update kernels of the other lanes share the SM.
-        for (OneFn f : {(OneFn)gemm_tc_kernel<__nv_bfloat16, 256>, (OneFn)gemm_tc_kernel<float, 256>}) {
-            ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, onecta_smem(256)));
-            cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        }
-        for (OneFn f : {(OneFn)gemm_tc_kernel<__nv_bfloat16, 128>, (OneFn)gemm_tc_kernel<float, 128>}) {
-            ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, onecta_smem(128)));
-            cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        const struct { OneFn f; int smem; } fns[] = {
+            {(OneFn)gemm_tc_kernel<__nv_bfloat16, 256, true>, onecta_smem(256, true)}, {(OneFn)gemm_tc_kernel<float, 256, true>, onecta_smem(256, true)},
+            {(OneFn)gemm_tc_kernel<__nv_bfloat16, 256, false>, onecta_smem(256, false)}, {(OneFn)gemm_tc_kernel<float, 256, false>, onecta_smem(256, false)},
+            {(OneFn)gemm_tc_kernel<__nv_bfloat16, 128, true>, onecta_smem(128, true)}, {(OneFn)gemm_tc_kernel<float, 128, true>, onecta_smem(128, true)}};
+        for (const auto &k : fns) {
+            ZN_CUDA(ctx, cudaFuncSetAttribute(k.f, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
+            cudaFuncSetAttribute(k.f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         }
         cudaGetLastError();
         attr_set_mask.fetch_or(dev_bit);
@@ -1180,7 +1253,33 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
     static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
     const int num_k_blocks = (int)((k + bk - 1) / bk);
-    const bool use_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && num_k_blocks > 16));
+    // A product whose 256 x 256 tiles do not fill the SM pairs more than once also goes to the one-CTA kernel: in a
+    // single wave nothing hides the epilogue of the large tile, and the smaller tiles reach more SMs.  Measured,
+    // one-CTA against two-CTA kernel: 2048^3 bf16 692-741 against 635-639 TFLOP/s, 1024^3 tf32 88-103 against 73-86,
+    // the 784-512-256-10 training step at batch 1024 in tf32 0.205 against 0.238 ms.
+    const long long pair_tiles_all = (long long)((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    const int pair_clusters = ctx->sm_count / 2 - (e.reserve_sms + 1) / 2;
+    const bool long_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && num_k_blocks > 16 && pair_tiles_all > pair_clusters));
+    // Option: a form of the two-CTA kernel with 8 epilogue warps and staged stores for short main loops with more
+    // than one wave of 256 x 256 tiles (per 128 x 256 of output and k-block it takes in 32 KB where the one-CTA
+    // kernel takes in 48 KB).  Measured against the one-CTA kernel in bf16: 65536 x 512 x 512 578-594 against
+    // 633-683 TFLOP/s, 4096 x 4096 x 512 488-493 against 552-573, 8192 x 2048 x 256 273-275 against 342-371 (tf32
+    // within 5 % either way): the pair's hand-over of tile indices across the cluster costs more per tile than
+    // the operand bytes saved, so it is off unless asked for.  It needs C to be stageable (see below).
+    // ZN_TC_PAIR8=1 / 2: for those short main loops / for every product the two-CTA kernel takes.
+    static const int pair8_mode = getenv("ZN_TC_PAIR8") ? atoi(getenv("ZN_TC_PAIR8")) : 0;
+    static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : -1;
+    const bool tf32 = elem_type != 0;
+    bool stageable = false;        // C is one block the TMA unit can address and is only written
+    if (!e.accumulate && (e.out_f32 != nullptr) != (e.out_t != nullptr)) {
+        const void *cptr = e.out_f32 ? (const void *)e.out_f32 : (const void *)e.out_t;
+        const int64_t ldc = e.out_f32 ? e.ld_out_f32 : e.ld_out_t;
+        const int ces = (e.out_f32 != nullptr || tf32) ? 4 : 2;
+        stageable = (reinterpret_cast<uintptr_t>(cptr) & 15) == 0 && (ldc * ces) % 16 == 0 && ldc >= n;
+    }
+    const bool short_pair = pair_mode == 1 && pair8_mode == 1 && m > BM && num_k_blocks <= 16 && pair_tiles_all > pair_clusters;
+    const bool pair8 = stageable && staged_mode != 0 && (short_pair || (long_pair && pair8_mode == 2));
+    const bool use_pair = long_pair || (short_pair && pair8);
     // Tile width of the one-CTA kernel: 128 columns instead of 256 where N fits one narrow tile, or where the wide
     // tiles would occupy at most half the SMs (twice the tiles, each half the work).
     // ZN_TC_NARROW=0 / 2: never / always in the one-CTA kernel (diagnostic).
@@ -1190,7 +1289,6 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const int bn = narrow ? 128 : BN;
 
     CUtensorMap tmA, tmB;
-    const bool tf32 = elem_type != 0;
     if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM, 0));         // [m][k]: inner k
     else ZN_TRY(make_tmap(ctx, &tmA, es, a, m, k, lda, ch, bk, tf32 ? 1 : 0));    // [k][m]: inner m
     if (!b_mn) ZN_TRY(make_tmap(ctx, &tmB, es, b, k, n, ldb, bk, use_pair ? HALF : bn, 0));   // [n][k]: inner k; the pair stages B in halves of 128 columns per CTA
@@ -1281,22 +1379,19 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     // have a short main loop and so wait for their epilogue, stages; the two-CTA kernel, whose epilogue hides under
     // the next tile's long main loop and whose TMA unit is busy with operand loads, stores per thread (measured
     // there, staged against per-thread: 16384^3 TN 1188 against 1245 TFLOP/s, the 8192-wide training step 58.1
-    // against 57.5 ms).  ZN_TC_STAGED_STORE=0 / 1 forces one path in both kernels (diagnostic).  Staging needs C to
+    // against 57.5 ms); its variant for short main loops stages.  ZN_TC_STAGED_STORE=0 / 1 forces one path in both
+    // kernels (diagnostic).  Staging needs C to
     // be ONE block the unit can address (16-byte aligned base and row pitch) that is only written; C += ..., two
     // outputs at once and odd pitches always take the per-thread stores.
-    static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : -1;
-    const bool want_staged = staged_mode < 0 ? !use_pair : staged_mode != 0;
+    const bool want_staged = pair8 || (staged_mode < 0 ? !use_pair : staged_mode != 0);
     CUtensorMap tmC;
     memset(&tmC, 0, sizeof tmC);
-    if (want_staged && !e.accumulate && (e.out_f32 != nullptr) != (e.out_t != nullptr)) {
+    if (want_staged && stageable) {
         const bool wide = e.out_f32 != nullptr || tf32;                  // 4-byte results
         const void *cptr = e.out_f32 ? (const void *)e.out_f32 : (const void *)e.out_t;
         const int64_t ldc = e.out_f32 ? e.ld_out_f32 : e.ld_out_t;
-        const int ces = wide ? 4 : 2;
-        if ((reinterpret_cast<uintptr_t>(cptr) & 15) == 0 && (ldc * ces) % 16 == 0 && ldc >= n) {
-            ZN_TRY(make_tmap(ctx, &tmC, ces, cptr, n, m, ldc, 32, 32, wide ? 0 : 2));
-            p.out_mode = wide ? 1 : 2;
-        }
+        ZN_TRY(make_tmap(ctx, &tmC, wide ? 4 : 2, cptr, n, m, ldc, 32, 32, wide ? 0 : 2));
+        p.out_mode = wide ? 1 : 2;
     }
     if (use_pair) {
         // two-CTA kernel: 256 x 256 tiles
@@ -1313,12 +1408,14 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         if (nst_env == 6 && p.out_mode == 0) nst = 6;
         using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TcParams);
         PairFn fn;
-        if (elem_type == 0) fn = nst == 4 ? gemm_tc_pair_kernel<__nv_bfloat16, 4> : nst == 6 ? gemm_tc_pair_kernel<__nv_bfloat16, 6> : gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>;
-        else fn = nst == 4 ? gemm_tc_pair_kernel<float, 4> : nst == 6 ? gemm_tc_pair_kernel<float, 6> : gemm_tc_pair_kernel<float, STAGES2>;
+        if (pair8) fn = elem_type == 0 ? (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4, 8> : (PairFn)gemm_tc_pair_kernel<float, 4, 8>;
+        else if (elem_type == 0) fn = nst == 4 ? gemm_tc_pair_kernel<__nv_bfloat16, 4, 4> : nst == 6 ? gemm_tc_pair_kernel<__nv_bfloat16, 6, 4> : gemm_tc_pair_kernel<__nv_bfloat16, STAGES2, 4>;
+        else fn = nst == 4 ? gemm_tc_pair_kernel<float, 4, 4> : nst == 6 ? gemm_tc_pair_kernel<float, 6, 4> : gemm_tc_pair_kernel<float, STAGES2, 4>;
         static std::atomic<uint64_t> pair_attr_mask{0};
         if (!(pair_attr_mask.load() & dev_bit)) {
-            for (PairFn f : {(PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, STAGES2>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 6>,
-                             (PairFn)gemm_tc_pair_kernel<float, 4>, (PairFn)gemm_tc_pair_kernel<float, STAGES2>, (PairFn)gemm_tc_pair_kernel<float, 6>}) {
+            for (PairFn f : {(PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, STAGES2, 4>, (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 6, 4>,
+                             (PairFn)gemm_tc_pair_kernel<float, 4, 4>, (PairFn)gemm_tc_pair_kernel<float, STAGES2, 4>, (PairFn)gemm_tc_pair_kernel<float, 6, 4>,
+                             (PairFn)gemm_tc_pair_kernel<__nv_bfloat16, 4, 8>, (PairFn)gemm_tc_pair_kernel<float, 4, 8>}) {
                 ZN_CUDA(ctx, cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2, true)));
                 cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             }
@@ -1327,8 +1424,8 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(2 * clusters));
-        cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = smem2_bytes(nst, nst != 6);
+        cfg.blockDim = dim3(pair8 ? 64 + 32 * 8 : THREADS);
+        cfg.dynamicSmemBytes = pair8 ? smem2_bytes(4, true, 8) : smem2_bytes(nst, nst != 6);
         cfg.stream = ctx->stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1364,11 +1461,14 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const int sms = ctx->sm_count - e.reserve_sms > 0 ? ctx->sm_count - e.reserve_sms : 1;
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (narrow) {
-        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 128><<<grid, THREADS, onecta_smem(128), ctx->stream>>>(tmA, tmB, tmC, p);
-        else gemm_tc_kernel<float, 128><<<grid, THREADS, onecta_smem(128), ctx->stream>>>(tmA, tmB, tmC, p);
+        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 128, true><<<grid, THREADS1, onecta_smem(128, true), ctx->stream>>>(tmA, tmB, tmC, p);
+        else gemm_tc_kernel<float, 128, true><<<grid, THREADS1, onecta_smem(128, true), ctx->stream>>>(tmA, tmB, tmC, p);
+    } else if (p.out_mode != 0) {
+        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 256, true><<<grid, THREADS1, onecta_smem(256, true), ctx->stream>>>(tmA, tmB, tmC, p);
+        else gemm_tc_kernel<float, 256, true><<<grid, THREADS1, onecta_smem(256, true), ctx->stream>>>(tmA, tmB, tmC, p);
     } else {
-        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 256><<<grid, THREADS, onecta_smem(256), ctx->stream>>>(tmA, tmB, tmC, p);
-        else gemm_tc_kernel<float, 256><<<grid, THREADS, onecta_smem(256), ctx->stream>>>(tmA, tmB, tmC, p);
+        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 256, false><<<grid, THREADS1, onecta_smem(256, false), ctx->stream>>>(tmA, tmB, tmC, p);
+        else gemm_tc_kernel<float, 256, false><<<grid, THREADS1, onecta_smem(256, false), ctx->stream>>>(tmA, tmB, tmC, p);
     }
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return launch_failed(le, "launch of the tensor-core GEMM");
@@ -1379,6 +1479,13 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         for (int i = 1; i <= 8; ++i)
             fprintf(stderr, " %d:%+.2fus", i, phase_host[i] ? (double)((long long)phase_host[i] - (long long)phase_host[0]) / 1e3 : -1.0);
         fprintf(stderr, "\n");
+        long long wt[8];
+        cudaMemcpyFromSymbol(wt, zn_diag_wait, sizeof wt);
+        fprintf(stderr, "  CTA 0: %lld tiles, %lld cycles from the first tile's last MMA to the last tile's; MMA thread waited %lld for a free accumulator, "
+                        "%lld for operands; epilogue warp 2 waited %lld for accumulators and worked %lld on them\n",
+                wt[3], wt[2], wt[0], wt[1], wt[4], wt[5]);
+        static const long long wzeros[8] = {0};
+        cudaMemcpyToSymbol(zn_diag_wait, wzeros, sizeof wzeros);
         long long clk[128];
         cudaMemcpyFromSymbol(clk, zn_diag_clk, sizeof clk);
         fprintf(stderr, "  epilogue clocks of warp 2 (cycles from the block's start: wait_ld, values, buffer free, staged, fence, issued):");
