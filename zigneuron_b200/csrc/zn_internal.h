@@ -2,6 +2,8 @@
 #pragma once
 
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 #include <cuda_bf16.h>
 
 #include <cstdint>
@@ -100,6 +102,30 @@ struct zn_launch_scope {
     zn_launch_scope(zn_ctx *c, int fam, double flops, double bytes, int n_launches = 1);
     ~zn_launch_scope();
 };
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while the stream's previous kernel
+// still runs, so it MUST execute zn_pdl_wait() before its first access to global memory.  Kernels that call
+// zn_pdl_release() at their start let the kernel after them (if launched this way) be scheduled at once.
+// ZN_TC_PDL=0 in the environment makes these ordinary launches (diagnostic).
+#ifdef __CUDACC__
+__device__ __forceinline__ void zn_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void zn_pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... Params, typename... Args>
+inline cudaError_t zn_launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    static const bool pdl = !(getenv("ZN_TC_PDL") && atoi(getenv("ZN_TC_PDL")) == 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+#endif
 
 enum { ZN_LANE_MAIN = 0, ZN_LANE_COMM = 1, ZN_LANE_OPT = 2, ZN_LANE_AUX = 3 };
 void zn_lane_switch(zn_ctx *ctx, int lane);       // makes `lane` the active one (stream + scratch)
