@@ -315,6 +315,13 @@ ZN_API int32_t zn_wait_poll(zn_poll_ready_fn ready, zn_poll_error_fn comm_error,
  * nothing ever arrives at, and reports code 99; the second writes `code` into the status word from the host. */
 ZN_API zn_status zn_debug_bounded_wait_probe(zn_ctx *ctx, int64_t limit_cycles);
 ZN_API zn_status zn_debug_set_device_status(zn_ctx *ctx, int32_t code);
+/* Which tensor-core GEMM form a product of this shape would get on a GPU of `sm_count` SMs with `reserve_sms` of
+ * them left free (elem_type 0 = bf16, 1 = tf32; `stageable` = C is a single, only-written block with 16-byte
+ * aligned base and pitch).  Host arithmetic only, no device needed; no counterpart in the reference.
+ * out[0] kernel (0 one-CTA, 1 two-CTA), out[1] tile columns, out[2] results staged through shared memory,
+ * out[3] epilogue warps per CTA, out[4] rows of tiles per band, out[5] k-blocks of the main loop. */
+ZN_API zn_status zn_debug_tc_route(int32_t elem_type, int64_t m, int64_t n, int64_t k, int32_t sm_count,
+                                   int32_t reserve_sms, int32_t stageable, int32_t out[6]);
 
 /* ---- measurement ------------------------------------------------------------------ */
 /* Per-kernel-family CUDA-event timing on the compute stream. */

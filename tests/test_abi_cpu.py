@@ -69,3 +69,50 @@ def test_product_package_does_not_touch_the_oracle():
             if f.endswith((".py", ".cu", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "zn_oracle" not in text and "import oracle" not in text and "from oracle" not in text, f
+
+
+def _route(elem, m, n, k, sms=148, reserve=0, stageable=1):
+    out = (C.c_int32 * 6)()
+    assert _lib.lib.zn_debug_tc_route(elem, m, n, k, sms, reserve, stageable, out) == 0
+    return dict(zip(("pair", "tile_cols", "staged", "epi_warps", "band", "k_blocks"), out))
+
+
+@pytest.mark.skipif(any(v in os.environ for v in ("ZN_TC_PAIR", "ZN_TC_NARROW", "ZN_TC_PAIR8", "ZN_TC_STAGED_STORE", "ZN_TC_BAND")),
+                    reason="a diagnostic switch overrides the routing")
+def test_tensor_core_gemm_routing():
+    """Which tcgen05 GEMM form a product gets (host arithmetic, no device): the two-CTA kernel where the main loop is
+    long AND its 256 x 256 tiles fill the 74 SM pairs more than once; otherwise the one-CTA kernel, with 128-column
+    tiles where N fits one or the 256-column tiles would leave more than half the SMs idle."""
+    BF16, TF32 = 0, 1
+    # the wide MLP's products at 65,536 rows and at one rank's 8,192 rows of the 8-GPU step: two-CTA, per-thread stores
+    for rows in (65536, 8192):
+        for (m, n, k) in ((rows, 8192, 4096), (rows, 8192, 8192), (4096, 8192, rows), (8192, 8192, rows), (rows, 4096, 8192)):
+            r = _route(BF16, m, n, k)
+            assert (r["pair"], r["tile_cols"], r["staged"], r["epi_warps"]) == (1, 256, 0, 4), (m, n, k, r)
+    # band height: 16 row tiles while a band's A strips stay within 34 MB (K up to 4096 bf16), else 8
+    assert _route(BF16, 65536, 8192, 4096)["band"] == 16 and _route(BF16, 65536, 8192, 8192)["band"] == 8
+    assert _route(TF32, 65536, 8192, 2048)["band"] == 16 and _route(TF32, 65536, 8192, 4096)["band"] == 8
+    # a data-parallel step leaves 32 SMs free during its last GEMM's first rows: still two-CTA
+    assert _route(BF16, 8192, 4096, 8192, reserve=32)["pair"] == 1
+    # short main loop (at most 16 k-blocks: 1024 bf16 / 512 tf32 values): one-CTA, staged stores, 8 epilogue warps
+    r = _route(BF16, 65536, 512, 512)
+    assert (r["pair"], r["tile_cols"], r["staged"], r["epi_warps"], r["k_blocks"]) == (0, 256, 1, 8, 8)
+    assert _route(BF16, 4096, 4096, 1024)["pair"] == 0 and _route(BF16, 4096, 4096, 1088)["pair"] == 1
+    assert _route(TF32, 4096, 4096, 512)["pair"] == 0 and _route(TF32, 4096, 4096, 544)["pair"] == 1
+    # a single wave of 256 x 256 tiles (2048^3: 64 tiles for 74 SM pairs) stays on the one-CTA kernel, two waves do not
+    assert _route(BF16, 2048, 2048, 2048)["pair"] == 0 and _route(BF16, 4096, 4096, 4096)["pair"] == 1
+    assert _route(BF16, 2048, 2048, 2048)["tile_cols"] == 256          # 128 wide tiles: enough for 148 SMs
+    # few tiles: 128-column tiles double them (1024^3: 32 -> 64; the 784-512-256-10 network's layers)
+    for shape in ((1024, 1024, 1024), (1024, 512, 784), (784, 512, 1024), (1024, 256, 512), (1024, 10, 256), (130, 10, 256)):
+        for elem in (BF16, TF32):
+            r = _route(elem, *shape)
+            assert (r["pair"], r["tile_cols"]) == (0, 128), (shape, elem, r)
+    # one row tile never pairs, whatever K
+    assert _route(BF16, 128, 8192, 8192)["pair"] == 0 and _route(BF16, 64, 2048, 1500)["pair"] == 0
+    # C += ..., two outputs or an odd pitch: per-thread stores in whichever kernel
+    assert _route(BF16, 65536, 512, 512, stageable=0)["staged"] == 0 and _route(BF16, 1024, 1024, 1024, stageable=0)["staged"] == 0
+    # bad arguments are refused
+    out = (C.c_int32 * 6)()
+    assert _lib.lib.zn_debug_tc_route(2, 128, 128, 128, 148, 0, 1, out) != 0
+    assert _lib.lib.zn_debug_tc_route(0, 0, 128, 128, 148, 0, 1, out) != 0
+    assert _lib.lib.zn_debug_tc_route(0, 128, 128, 128, 148, 0, 1, None) != 0

@@ -104,6 +104,7 @@ SIGNATURES = {
     "zn_wait_poll": (i32, [vp, vp, vp, C.c_int64, C.POINTER(i32)]),
     "zn_debug_bounded_wait_probe": (i32, [vp, C.c_int64]),
     "zn_debug_set_device_status": (i32, [vp, i32]),
+    "zn_debug_tc_route": (i32, [i32, C.c_int64, C.c_int64, C.c_int64, i32, i32, i32, C.POINTER(i32)]),
     "zn_profile_enable": (i32, [vp, i32]),
     "zn_profile_reset": (i32, [vp]),
     "zn_profile_get": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),

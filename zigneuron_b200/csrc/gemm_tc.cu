@@ -1212,6 +1212,73 @@ zn_status make_tmap(zn_ctx *ctx, CUtensorMap *out, int es, const void *ptr, int6
     return ZN_OK;
 }
 
+// Which kernel, tile width, output path and band height a product gets.  Pure host arithmetic on the shape, the SM
+// count and the environment's diagnostic switches, so that it can be checked without a device (zn_debug_tc_route).
+struct TcRoute {
+    bool use_pair, pair8, narrow, want_staged;
+    int bn, num_k_blocks, band;
+};
+TcRoute tc_route(int elem_type, int64_t m, int64_t n, int64_t k, int sm_count, int reserve_sms, bool stageable) {
+    const int es = elem_type == 0 ? 2 : 4;
+    const int bk = ROW_BYTES / es;
+    // Which kernel.  The two-CTA kernel halves the operand traffic per SM and wins wherever the main loop is long.
+    // With a short main loop (K of at most 16 k-blocks: 1024 bf16 / 512 tf32 values) a tile is over before the
+    // pair's cluster-wide hand-shakes pay off and the one-CTA kernel is faster: measured in bf16, 65536 x 512 x 512
+    // 665 against 510-530 TFLOP/s, 1024^3 114-128 against 103, 256^3 12.8 against 16.8 us per launch.
+    // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
+    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
+    const int num_k_blocks = (int)((k + bk - 1) / bk);
+    // A product whose 256 x 256 tiles do not fill the SM pairs more than once also goes to the one-CTA kernel: in a
+    // single wave nothing hides the epilogue of the large tile, and the smaller tiles reach more SMs.  Measured,
+    // one-CTA against two-CTA kernel: 2048^3 bf16 692-741 against 635-639 TFLOP/s, 1024^3 tf32 88-103 against 73-86,
+    // the 784-512-256-10 training step at batch 1024 in tf32 0.205 against 0.238 ms.
+    const long long pair_tiles_all = (long long)((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    const int pair_clusters = sm_count / 2 - (reserve_sms + 1) / 2;
+    const bool long_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && num_k_blocks > 16 && pair_tiles_all > pair_clusters));
+    // Option: a form of the two-CTA kernel with 8 epilogue warps and staged stores for short main loops with more
+    // than one wave of 256 x 256 tiles (per 128 x 256 of output and k-block it takes in 32 KB where the one-CTA
+    // kernel takes in 48 KB).  Measured against the one-CTA kernel in bf16: 65536 x 512 x 512 578-594 against
+    // 633-683 TFLOP/s, 4096 x 4096 x 512 488-493 against 552-573, 8192 x 2048 x 256 273-275 against 342-371 (tf32
+    // within 5 % either way): the pair's hand-over of tile indices across the cluster costs more per tile than
+    // the operand bytes saved, so it is off unless asked for.  It needs C to be stageable (see below).
+    // ZN_TC_PAIR8=1 / 2: for those short main loops / for every product the two-CTA kernel takes.
+    static const int pair8_mode = getenv("ZN_TC_PAIR8") ? atoi(getenv("ZN_TC_PAIR8")) : 0;
+    static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : -1;
+    const bool short_pair = pair_mode == 1 && pair8_mode == 1 && m > BM && num_k_blocks <= 16 && pair_tiles_all > pair_clusters;
+    const bool pair8 = stageable && staged_mode != 0 && (short_pair || (long_pair && pair8_mode == 2));
+    const bool use_pair = long_pair || (short_pair && pair8);
+    // Tile width of the one-CTA kernel: 128 columns instead of 256 where N fits one narrow tile, or where the wide
+    // tiles would occupy at most half the SMs (twice the tiles, each half the work).
+    // ZN_TC_NARROW=0 / 2: never / always in the one-CTA kernel (diagnostic).
+    static const int narrow_mode = getenv("ZN_TC_NARROW") ? atoi(getenv("ZN_TC_NARROW")) : 1;
+    const long long wide_tiles = (long long)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const bool narrow = !use_pair && (narrow_mode == 2 || (narrow_mode == 1 && (n <= 128 || 2 * wide_tiles <= sm_count - reserve_sms)));
+    const int bn = narrow ? 128 : BN;
+
+    // Output path.  Either every thread stores its own row of the tile straight from the registers the accumulator
+    // was read into (32-byte pieces, one row per lane: an instruction touches 32 different lines, and the L1 store
+    // path takes about two cycles per line, 5 us for a 128 x 256 fp32 tile), or the epilogue warps stage 32 x 32
+    // blocks in shared memory and the TMA unit writes them as whole 128-byte lines.  The one-CTA kernel, whose tiles
+    // have a short main loop and so wait for their epilogue, stages; the two-CTA kernel, whose epilogue hides under
+    // the next tile's long main loop and whose TMA unit is busy with operand loads, stores per thread (measured
+    // there, staged against per-thread: 16384^3 TN 1188 against 1245 TFLOP/s, the 8192-wide training step 58.1
+    // against 57.5 ms); its variant for short main loops stages.  ZN_TC_STAGED_STORE=0 / 1 forces one path in both
+    // kernels (diagnostic).  Staging needs C to be ONE block the unit can address (16-byte aligned base and row
+    // pitch) that is only written; C += ..., two outputs at once and odd pitches always take the per-thread stores.
+    const bool want_staged = stageable && (pair8 || (staged_mode < 0 ? !use_pair : staged_mode != 0));
+    // Rows of tiles per band.  A wave of 74 tile pairs shares `band` strips of A and about 74 / band strips of B;
+    // 8 gives the fewest distinct strips (8 + 9.25), i.e. the fewest DRAM reads per wave, and 16 keeps a band's A
+    // strips (band x 256 rows x K) in L2 across the waves of the band as long as they are small enough.  So: 16
+    // while the A strips of such a band stay within 34 MB (K up to 4096 bf16), else 8.  Measured on the 8192-wide
+    // training step (ncu, 8192 rows): an 8192 x 8192 x 8192 product reads 0.99 GB from DRAM with bands of 8 and
+    // 1.25 GB with 16, an 8192 x 8192 x 4096 product 0.34 GB against 0.22 GB; under the 1 kW cap the DRAM power
+    // saved raises the SM clock (median 1567 -> 1634 MHz) and the step went from 57.2 to 56.5 ms.
+    // ZN_TC_BAND overrides (diagnostic).
+    static const int band_env = [] { const char *e = getenv("ZN_TC_BAND"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 64 ? v : 0; }();
+    const int band = band_env ? band_env : ((long long)16 * 256 * k * es <= (34ll << 20) ? 16 : 8);
+    return TcRoute{use_pair, pair8, narrow, want_staged, bn, num_k_blocks, band};
+}
+
 }   // namespace
 
 extern "C" zn_status zn_debug_bounded_wait_probe(zn_ctx *ctx, int64_t limit_cycles) {
@@ -1222,6 +1289,19 @@ extern "C" zn_status zn_debug_bounded_wait_probe(zn_ctx *ctx, int64_t limit_cycl
     ctx->launches += 1;
     bounded_wait_probe_kernel<<<1, 64, 0, ctx->stream>>>(ctx->status_dev, (long long)limit_cycles);
     ZN_CUDA(ctx, cudaGetLastError());
+    return ZN_OK;
+}
+
+extern "C" zn_status zn_debug_tc_route(int32_t elem_type, int64_t m, int64_t n, int64_t k, int32_t sm_count, int32_t reserve_sms,
+                                        int32_t stageable, int32_t out[6]) {
+    if (!out || m <= 0 || n <= 0 || k <= 0 || sm_count <= 0 || (elem_type != 0 && elem_type != 1)) return ZN_ERR_INVALID_VALUE;
+    const TcRoute r = tc_route(elem_type, m, n, k, sm_count, reserve_sms, stageable != 0);
+    out[0] = r.use_pair ? 1 : 0;
+    out[1] = r.use_pair ? 256 : r.bn;
+    out[2] = r.want_staged ? 1 : 0;
+    out[3] = r.use_pair ? (r.pair8 ? 8 : 4) : EPI1;
+    out[4] = r.band;
+    out[5] = r.num_k_blocks;
     return ZN_OK;
 }
 
@@ -1251,29 +1331,6 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         attr_set_mask.fetch_or(dev_bit);
     }
 
-    // Which kernel.  The two-CTA kernel halves the operand traffic per SM and wins wherever the main loop is long.
-    // With a short main loop (K of at most 16 k-blocks: 1024 bf16 / 512 tf32 values) a tile is over before the
-    // pair's cluster-wide hand-shakes pay off and the one-CTA kernel is faster: measured in bf16, 65536 x 512 x 512
-    // 665 against 510-530 TFLOP/s, 1024^3 114-128 against 103, 256^3 12.8 against 16.8 us per launch.
-    // ZN_TC_PAIR=0 / 2: one-CTA kernel only / two-CTA kernel wherever it can run (diagnostic).
-    static const int pair_mode = getenv("ZN_TC_PAIR") ? atoi(getenv("ZN_TC_PAIR")) : 1;
-    const int num_k_blocks = (int)((k + bk - 1) / bk);
-    // A product whose 256 x 256 tiles do not fill the SM pairs more than once also goes to the one-CTA kernel: in a
-    // single wave nothing hides the epilogue of the large tile, and the smaller tiles reach more SMs.  Measured,
-    // one-CTA against two-CTA kernel: 2048^3 bf16 692-741 against 635-639 TFLOP/s, 1024^3 tf32 88-103 against 73-86,
-    // the 784-512-256-10 training step at batch 1024 in tf32 0.205 against 0.238 ms.
-    const long long pair_tiles_all = (long long)((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
-    const int pair_clusters = ctx->sm_count / 2 - (e.reserve_sms + 1) / 2;
-    const bool long_pair = m > BM && (pair_mode == 2 || (pair_mode == 1 && num_k_blocks > 16 && pair_tiles_all > pair_clusters));
-    // Option: a form of the two-CTA kernel with 8 epilogue warps and staged stores for short main loops with more
-    // than one wave of 256 x 256 tiles (per 128 x 256 of output and k-block it takes in 32 KB where the one-CTA
-    // kernel takes in 48 KB).  Measured against the one-CTA kernel in bf16: 65536 x 512 x 512 578-594 against
-    // 633-683 TFLOP/s, 4096 x 4096 x 512 488-493 against 552-573, 8192 x 2048 x 256 273-275 against 342-371 (tf32
-    // within 5 % either way): the pair's hand-over of tile indices across the cluster costs more per tile than
-    // the operand bytes saved, so it is off unless asked for.  It needs C to be stageable (see below).
-    // ZN_TC_PAIR8=1 / 2: for those short main loops / for every product the two-CTA kernel takes.
-    static const int pair8_mode = getenv("ZN_TC_PAIR8") ? atoi(getenv("ZN_TC_PAIR8")) : 0;
-    static const int staged_mode = getenv("ZN_TC_STAGED_STORE") ? atoi(getenv("ZN_TC_STAGED_STORE")) : -1;
     const bool tf32 = elem_type != 0;
     bool stageable = false;        // C is one block the TMA unit can address and is only written
     if (!e.accumulate && (e.out_f32 != nullptr) != (e.out_t != nullptr)) {
@@ -1282,16 +1339,9 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
         const int ces = (e.out_f32 != nullptr || tf32) ? 4 : 2;
         stageable = (reinterpret_cast<uintptr_t>(cptr) & 15) == 0 && (ldc * ces) % 16 == 0 && ldc >= n;
     }
-    const bool short_pair = pair_mode == 1 && pair8_mode == 1 && m > BM && num_k_blocks <= 16 && pair_tiles_all > pair_clusters;
-    const bool pair8 = stageable && staged_mode != 0 && (short_pair || (long_pair && pair8_mode == 2));
-    const bool use_pair = long_pair || (short_pair && pair8);
-    // Tile width of the one-CTA kernel: 128 columns instead of 256 where N fits one narrow tile, or where the wide
-    // tiles would occupy at most half the SMs (twice the tiles, each half the work).
-    // ZN_TC_NARROW=0 / 2: never / always in the one-CTA kernel (diagnostic).
-    static const int narrow_mode = getenv("ZN_TC_NARROW") ? atoi(getenv("ZN_TC_NARROW")) : 1;
-    const long long wide_tiles = (long long)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-    const bool narrow = !use_pair && (narrow_mode == 2 || (narrow_mode == 1 && (n <= 128 || 2 * wide_tiles <= ctx->sm_count - e.reserve_sms)));
-    const int bn = narrow ? 128 : BN;
+    const TcRoute route = tc_route(elem_type, m, n, k, ctx->sm_count, e.reserve_sms, stageable);
+    const bool use_pair = route.use_pair, pair8 = route.pair8, narrow = route.narrow;
+    const int bn = route.bn, num_k_blocks = route.num_k_blocks;
 
     CUtensorMap tmA, tmB;
     if (!a_mn) ZN_TRY(make_tmap(ctx, &tmA, es, a, k, m, lda, bk, BM, 0));         // [m][k]: inner k
@@ -1321,17 +1371,7 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
     p.out_f32 = e.out_f32; p.ld_out_f32 = e.ld_out_f32; p.out_t = e.out_t; p.ld_out_t = e.ld_out_t;
     p.accumulate = e.accumulate;
     p.out_mode = 0;
-    // Rows of tiles per band.  A wave of 74 tile pairs shares `band` strips of A and about 74 / band strips of B;
-    // 8 gives the fewest distinct strips (8 + 9.25), i.e. the fewest DRAM reads per wave, and 16 keeps a band's A
-    // strips (band x 256 rows x K) in L2 across the waves of the band as long as they are small enough.  So: 16
-    // while the A strips of such a band stay within 34 MB (K up to 4096 bf16), else 8.  Measured on the 8192-wide
-    // training step (ncu, 8192 rows): an 8192 x 8192 x 8192 product reads 0.99 GB from DRAM with bands of 8 and
-    // 1.25 GB with 16, an 8192 x 8192 x 4096 product 0.34 GB against 0.22 GB; under the 1 kW cap the DRAM power
-    // saved raises the SM clock (median 1567 -> 1634 MHz) and the step went from 57.2 to 56.5 ms.
-    // ZN_TC_BAND overrides (diagnostic).
-    static const int band_env = [] { const char *e = getenv("ZN_TC_BAND"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 64 ? v : 0; }();
-    const int band = band_env ? band_env : ((long long)16 * 256 * k * es <= (34ll << 20) ? 16 : 8);
-    p.band = band;
+    p.band = route.band;
 #ifdef ZN_DIAG
     // ZN_TC_PHASES=1 (diagnostic builds): CTA 0 of every one-CTA launch stamps its phases; the host waits for the launch
     // and prints them relative to the kernel's first stamp
@@ -1377,21 +1417,9 @@ zn_status zn_gemm_tc(zn_ctx *ctx, int elem_type, const void *a, int64_t lda, boo
 
     zn_launch_scope scope(ctx, ZN_PROF_GEMM_TC, 2.0 * m * n * k,
                           (double)es * (m * k + k * n) + (e.out_f32 ? 4.0 : (double)es) * m * n);
-    // Output path.  Either every thread stores its own row of the tile straight from the registers the accumulator
-    // was read into (32-byte pieces, one row per lane: an instruction touches 32 different lines, and the L1 store
-    // path takes about two cycles per line, 5 us for a 128 x 256 fp32 tile), or the epilogue warps stage 32 x 32
-    // blocks in shared memory and the TMA unit writes them as whole 128-byte lines.  The one-CTA kernel, whose tiles
-    // have a short main loop and so wait for their epilogue, stages; the two-CTA kernel, whose epilogue hides under
-    // the next tile's long main loop and whose TMA unit is busy with operand loads, stores per thread (measured
-    // there, staged against per-thread: 16384^3 TN 1188 against 1245 TFLOP/s, the 8192-wide training step 58.1
-    // against 57.5 ms); its variant for short main loops stages.  ZN_TC_STAGED_STORE=0 / 1 forces one path in both
-    // kernels (diagnostic).  Staging needs C to
-    // be ONE block the unit can address (16-byte aligned base and row pitch) that is only written; C += ..., two
-    // outputs at once and odd pitches always take the per-thread stores.
-    const bool want_staged = pair8 || (staged_mode < 0 ? !use_pair : staged_mode != 0);
     CUtensorMap tmC;
     memset(&tmC, 0, sizeof tmC);
-    if (want_staged && stageable) {
+    if (route.want_staged) {
         const bool wide = e.out_f32 != nullptr || tf32;                  // 4-byte results
         const void *cptr = e.out_f32 ? (const void *)e.out_f32 : (const void *)e.out_t;
         const int64_t ldc = e.out_f32 ? e.ld_out_f32 : e.ld_out_t;
